@@ -1,0 +1,170 @@
+"""ctypes view of the C ABI (``include/bfly.h``) for callers that hold raw device pointers.
+
+The torch operators go through the same entry points from C++; this module exists so that
+tests and benchmarks can drive ``libbfly_b200.so`` directly, the way a non-torch host
+(the reference's own FFI, a C++ server) would.  All functions take torch CUDA tensors only
+to obtain device pointers and strides; nothing is copied.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libbfly_b200.so")
+
+F32, C64 = 0, 1
+
+# every symbol include/bfly.h declares
+SYMBOLS = (
+    "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
+    "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
+    "bfly4_bw_f32", "bfly_launch_count",
+)
+
+_lib = None
+
+
+def lib():
+    """The loaded library (raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("libbfly_b200.so not built; run `python -m butterfly_b200._build`")
+        L = ctypes.CDLL(LIB_PATH)
+        L.bfly_strerror.restype = ctypes.c_char_p
+        L.bfly_strerror.argtypes = [ctypes.c_int]
+        L.bfly_bw_workspace_bytes.restype = ctypes.c_int64
+        L.bfly4_bw_workspace_bytes.restype = ctypes.c_int64
+        L.bfly_launch_count.restype = ctypes.c_int64
+        _lib = L
+    return _lib
+
+
+def strerror(rc):
+    return lib().bfly_strerror(int(rc)).decode()
+
+
+class BflyError(RuntimeError):
+    def __init__(self, rc, what):
+        super().__init__("%s failed: %s (status %d)" % (what, strerror(rc), rc))
+        self.status = rc
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr() if (t is not None and t.numel() > 0) else 0)
+
+
+def _i64(v):
+    return ctypes.c_int64(int(v))
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check_rows(t):
+    assert t.is_cuda and t.dim() == 3 and (t.size(2) <= 1 or t.stride(2) == 1)
+
+
+def fw(twiddle, x, increasing_stride=True, output_size=None, out=None, check=True):
+    """``bfly_fw_f32`` / ``bfly_fw_c64``.  Returns the (batch, nstacks, n) output buffer and the status."""
+    _check_rows(x)
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    output_size = n if output_size is None else output_size
+    if out is None:
+        out = torch.empty(B, S, n, dtype=x.dtype, device=x.device)
+    fn = lib().bfly_fw_f32 if x.dtype == torch.float32 else lib().bfly_fw_c64
+    rc = fn(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(B), int(S), int(log_n),
+            int(nblocks), int(in_size), int(output_size), int(bool(increasing_stride)), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_fw")
+    return out, rc
+
+
+def bw_workspace_bytes(dtype, B, S, log_n, nblocks, base4=False):
+    code = F32 if dtype == torch.float32 else C64
+    fn = lib().bfly4_bw_workspace_bytes if base4 else lib().bfly_bw_workspace_bytes
+    return int(fn(code, int(B), int(S), int(log_n), int(nblocks)))
+
+
+def bw(twiddle, x, grad, increasing_stride=True, workspace=None, d_twiddle=None, d_x=None, check=True):
+    """``bfly_bw_f32`` / ``bfly_bw_c64``.  Returns (d_twiddle, d_x buffer (batch, nstacks, max(in, n)), status)."""
+    _check_rows(x)
+    _check_rows(grad)
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    out_size = grad.shape[2]
+    if d_twiddle is None:
+        d_twiddle = torch.empty_like(twiddle)
+    if d_x is None:
+        d_x = torch.empty(B, S, max(in_size, n), dtype=x.dtype, device=x.device)
+    need = bw_workspace_bytes(x.dtype, B, S, log_n, nblocks)
+    if need < 0:
+        if check:
+            raise BflyError(need, "bfly_bw_workspace_bytes")
+        return d_twiddle, d_x, need
+    if workspace is None and need > 0:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    ws_bytes = 0 if workspace is None else workspace.numel()
+    fn = lib().bfly_bw_f32 if x.dtype == torch.float32 else lib().bfly_bw_c64
+    rc = fn(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(grad), _i64(grad.stride(0)),
+            _i64(grad.stride(1)), _p(d_twiddle), _p(d_x), int(B), int(S), int(log_n), int(nblocks), int(in_size),
+            int(out_size), int(bool(increasing_stride)), _p(workspace), ctypes.c_size_t(ws_bytes), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_bw")
+    return d_twiddle, d_x, rc
+
+
+def fw_base4(twiddle4, twiddle2, x, increasing_stride=True, output_size=None, out=None, check=True):
+    """``bfly4_fw_f32``."""
+    _check_rows(x)
+    S, nblocks = twiddle4.shape[:2]
+    log_n = twiddle4.shape[2] * 2 + twiddle2.shape[2]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    output_size = n if output_size is None else output_size
+    if out is None:
+        out = torch.empty(B, S, n, dtype=x.dtype, device=x.device)
+    rc = lib().bfly4_fw_f32(_p(twiddle4), _p(twiddle2), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(B),
+                            int(S), int(log_n), int(nblocks), int(in_size), int(output_size),
+                            int(bool(increasing_stride)), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly4_fw")
+    return out, rc
+
+
+def bw_base4(twiddle4, twiddle2, x, grad, increasing_stride=True, workspace=None, check=True):
+    """``bfly4_bw_f32``.  Returns (d_twiddle4, d_twiddle2, d_x buffer, status)."""
+    _check_rows(x)
+    _check_rows(grad)
+    S, nblocks = twiddle4.shape[:2]
+    log_n = twiddle4.shape[2] * 2 + twiddle2.shape[2]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    out_size = grad.shape[2]
+    d4 = torch.empty_like(twiddle4)
+    d2 = torch.empty_like(twiddle2)
+    d_x = torch.empty(B, S, max(in_size, n), dtype=x.dtype, device=x.device)
+    need = bw_workspace_bytes(x.dtype, B, S, log_n, nblocks, base4=True)
+    if need < 0:
+        if check:
+            raise BflyError(need, "bfly4_bw_workspace_bytes")
+        return d4, d2, d_x, need
+    if workspace is None and need > 0:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    ws_bytes = 0 if workspace is None else workspace.numel()
+    rc = lib().bfly4_bw_f32(_p(twiddle4), _p(twiddle2), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(grad),
+                            _i64(grad.stride(0)), _i64(grad.stride(1)), _p(d4), _p(d2), _p(d_x), int(B), int(S),
+                            int(log_n), int(nblocks), int(in_size), int(out_size), int(bool(increasing_stride)),
+                            _p(workspace), ctypes.c_size_t(ws_bytes), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly4_bw")
+    return d4, d2, d_x, rc
+
+
+def launch_count():
+    return int(lib().bfly_launch_count())

@@ -1,0 +1,226 @@
+// Host driver shared by the CUDA library and the test-suite's host emulator: validates
+// arguments, plans the launches and hands filled parameter blocks to an executor.
+//
+// Executor concept (E):
+//   int  num_sms() const;
+//   int  run_fw(const FwParams<T>&);                       // one forward launch
+//   int  run_bw(const BwParams<T>&, int KW);               // one backward-phase launch
+//   int  zero(void* ptr, size_t bytes);                    // async memset
+//   int  zero2d(void* ptr, size_t pitch_bytes, size_t width_bytes, size_t rows);
+#pragma once
+#include "bfly_plan.h"
+
+namespace bfly {
+
+template <typename T> struct KernelCfg;
+template <> struct KernelCfg<float> {
+  static constexpr int kFwKmax = 4;
+  static constexpr int kThreads = 256;
+  static int bw_kw(int log_n) { return log_n >= 2 ? 2 : 1; }
+  static int bw_max_sg(int kw) { return kw == 2 ? 5 : 10; }
+};
+template <> struct KernelCfg<cf> {
+  static constexpr int kFwKmax = 3;
+  static constexpr int kThreads = 256;
+  static int bw_kw(int) { return 1; }
+  static int bw_max_sg(int) { return 10; }
+};
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+template <typename T> inline bool vec_ok(const void* p, int64_t sB, int64_t sS) {
+  return aligned16(p) && (sB * (int64_t)sizeof(T)) % 16 == 0 && (sS * (int64_t)sizeof(T)) % 16 == 0;
+}
+
+struct Problem {
+  int B, S, log_n, nblocks, in_size, out_size;
+  bool inc, base4;
+};
+
+inline int check_problem(const Problem& q) {
+  if (q.B < 0 || q.S < 1 || q.log_n < 1 || q.log_n > 24 || q.nblocks < 1) return BFLY_E_ARG;
+  if (q.in_size < 0 || q.out_size < 0 || q.out_size > (1 << q.log_n)) return BFLY_E_ARG;
+  return BFLY_OK;
+}
+
+inline std::vector<Stage> problem_stages(const Problem& q) {
+  return q.base4 ? make_stages_r4(q.log_n, q.nblocks, q.inc) : make_stages_r2(q.log_n, q.nblocks, q.inc);
+}
+// elements per stack of the radix-2 (`which` 0) and radix-4 (`which` 1) twiddle tensors
+inline void twiddle_stack_sizes(const Problem& q, int64_t out[2]) {
+  const int64_t n = (int64_t)1 << q.log_n;
+  if (q.base4) {
+    out[0] = (int64_t)q.nblocks * (q.log_n % 2) * (n / 2) * 4;
+    out[1] = (int64_t)q.nblocks * (q.log_n / 2) * (n / 4) * 16;
+  } else {
+    out[0] = (int64_t)q.nblocks * q.log_n * (n / 2) * 4;
+    out[1] = 0;
+  }
+}
+
+// Run stages [t0, t1) of the product with the row-owner forward kernel.  `cuts` lists the
+// stage indices after which a snapshot is written (slot i -> snaps[i]); `out` may be null.
+template <typename T, typename E>
+int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int t1,
+                   const std::vector<int>& cuts, T* const* snaps, const T* tw2, const T* tw4, const T* x,
+                   int64_t x_sB, int64_t x_sS, int x_cols, T* out, int64_t out_sB, int64_t out_sS,
+                   int out_cols) {
+  if (q.B == 0 || t1 <= t0) return BFLY_OK;
+  if (((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;
+  const Panel pn = full_row_panel(q.log_n);
+  std::vector<FwGroup> groups;
+  if (!plan_fw_groups(st, t0, t1, cuts, pn, SwBits<T>::value, KernelCfg<T>::kFwKmax, groups))
+    return BFLY_E_UNSUPPORTED;
+  int64_t stk[2];
+  twiddle_stack_sizes(q, stk);
+  const int64_t n = (int64_t)1 << q.log_n;
+  size_t g0 = 0;
+  bool first = true;
+  while (g0 < groups.size()) {
+    const size_t g1 = std::min(groups.size(), g0 + (size_t)kMaxFwGroups);
+    const bool last = (g1 == groups.size());
+    FwParams<T> p;
+    std::memset(&p, 0, sizeof(p));
+    p.tw[0] = tw2; p.tw[1] = tw4; p.tw_stack[0] = stk[0]; p.tw_stack[1] = stk[1];
+    if (first) {
+      p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
+    } else {  // continue in place from the full-width rows written by the previous launch
+      if (!out) return BFLY_E_UNSUPPORTED;
+      p.x = out; p.x_sB = out_sB; p.x_sS = out_sS; p.x_cols = (int)n;
+    }
+    p.out = out; p.out_sB = out_sB; p.out_sS = out_sS;
+    p.out_cols = last ? out_cols : (int)n;
+    for (int i = 0; i < kMaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
+    p.B = q.B; p.S = q.S; p.log_n = q.log_n;
+    p.R = fw_rows_per_tile<T>(q.log_n, q.B);
+    p.vec_in = vec_ok<T>(p.x, p.x_sB, p.x_sS);
+    p.vec_out = out ? vec_ok<T>(out, out_sB, out_sS) : 1;
+    p.panel = pn;
+    p.ngroups = (int)(g1 - g0);
+    for (size_t g = g0; g < g1; ++g) p.g[g - g0] = groups[g];
+    const int rc = ex.run_fw(p);
+    if (rc != BFLY_OK) return rc;
+    g0 = g1;
+    first = false;
+  }
+  return BFLY_OK;
+}
+
+template <typename T, typename E>
+int drive_fw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, int64_t x_sB, int64_t x_sS,
+             T* out) {
+  int rc = check_problem(q);
+  if (rc != BFLY_OK) return rc;
+  if (q.B == 0) return BFLY_OK;
+  if (!x || !out || (!tw2 && !tw4)) return BFLY_E_ARG;
+  if ((tw2 && !aligned16(tw2)) || (tw4 && !aligned16(tw4))) return BFLY_E_ALIGN;
+  const std::vector<Stage> st = problem_stages(q);
+  const int64_t n = (int64_t)1 << q.log_n;
+  return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), {}, nullptr, tw2, tw4, x, x_sB, x_sS, q.in_size,
+                           out, (int64_t)q.S * n, n, q.out_size);
+}
+
+template <typename T> struct BwLayout {
+  std::vector<BwPhase> phases;
+  int kw;
+  size_t ws_bytes;
+};
+
+template <typename T>
+int plan_bw(const Problem& q, BwLayout<T>& lay) {
+  const std::vector<Stage> st = problem_stages(q);
+  lay.kw = KernelCfg<T>::bw_kw(q.log_n);
+  int logCmax = 0;
+  while ((1 << logCmax) < (KernelCfg<T>::kThreads << lay.kw)) ++logCmax;
+  lay.phases = plan_bw_phases(st, q.log_n, logCmax, lay.kw, KernelCfg<T>::bw_max_sg(lay.kw), SwBits<T>::value);
+  if (lay.phases.empty()) return BFLY_E_UNSUPPORTED;
+  if ((int)lay.phases.size() - 1 > kMaxSnap) return BFLY_E_UNSUPPORTED;
+  if (lay.phases.size() > 1 && ((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;
+  const size_t plane = (size_t)q.B * q.S * sizeof(T) << q.log_n;
+  lay.ws_bytes = (lay.phases.size() - 1) * ((plane + 255) / 256 * 256);
+  return BFLY_OK;
+}
+
+// Backward of the whole product.  d_x is (B, S, max(in_size, n)) contiguous and doubles as
+// the gradient buffer between phases; d_tw2 / d_tw4 are overwritten.
+template <typename T, typename E>
+int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, int64_t x_sB, int64_t x_sS,
+             const T* grad, int64_t g_sB, int64_t g_sS, T* d_tw2, T* d_tw4, T* d_x, void* ws,
+             size_t ws_bytes) {
+  int rc = check_problem(q);
+  if (rc != BFLY_OK) return rc;
+  int64_t stk[2];
+  twiddle_stack_sizes(q, stk);
+  if ((stk[0] && (!tw2 || !d_tw2)) || (stk[1] && (!tw4 || !d_tw4))) return BFLY_E_ARG;
+  if ((tw2 && !aligned16(tw2)) || (tw4 && !aligned16(tw4))) return BFLY_E_ALIGN;
+  if (stk[0]) { rc = ex.zero(d_tw2, (size_t)q.S * stk[0] * sizeof(T)); if (rc) return rc; }
+  if (stk[1]) { rc = ex.zero(d_tw4, (size_t)q.S * stk[1] * sizeof(T)); if (rc) return rc; }
+  if (q.B == 0) return BFLY_OK;
+  if (!x || !grad || !d_x) return BFLY_E_ARG;
+  BwLayout<T> lay;
+  rc = plan_bw<T>(q, lay);
+  if (rc != BFLY_OK) return rc;
+  if (lay.ws_bytes > 0 && (!ws || ws_bytes < lay.ws_bytes || !aligned16(ws))) return BFLY_E_WORKSPACE;
+  const std::vector<Stage> st = problem_stages(q);
+  const int64_t n = (int64_t)1 << q.log_n;
+  const int nph = (int)lay.phases.size();
+  const size_t plane = ((size_t)q.B * q.S * sizeof(T) << q.log_n);
+  const size_t plane_pad = (plane + 255) / 256 * 256;
+  T* snaps[kMaxSnap] = {nullptr};
+  std::vector<int> cuts;
+  for (int ph = 1; ph < nph; ++ph) {
+    snaps[ph - 1] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
+    cuts.push_back(lay.phases[ph].t0);
+  }
+  if (nph > 1) {
+    rc = drive_fw_range<T>(ex, q, st, 0, lay.phases[nph - 1].t0, cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size,
+                           (T*)nullptr, 0, 0, 0);
+    if (rc != BFLY_OK) return rc;
+  }
+  const int64_t DX = std::max<int64_t>(q.in_size, n);
+  for (int ph = nph - 1; ph >= 0; --ph) {
+    const BwPhase& P = lay.phases[ph];
+    BwParams<T> p;
+    std::memset(&p, 0, sizeof(p));
+    p.tw[0] = tw2; p.tw[1] = tw4; p.dtw[0] = d_tw2; p.dtw[1] = d_tw4;
+    p.tw_stack[0] = stk[0]; p.tw_stack[1] = stk[1];
+    if (ph == 0) { p.xin = x; p.xin_sB = x_sB; p.xin_sS = x_sS; p.xin_cols = q.in_size; }
+    else { p.xin = snaps[ph - 1]; p.xin_sB = (int64_t)q.S * n; p.xin_sS = n; p.xin_cols = (int)n; }
+    if (ph == nph - 1) { p.gin = grad; p.gin_sB = g_sB; p.gin_sS = g_sS; p.gin_cols = q.out_size; }
+    else { p.gin = d_x; p.gin_sB = (int64_t)q.S * DX; p.gin_sS = DX; p.gin_cols = (int)n; }
+    p.gout = d_x; p.gout_sB = (int64_t)q.S * DX; p.gout_sS = DX;
+    p.gout_cols = (ph == 0) ? (int)std::min<int64_t>(q.in_size, n) : (int)n;
+    p.B = q.B; p.S = q.S; p.log_n = q.log_n;
+    p.panel = P.panel;
+    p.nsg = P.nsg;
+    for (int j = 0; j < P.nsg; ++j) p.sg[j] = P.sg[j];
+    const size_t row_bytes = (size_t)(P.nsg + 1) * sizeof(T) << P.panel.logC;
+    int Rb = (int)(kSmemMax / row_bytes);
+    if (Rb > 16) Rb = 16;
+    if (Rb < 1) return BFLY_E_UNSUPPORTED;
+    // rows that run in parallel inside a CTA when the panel has fewer units than threads
+    const int U = (1 << P.panel.logC) >> lay.kw;
+    const int par = U >= KernelCfg<T>::kThreads ? 1 : KernelCfg<T>::kThreads / std::max(U, 1);
+    if (Rb < par && (size_t)par * row_bytes <= (size_t)kSmemMax) Rb = par;
+    if (Rb > q.B) Rb = std::max(q.B, 1);
+    p.Rb = Rb;
+    const int groups = (1 << P.panel.npanels_log) * q.S;
+    int nslices = std::max(1, ex.num_sms() / groups);
+    int rows = (q.B + nslices - 1) / nslices;
+    rows = (rows + Rb - 1) / Rb * Rb;
+    nslices = (q.B + rows - 1) / rows;
+    p.rows_per_cta = rows;
+    p.nslices = nslices;
+    p.vec_x = vec_ok<T>(p.xin, p.xin_sB, p.xin_sS);
+    p.vec_g = vec_ok<T>(p.gin, p.gin_sB, p.gin_sS);
+    p.vec_o = vec_ok<T>(p.gout, p.gout_sB, p.gout_sS);
+    rc = ex.run_bw(p, lay.kw);
+    if (rc != BFLY_OK) return rc;
+  }
+  if (q.in_size > n) {
+    rc = ex.zero2d(d_x + n, (size_t)DX * sizeof(T), (size_t)(q.in_size - n) * sizeof(T), (size_t)q.B * q.S);
+    if (rc != BFLY_OK) return rc;
+  }
+  return BFLY_OK;
+}
+
+}  // namespace bfly

@@ -1,0 +1,298 @@
+// CUDA kernels (sm_100a) and C ABI of the butterfly multiply library.
+//
+// Two kernel families:
+//  * bfly_fw_kernel: a CTA owns R whole batch rows in shared memory and runs every stage of
+//    the product on them in one launch.  Stages are grouped into register windows of up to
+//    4 bits: a thread pulls the 16 elements of its unit and the group's twiddles into
+//    registers, runs the group's stages register-to-register, and writes the elements back
+//    in place (one shared-memory round trip per group, twiddles amortised over the R rows).
+//  * bfly_bw_kernel: twiddle-stationary backward.  A CTA owns a column panel that is closed
+//    under the stages of one phase, keeps the twiddles AND the twiddle-gradient
+//    accumulators of those stages in registers for its whole life, and streams batches of
+//    rows through shared memory (forward recompute into per-sub-group snapshots, then the
+//    reverse sweep).  The accumulators are added to d_twiddle once, at the end.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "../../include/bfly.h"
+#include "bfly_core.h"
+#include "bfly_driver.h"
+
+namespace bfly {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) bfly_fw_kernel(const __grid_constant__ FwParams<T> p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* sm = reinterpret_cast<T*>(smem_raw);
+  const int tid = threadIdx.x;
+  const int64_t ntiles = fw_num_tiles(p);
+  const int64_t n = (int64_t)1 << p.log_n;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    int row0, stack, pbase;
+    fw_tile_coords(p, tile, row0, stack, pbase);
+    tile_load<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
+    __syncthreads();
+    for (int g = 0; g < p.ngroups; ++g) {
+      fw_group_dispatch<T>(p, p.g[g], sm, p.R, stack, pbase, tid, kThreads);
+      __syncthreads();
+      if (p.g[g].emit) {
+        tile_store<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm, tid, kThreads);
+        __syncthreads();
+      }
+    }
+    if (p.out) {
+      tile_store<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm, tid, kThreads);
+      __syncthreads();
+    }
+  }
+}
+
+template <typename T, int KW, int NSG>
+__global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_constant__ BwParams<T> p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* smX = reinterpret_cast<T*>(smem_raw);
+  const int C = 1 << p.panel.logC;
+  T* smG = smX + (size_t)p.nsg * p.Rb * C;
+  const int tid = threadIdx.x;
+  int pbase, stack, row_begin, row_end;
+  bw_cta_coords(p, blockIdx.x, pbase, stack, row_begin, row_end);
+  BwState<T, KW, NSG> st;
+  bw_load_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
+  for (int row0 = row_begin; row0 < row_end; row0 += p.Rb) {
+    const int R = p.Rb;
+    tile_load<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
+    tile_load<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NSG - 1; ++j) {
+      if (j + 1 < p.nsg) {
+        bw_sg_forward<T, KW, NSG>(p, st, j, smX, R, tid, kThreads);
+        __syncthreads();
+      }
+    }
+#pragma unroll
+    for (int j = NSG - 1; j >= 0; --j) {
+      if (j < p.nsg) {
+        bw_sg_backward<T, KW, NSG>(p, st, j, smX, smG, R, tid, kThreads);
+        __syncthreads();
+      }
+    }
+    tile_store<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
+    __syncthreads();
+  }
+  bw_flush_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
+}
+
+// ------------------------------------------------------------------ launch side
+
+static std::atomic<int64_t> g_launches{0};
+
+struct DeviceInfo {
+  int sms = 0;
+  bool ok = false;
+};
+
+static int device_info(DeviceInfo& out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BFLY_E_NODEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cache[dev].ok) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return BFLY_E_NODEVICE;
+    cache[dev].sms = sms;
+    cache[dev].ok = true;
+  }
+  out = cache[dev];
+  return BFLY_OK;
+}
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes) {
+  // the attribute is per device and cheap to set; set it on every launch that needs it
+  if (bytes > 48 * 1024) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return BFLY_E_CUDA;
+    }
+  }
+  return BFLY_OK;
+}
+
+struct CudaExec {
+  cudaStream_t stream;
+  DeviceInfo dev;
+  int num_sms() const { return dev.sms; }
+
+  template <typename T> int run_fw(const FwParams<T>& p) {
+    const size_t smem = (size_t)p.R * sizeof(T) << p.panel.logC;
+    int rc = set_smem(bfly_fw_kernel<T>, smem);
+    if (rc) return rc;
+    const int64_t ntiles = fw_num_tiles(p);
+    const int grid = (int)std::min<int64_t>(ntiles, dev.sms);
+    bfly_fw_kernel<T><<<grid, kThreads, smem, stream>>>(p);
+    g_launches.fetch_add(1);
+    return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+  }
+
+  template <typename T, int KW, int NSG> int launch_bw(const BwParams<T>& p) {
+    const size_t smem = (size_t)(p.nsg + 1) * p.Rb * sizeof(T) << p.panel.logC;
+    int rc = set_smem(bfly_bw_kernel<T, KW, NSG>, smem);
+    if (rc) return rc;
+    bfly_bw_kernel<T, KW, NSG><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+    g_launches.fetch_add(1);
+    return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+  }
+  int run_bw(const BwParams<float>& p, int KW) {
+    if (KW == 2) return p.nsg <= 3 ? launch_bw<float, 2, 3>(p) : launch_bw<float, 2, 5>(p);
+    return launch_bw<float, 1, 10>(p);
+  }
+  int run_bw(const BwParams<cf>& p, int KW) {
+    if (KW != 1) return BFLY_E_UNSUPPORTED;
+    return p.nsg <= 5 ? launch_bw<cf, 1, 5>(p) : launch_bw<cf, 1, 10>(p);
+  }
+  int zero(void* ptr, size_t bytes) {
+    if (bytes == 0) return BFLY_OK;
+    return cudaMemsetAsync(ptr, 0, bytes, stream) == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+  }
+  int zero2d(void* ptr, size_t pitch, size_t width, size_t rows) {
+    if (width == 0 || rows == 0) return BFLY_OK;
+    return cudaMemset2DAsync(ptr, pitch, 0, width, rows, stream) == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+  }
+};
+
+static int make_exec(void* stream, CudaExec& ex) {
+  ex.stream = static_cast<cudaStream_t>(stream);
+  return device_info(ex.dev);
+}
+
+template <typename T>
+static int fw_entry(bool base4, const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS,
+                    void* out, int B, int S, int log_n, int nblocks, int in_size, int out_size, int inc,
+                    void* stream) {
+  CudaExec ex;
+  int rc = make_exec(stream, ex);
+  if (rc) return rc;
+  Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, base4};
+  return drive_fw<T>(ex, q, static_cast<const T*>(tw2), static_cast<const T*>(tw4), static_cast<const T*>(x),
+                     x_sB, x_sS, static_cast<T*>(out));
+}
+
+template <typename T>
+static int bw_entry(bool base4, const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS,
+                    const void* grad, int64_t g_sB, int64_t g_sS, void* d2, void* d4, void* dx, int B, int S,
+                    int log_n, int nblocks, int in_size, int out_size, int inc, void* ws, size_t ws_bytes,
+                    void* stream) {
+  CudaExec ex;
+  int rc = make_exec(stream, ex);
+  if (rc) return rc;
+  Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, base4};
+  return drive_bw<T>(ex, q, static_cast<const T*>(tw2), static_cast<const T*>(tw4), static_cast<const T*>(x),
+                     x_sB, x_sS, static_cast<const T*>(grad), g_sB, g_sS, static_cast<T*>(d2),
+                     static_cast<T*>(d4), static_cast<T*>(dx), ws, ws_bytes);
+}
+
+template <typename T>
+static int64_t ws_for(const Problem& q0) {
+  // the phase plan depends on the direction of the first block: report the larger need
+  int64_t best = 0;
+  for (int inc = 0; inc < 2; ++inc) {
+    Problem q = q0;
+    q.inc = inc != 0;
+    BwLayout<T> lay;
+    const int rc = plan_bw<T>(q, lay);
+    if (rc) return rc;
+    best = std::max<int64_t>(best, (int64_t)lay.ws_bytes);
+  }
+  return best;
+}
+
+static int64_t ws_entry(bool base4, int dtype, int B, int S, int log_n, int nblocks) {
+  Problem q{B, S, log_n, nblocks, 1, 1, true, base4};
+  int rc = check_problem(q);
+  if (rc) return rc;
+  if (dtype == BFLY_F32) return ws_for<float>(q);
+  if (dtype == BFLY_C64 && !base4) return ws_for<cf>(q);
+  return BFLY_E_UNSUPPORTED;
+}
+
+}  // namespace bfly
+
+using namespace bfly;
+
+extern "C" {
+
+const char* bfly_strerror(int status) {
+  switch (status) {
+    case BFLY_OK: return "success";
+    case BFLY_E_ARG: return "invalid argument (sizes inconsistent or null pointer)";
+    case BFLY_E_UNSUPPORTED: return "shape not supported by the B200 butterfly kernels";
+    case BFLY_E_ALIGN: return "twiddle pointer must be 16-byte aligned";
+    case BFLY_E_WORKSPACE: return "workspace missing, misaligned or too small";
+    case BFLY_E_CUDA: return "CUDA runtime call or kernel launch failed";
+    case BFLY_E_NODEVICE: return "no usable CUDA device";
+    default: return "unknown status";
+  }
+}
+
+int bfly_version(void) { return 100; }
+int bfly_cuda_version(void) { return CUDA_VERSION; }
+int64_t bfly_launch_count(void) { return g_launches.load(); }
+
+int bfly_fw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, int batch,
+                int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                void* stream) {
+  return fw_entry<float>(false, twiddle, nullptr, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks,
+                         input_size, output_size, increasing_stride, stream);
+}
+int bfly_fw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, void* out, int batch,
+                int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                void* stream) {
+  return fw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks, input_size,
+                      output_size, increasing_stride, stream);
+}
+int64_t bfly_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks) {
+  return ws_entry(false, dtype, batch, nstacks, log_n, nblocks);
+}
+int bfly_bw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, const float* grad,
+                int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x, int batch, int nstacks, int log_n,
+                int nblocks, int input_size, int output_size, int increasing_stride, void* workspace,
+                size_t workspace_bytes, void* stream) {
+  return bw_entry<float>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x,
+                         batch, nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
+                         workspace_bytes, stream);
+}
+int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, const void* grad, int64_t g_sB,
+                int64_t g_sS, void* d_twiddle, void* d_x, int batch, int nstacks, int log_n, int nblocks,
+                int input_size, int output_size, int increasing_stride, void* workspace, size_t workspace_bytes,
+                void* stream) {
+  return bw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x, batch,
+                      nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
+                      workspace_bytes, stream);
+}
+int bfly4_fw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB, int64_t x_sS,
+                 float* out, int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                 int increasing_stride, void* stream) {
+  return fw_entry<float>(true, twiddle2, twiddle4, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks,
+                         input_size, output_size, increasing_stride, stream);
+}
+int64_t bfly4_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks) {
+  return ws_entry(true, dtype, batch, nstacks, log_n, nblocks);
+}
+int bfly4_bw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB, int64_t x_sS,
+                 const float* grad, int64_t g_sB, int64_t g_sS, float* d_twiddle4, float* d_twiddle2, float* d_x,
+                 int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                 int increasing_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  return bw_entry<float>(true, twiddle2, twiddle4, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle2, d_twiddle4, d_x,
+                         batch, nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
+                         workspace_bytes, stream);
+}
+
+}  // extern "C"

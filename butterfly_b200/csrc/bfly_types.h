@@ -1,0 +1,210 @@
+// Shared host/device plain-old-data types and arithmetic helpers of the butterfly
+// multiply kernels.  This header compiles as CUDA (nvcc) and as plain C++ (g++),
+// so the tile routines built on it can be executed thread-by-thread on the host
+// by the test-suite's emulator to check their index arithmetic without a GPU.
+#pragma once
+#include <stdint.h>
+#include <math.h>
+
+#include "../../include/bfly.h"  // status codes
+
+#if defined(__CUDACC__)
+#define BFLY_HD __host__ __device__ __forceinline__
+#else
+#define BFLY_HD inline
+#endif
+
+namespace bfly {
+
+// ---------------------------------------------------------------- element types
+
+struct cf {  // complex<float>, re/im interleaved exactly like torch.complex64
+  float re, im;
+};
+
+BFLY_HD float fma_(float a, float b, float c) {
+#if defined(__CUDA_ARCH__)
+  return __fmaf_rn(a, b, c);
+#else
+  return fmaf(a, b, c);
+#endif
+}
+BFLY_HD float mul_(float a, float b) {
+#if defined(__CUDA_ARCH__)
+  return __fmul_rn(a, b);
+#else
+  return a * b;
+#endif
+}
+
+template <typename T> struct Ops;
+
+// Real arithmetic.  One butterfly output is  y = a*x + b*z  evaluated as
+// fma(a, x, rn(b*z)): the product of the partner coefficient is rounded first and
+// the own-coefficient product is fused, which is how the reference's CUDA
+// expression `t_own * x_own + t_partner * x_partner` (csrc/cuda/butterfly_cuda.cu:256)
+// contracts under nvcc's default -fmad=true.
+template <> struct Ops<float> {
+  static BFLY_HD float zero() { return 0.f; }
+  // a*x + b*z
+  static BFLY_HD float madd2(float a, float x, float b, float z) { return fma_(a, x, mul_(b, z)); }
+  // conj(a)*x + conj(b)*z
+  static BFLY_HD float madd2c(float a, float x, float b, float z) { return fma_(a, x, mul_(b, z)); }
+  // acc + g*conj(x)
+  static BFLY_HD float acc_gxc(float acc, float g, float x) { return fma_(g, x, acc); }
+  // acc + a*x
+  static BFLY_HD float fmadd(float acc, float a, float x) { return fma_(a, x, acc); }
+  static BFLY_HD float mul(float a, float x) { return mul_(a, x); }
+  // acc + conj(a)*x
+  static BFLY_HD float fmaddc(float acc, float a, float x) { return fma_(a, x, acc); }
+  static BFLY_HD float mulc(float a, float x) { return mul_(a, x); }
+};
+
+// Complex arithmetic as fused chains (4 FMA-pipe operations per complex multiply-add).
+template <> struct Ops<cf> {
+  static BFLY_HD cf zero() { return cf{0.f, 0.f}; }
+  static BFLY_HD cf mul(cf a, cf x) {
+    cf r;
+    r.re = fma_(a.re, x.re, -mul_(a.im, x.im));
+    r.im = fma_(a.re, x.im, mul_(a.im, x.re));
+    return r;
+  }
+  static BFLY_HD cf fmadd(cf acc, cf a, cf x) {
+    cf r;
+    r.re = fma_(a.re, x.re, fma_(-a.im, x.im, acc.re));
+    r.im = fma_(a.re, x.im, fma_(a.im, x.re, acc.im));
+    return r;
+  }
+  static BFLY_HD cf mulc(cf a, cf x) {  // conj(a)*x
+    cf r;
+    r.re = fma_(a.re, x.re, mul_(a.im, x.im));
+    r.im = fma_(a.re, x.im, -mul_(a.im, x.re));
+    return r;
+  }
+  static BFLY_HD cf fmaddc(cf acc, cf a, cf x) {  // acc + conj(a)*x
+    cf r;
+    r.re = fma_(a.re, x.re, fma_(a.im, x.im, acc.re));
+    r.im = fma_(a.re, x.im, fma_(-a.im, x.re, acc.im));
+    return r;
+  }
+  static BFLY_HD cf madd2(cf a, cf x, cf b, cf z) { return fmadd(mul(b, z), a, x); }
+  static BFLY_HD cf madd2c(cf a, cf x, cf b, cf z) { return fmaddc(mulc(b, z), a, x); }
+  static BFLY_HD cf acc_gxc(cf acc, cf g, cf x) {  // acc + g*conj(x)
+    cf r;
+    r.re = fma_(g.re, x.re, fma_(g.im, x.im, acc.re));
+    r.im = fma_(g.im, x.re, fma_(-g.re, x.im, acc.im));
+    return r;
+  }
+};
+
+// ---------------------------------------------------------------- bit helpers
+
+// Remove bit `pos` from x (bits above move down by one).
+BFLY_HD int delete_bit(int x, int pos) {
+  const int low = (1 << pos) - 1;
+  return ((x >> 1) & ~low) | (x & low);
+}
+// Remove bits pos, pos+1 from x.
+BFLY_HD int delete_2bits(int x, int pos) {
+  const int low = (1 << pos) - 1;
+  return ((x >> 2) & ~low) | (x & low);
+}
+// Insert `nbits` zero bits at position pos.
+BFLY_HD int insert_zeros(int x, int pos, int nbits) {
+  const int low = (1 << pos) - 1;
+  return ((x & ~low) << nbits) | (x & low);
+}
+
+// Shared-memory placement of local column l of a tile row: the low SW bits (the bank
+// index of a 4-byte word for SW=5, of an 8-byte word within a half-warp for SW=4) are
+// XORed with the next SW bits, so that every access pattern "32 lanes differ in 5 chosen
+// bits of l" used by the kernels is free of bank conflicts.
+template <int SW> BFLY_HD int swz(int l) { return l ^ ((l >> SW) & ((1 << SW) - 1)); }
+template <typename T> struct SwBits { static constexpr int value = (sizeof(T) == 4) ? 5 : 4; };
+
+// ---------------------------------------------------------------- descriptors
+
+constexpr int kMaxK = 4;          // widest register window of the forward kernel (2^4 elements/thread)
+constexpr int kMaxFwGroups = 40;  // stage groups one forward launch can carry
+constexpr int kMaxSg = 10;        // sub-groups of one backward phase
+constexpr int kMaxUnitBits = 16;
+
+// Column geometry of a tile ("panel"): 2^logC columns of one batch row, made of
+// 2^(logC-lseg) segments of 2^lseg consecutive columns; segment k of panel pi starts at
+// global column  base(pi) + k << pb .  A full row is the panel lseg = logC = log_n.
+struct Panel {
+  int logC;   // log2 columns in the panel
+  int lseg;   // log2 segment length (local bits [0,lseg) are global bits [0,lseg))
+  int pb;     // global bit that local bit lseg maps to (local bit lseg+j -> global pb+j)
+  int npanels_log;  // log2 number of panels per row
+  BFLY_HD int pw() const { return logC - lseg; }
+  BFLY_HD int base(int pi) const {
+    const int mid = pb - lseg;  // global bits [lseg, pb) come from the low bits of pi
+    return ((pi & ((1 << mid) - 1)) << lseg) | ((pi >> mid) << (pb + pw()));
+  }
+  BFLY_HD int col(int pbase, int l) const {
+    return pbase + (l & ((1 << lseg) - 1)) + ((l >> lseg) << pb);
+  }
+  BFLY_HD int global_bit(int lbit) const { return lbit < lseg ? lbit : lbit - lseg + pb; }
+};
+
+enum FwPattern : int { kR2Inc = 0, kR2Dec = 1, kR4Inc = 2, kR4Dec = 3 };
+
+// One register-window group of the forward kernel: K consecutive radix-2 stages (or K/2
+// radix-4 stages) acting on local bits [lbit, lbit+K).
+struct FwGroup {
+  uint8_t lbit, K, pattern, which;  // which: twiddle tensor (0 radix-2, 1 radix-4)
+  uint8_t nubits;                   // log2(units per tile row) = logC - K
+  uint8_t emit;                     // 1 + snapshot slot to write after this group, 0 = none
+  uint8_t pad_[2];
+  uint32_t tw_off[kMaxK];           // element offset of each stage's twiddle inside one stack
+  uint8_t ubit[kMaxUnitBits];       // local bit position of unit-index bit j
+};
+
+template <typename T> struct FwParams {
+  const T* tw[2];            // radix-2 / radix-4 twiddle tensors
+  int64_t tw_stack[2];       // elements per stack in each
+  const T* x;                // input rows
+  int64_t x_sB, x_sS;        // element strides (x_sS may be 0)
+  int x_cols;                // valid input columns (zero beyond)
+  T* out;                    // output rows, or nullptr when only snapshots are wanted
+  int64_t out_sB, out_sS;
+  int out_cols;              // columns written
+  T* snap[8];                // snapshot buffers, (B,S,n) contiguous
+  int B, S, log_n;
+  int R;                     // rows per tile
+  int vec_in, vec_out;       // 16-byte global accesses allowed
+  Panel panel;
+  int ngroups;
+  FwGroup g[kMaxFwGroups];
+};
+
+// One sub-group of a backward phase.  With a 2-bit window (KW = 2): up to two radix-2
+// stages, or one radix-4 stage, on the 4 elements at local bits [lbit, lbit+2).  With a
+// 1-bit window (KW = 1): one radix-2 stage on the 2 elements at local bit lbit.
+struct BwSg {
+  uint8_t lbit, nst, radix, which;
+  uint8_t q[2];                // bit offset of each stage inside the window
+  uint8_t nubits, pad_;
+  uint32_t tw_off[2];
+  uint8_t ubit[kMaxUnitBits];
+};
+
+template <typename T> struct BwParams {
+  const T* tw[2];
+  T* dtw[2];
+  int64_t tw_stack[2];
+  const T* xin;  int64_t xin_sB, xin_sS;   int xin_cols;   // activation entering the phase
+  const T* gin;  int64_t gin_sB, gin_sS;   int gin_cols;   // gradient leaving the phase (zero beyond)
+  T* gout;       int64_t gout_sB, gout_sS; int gout_cols;  // gradient entering the phase
+  int B, S, log_n;
+  int Rb;            // rows per batch held in shared memory
+  int rows_per_cta;  // rows of one row slice (multiple of Rb)
+  int nslices;
+  int vec_x, vec_g, vec_o;
+  Panel panel;
+  int nsg;
+  BwSg sg[kMaxSg];
+};
+
+}  // namespace bfly

@@ -1,0 +1,276 @@
+// Thin torch operator layer over the C ABI in include/bfly.h.
+//
+// Registers the operators the reference registers in csrc/butterfly.cpp:127-131
+// (torch_butterfly::butterfly_multiply_fw / _bw / butterfly_multiply) with the same
+// argument meaning and the same argument checks (csrc/butterfly.cpp:34-43, 72-83), plus
+// native operators for the base-4 product that the reference only has as PyTorch code
+// (torch_butterfly/multiply_base4.py:7-41) and torch_butterfly::cuda_version
+// (csrc/version.cpp:14-23).  Everything below this file is plain pointers and sizes.
+//
+// CUDA tensors only: there is no CPU implementation behind these operators, and they
+// raise instead of falling back when handed a CPU tensor.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/script.h>
+
+#include <tuple>
+
+#include "../../include/bfly.h"
+
+namespace {
+
+using torch::Tensor;
+
+#define BFLY_CHECK_CUDA(x) \
+  TORCH_CHECK((x).device().is_cuda(), #x " must be a CUDA tensor: the B200 butterfly library has no CPU path")
+#define BFLY_CHECK_SAME_DEVICE(x, y) \
+  TORCH_CHECK((x).device() == (y).device(), #x " and " #y " must be on the same device")
+#define BFLY_CHECK_DIM(x, d) TORCH_CHECK((x).dim() == (d), #x " must have dimension " #d)
+
+void check_status(int rc, const char* what) {
+  TORCH_CHECK(rc == BFLY_OK, what, " failed: ", bfly_strerror(rc), " (status ", rc, ")");
+}
+
+int dtype_code(const Tensor& t, const char* what) {
+  if (t.scalar_type() == at::kFloat) return BFLY_F32;
+  if (t.scalar_type() == at::kComplexFloat) return BFLY_C64;
+  TORCH_CHECK(false, what, " not implemented for '", toString(t.scalar_type()), "'");
+  return -1;
+}
+
+// Borrowed tensors are never mutated; lazily-conjugated or strided views are materialised.
+Tensor dense_twiddle(const Tensor& t) { return t.resolve_conj().contiguous(); }
+Tensor rows_view(const Tensor& t) {
+  Tensor r = t.resolve_conj();
+  if (r.size(2) > 1 && r.stride(2) != 1) r = r.contiguous();
+  if (r.size(2) <= 1 && r.stride(2) != 1) r = r.contiguous();
+  return r;
+}
+
+Tensor butterfly_multiply_fw(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
+                             c10::optional<int64_t> output_size) {
+  BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_SAME_DEVICE(twiddle, input);
+  BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 3);
+  const int64_t batch = input.size(0), nstacks = input.size(1), input_size = input.size(2);
+  const int64_t nblocks = twiddle.size(1), log_n = twiddle.size(2);
+  TORCH_CHECK(log_n >= 1 && log_n <= 24, "butterfly_multiply_fw: n must be a power of 2 (2 <= n <= 2^24)");
+  const int64_t n = (int64_t)1 << log_n;
+  TORCH_CHECK(twiddle.sizes() == torch::IntArrayRef({nstacks, nblocks, log_n, n / 2, 2, 2}),
+              "twiddle must have shape (nstacks, nblocks, log_n, n / 2, 2, 2)");
+  const int64_t out_size = output_size.has_value() ? output_size.value() : n;
+  TORCH_CHECK(out_size <= n, "butterfly_multiply_fw: output_size must be <= n");
+  TORCH_CHECK(out_size >= 0, "butterfly_multiply_fw: output_size must be >= 0");
+  TORCH_CHECK(twiddle.scalar_type() == input.scalar_type(), "twiddle and input must have the same dtype");
+  const int dt = dtype_code(input, "butterfly_multiply_fw_cuda");
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor tw = dense_twiddle(twiddle);
+  const Tensor x = rows_view(input);
+  Tensor output = torch::empty({batch, nstacks, n}, input.options());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  int rc;
+  if (dt == BFLY_F32) {
+    rc = bfly_fw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1),
+                     output.data_ptr<float>(), (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
+                     (int)input_size, (int)out_size, increasing_stride, stream.stream());
+  } else {
+    rc = bfly_fw_c64(tw.data_ptr(), x.data_ptr(), x.stride(0), x.stride(1), output.data_ptr(), (int)batch,
+                     (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
+                     increasing_stride, stream.stream());
+  }
+  check_status(rc, "butterfly_multiply_fw");
+  return out_size < n ? output.slice(2, 0, out_size) : output;
+}
+
+std::tuple<Tensor, Tensor> butterfly_multiply_bw(const Tensor& twiddle, const Tensor& input, const Tensor& grad,
+                                                 bool increasing_stride) {
+  BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_CUDA(grad);
+  BFLY_CHECK_SAME_DEVICE(twiddle, input); BFLY_CHECK_SAME_DEVICE(input, grad);
+  BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 3); BFLY_CHECK_DIM(grad, 3);
+  const int64_t batch = input.size(0), nstacks = input.size(1), input_size = input.size(2);
+  const int64_t nblocks = twiddle.size(1), log_n = twiddle.size(2);
+  TORCH_CHECK(log_n >= 1 && log_n <= 24, "butterfly_multiply_bw: n must be a power of 2 (2 <= n <= 2^24)");
+  const int64_t n = (int64_t)1 << log_n;
+  const int64_t out_size = grad.size(2);
+  TORCH_CHECK(twiddle.sizes() == torch::IntArrayRef({nstacks, nblocks, log_n, n / 2, 2, 2}),
+              "twiddle must have shape (nstacks, nblocks, log_n, n / 2, 2, 2)");
+  TORCH_CHECK(grad.sizes() == torch::IntArrayRef({batch, nstacks, out_size}),
+              "grad must have shape (batch_size, nstacks, output_size)");
+  TORCH_CHECK(out_size <= n, "butterfly_multiply_bw: output_size must be <= n");
+  TORCH_CHECK(twiddle.scalar_type() == input.scalar_type() && grad.scalar_type() == input.scalar_type(),
+              "twiddle, input and grad must have the same dtype");
+  const int dt = dtype_code(input, "butterfly_multiply_bw_cuda");
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor tw = dense_twiddle(twiddle);
+  const Tensor x = rows_view(input);
+  const Tensor g = rows_view(grad);
+  Tensor d_twiddle = torch::empty_like(tw);
+  Tensor d_input = torch::empty({batch, nstacks, std::max(input_size, n)}, input.options());
+  const int64_t ws_bytes = bfly_bw_workspace_bytes(dt, (int)batch, (int)nstacks, (int)log_n, (int)nblocks);
+  TORCH_CHECK(ws_bytes >= 0, "butterfly_multiply_bw failed: ", bfly_strerror((int)ws_bytes));
+  Tensor ws = torch::empty({ws_bytes}, input.options().dtype(at::kByte));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  int rc;
+  if (dt == BFLY_F32) {
+    rc = bfly_bw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1), g.data_ptr<float>(),
+                     g.stride(0), g.stride(1), d_twiddle.data_ptr<float>(), d_input.data_ptr<float>(), (int)batch,
+                     (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size, increasing_stride,
+                     ws_bytes ? ws.data_ptr() : nullptr, (size_t)ws_bytes, stream.stream());
+  } else {
+    rc = bfly_bw_c64(tw.data_ptr(), x.data_ptr(), x.stride(0), x.stride(1), g.data_ptr(), g.stride(0), g.stride(1),
+                     d_twiddle.data_ptr(), d_input.data_ptr(), (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
+                     (int)input_size, (int)out_size, increasing_stride, ws_bytes ? ws.data_ptr() : nullptr,
+                     (size_t)ws_bytes, stream.stream());
+  }
+  check_status(rc, "butterfly_multiply_bw");
+  if (input_size < n) d_input = d_input.slice(2, 0, input_size);
+  return std::make_tuple(d_twiddle, d_input);
+}
+
+using torch::autograd::AutogradContext;
+using torch::autograd::variable_list;
+
+// Same contract as the reference's autograd node (csrc/butterfly.cpp:99-118): saves
+// {twiddle, input} and the direction flag, returns {d_twiddle, d_input, none, none}.
+class ButterflyMultiply : public torch::autograd::Function<ButterflyMultiply> {
+ public:
+  static Tensor forward(AutogradContext* ctx, Tensor twiddle, Tensor input, bool increasing_stride,
+                        c10::optional<int64_t> output_size) {
+    ctx->saved_data["increasing_stride"] = increasing_stride;
+    ctx->save_for_backward({twiddle, input});
+    return butterfly_multiply_fw(twiddle, input, increasing_stride, output_size);
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grad_output) {
+    auto saved = ctx->get_saved_variables();
+    auto result = butterfly_multiply_bw(saved[0], saved[1], grad_output[0],
+                                        ctx->saved_data["increasing_stride"].toBool());
+    return {std::get<0>(result), std::get<1>(result), Tensor(), Tensor()};
+  }
+};
+
+Tensor butterfly_multiply(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
+                          c10::optional<int64_t> output_size) {
+  return ButterflyMultiply::apply(twiddle, input, increasing_stride, output_size);
+}
+
+// ---------------------------------------------------------------- base-4
+
+struct Base4Shape {
+  int64_t batch, nstacks, input_size, nblocks, log_n, n;
+};
+
+Base4Shape base4_shape(const Tensor& twiddle4, const Tensor& twiddle2, const Tensor& input, const char* what) {
+  BFLY_CHECK_CUDA(twiddle4); BFLY_CHECK_CUDA(twiddle2); BFLY_CHECK_CUDA(input);
+  BFLY_CHECK_SAME_DEVICE(twiddle4, input); BFLY_CHECK_SAME_DEVICE(twiddle2, input);
+  BFLY_CHECK_DIM(twiddle4, 6); BFLY_CHECK_DIM(twiddle2, 6); BFLY_CHECK_DIM(input, 3);
+  Base4Shape s;
+  s.batch = input.size(0); s.nstacks = input.size(1); s.input_size = input.size(2);
+  s.nblocks = twiddle4.size(1);
+  s.log_n = twiddle4.size(2) * 2 + twiddle2.size(2);
+  TORCH_CHECK(s.log_n >= 1 && s.log_n <= 24 && twiddle2.size(2) <= 1, what, ": n must be a power of 2");
+  s.n = (int64_t)1 << s.log_n;
+  if (s.log_n / 2 > 0)
+    TORCH_CHECK(twiddle4.sizes() == torch::IntArrayRef({s.nstacks, s.nblocks, s.log_n / 2, s.n / 4, 4, 4}),
+                "twiddle4 must have shape (nstacks, nblocks, log_n / 2, n / 4, 4, 4)");
+  if (s.log_n % 2 == 1)
+    TORCH_CHECK(twiddle2.sizes() == torch::IntArrayRef({s.nstacks, s.nblocks, 1, s.n / 2, 2, 2}),
+                "twiddle2 must have shape (nstacks, nblocks, 1, n / 2, 2, 2)");
+  TORCH_CHECK(input.scalar_type() == at::kFloat && twiddle4.scalar_type() == at::kFloat &&
+                  twiddle2.scalar_type() == at::kFloat,
+              what, " not implemented for '", toString(input.scalar_type()), "' (float32 only)");
+  return s;
+}
+
+Tensor butterfly_multiply_base4_fw(const Tensor& twiddle4, const Tensor& twiddle2, const Tensor& input,
+                                   bool increasing_stride, c10::optional<int64_t> output_size) {
+  const Base4Shape s = base4_shape(twiddle4, twiddle2, input, "butterfly_multiply_base4_fw");
+  const int64_t out_size = output_size.has_value() ? output_size.value() : s.n;
+  TORCH_CHECK(out_size <= s.n && out_size >= 0, "butterfly_multiply_base4_fw: output_size must be <= n");
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor t4 = dense_twiddle(twiddle4), t2 = dense_twiddle(twiddle2);
+  const Tensor x = rows_view(input);
+  Tensor output = torch::empty({s.batch, s.nstacks, s.n}, input.options());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int rc = bfly4_fw_f32(t4.numel() ? t4.data_ptr<float>() : nullptr, t2.numel() ? t2.data_ptr<float>() : nullptr,
+                              x.data_ptr<float>(), x.stride(0), x.stride(1), output.data_ptr<float>(), (int)s.batch,
+                              (int)s.nstacks, (int)s.log_n, (int)s.nblocks, (int)s.input_size, (int)out_size,
+                              increasing_stride, stream.stream());
+  check_status(rc, "butterfly_multiply_base4_fw");
+  return out_size < s.n ? output.slice(2, 0, out_size) : output;
+}
+
+std::tuple<Tensor, Tensor, Tensor> butterfly_multiply_base4_bw(const Tensor& twiddle4, const Tensor& twiddle2,
+                                                               const Tensor& input, const Tensor& grad,
+                                                               bool increasing_stride) {
+  const Base4Shape s = base4_shape(twiddle4, twiddle2, input, "butterfly_multiply_base4_bw");
+  BFLY_CHECK_CUDA(grad); BFLY_CHECK_SAME_DEVICE(input, grad); BFLY_CHECK_DIM(grad, 3);
+  const int64_t out_size = grad.size(2);
+  TORCH_CHECK(grad.sizes() == torch::IntArrayRef({s.batch, s.nstacks, out_size}) && out_size <= s.n,
+              "grad must have shape (batch_size, nstacks, output_size) with output_size <= n");
+  TORCH_CHECK(grad.scalar_type() == at::kFloat, "grad must be float32");
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor t4 = dense_twiddle(twiddle4), t2 = dense_twiddle(twiddle2);
+  const Tensor x = rows_view(input), g = rows_view(grad);
+  Tensor d4 = torch::empty_like(t4), d2 = torch::empty_like(t2);
+  Tensor d_input = torch::empty({s.batch, s.nstacks, std::max(s.input_size, s.n)}, input.options());
+  const int64_t ws_bytes = bfly4_bw_workspace_bytes(BFLY_F32, (int)s.batch, (int)s.nstacks, (int)s.log_n, (int)s.nblocks);
+  TORCH_CHECK(ws_bytes >= 0, "butterfly_multiply_base4_bw failed: ", bfly_strerror((int)ws_bytes));
+  Tensor ws = torch::empty({ws_bytes}, input.options().dtype(at::kByte));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int rc = bfly4_bw_f32(t4.numel() ? t4.data_ptr<float>() : nullptr, t2.numel() ? t2.data_ptr<float>() : nullptr,
+                              x.data_ptr<float>(), x.stride(0), x.stride(1), g.data_ptr<float>(), g.stride(0), g.stride(1),
+                              d4.numel() ? d4.data_ptr<float>() : nullptr, d2.numel() ? d2.data_ptr<float>() : nullptr,
+                              d_input.data_ptr<float>(), (int)s.batch, (int)s.nstacks, (int)s.log_n, (int)s.nblocks,
+                              (int)s.input_size, (int)out_size, increasing_stride, ws_bytes ? ws.data_ptr() : nullptr,
+                              (size_t)ws_bytes, stream.stream());
+  check_status(rc, "butterfly_multiply_base4_bw");
+  if (s.input_size < s.n) d_input = d_input.slice(2, 0, s.input_size);
+  return std::make_tuple(d4, d2, d_input);
+}
+
+class ButterflyMultiplyBase4 : public torch::autograd::Function<ButterflyMultiplyBase4> {
+ public:
+  static Tensor forward(AutogradContext* ctx, Tensor twiddle4, Tensor twiddle2, Tensor input, bool increasing_stride,
+                        c10::optional<int64_t> output_size) {
+    ctx->saved_data["increasing_stride"] = increasing_stride;
+    ctx->save_for_backward({twiddle4, twiddle2, input});
+    return butterfly_multiply_base4_fw(twiddle4, twiddle2, input, increasing_stride, output_size);
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grad_output) {
+    auto saved = ctx->get_saved_variables();
+    auto r = butterfly_multiply_base4_bw(saved[0], saved[1], saved[2], grad_output[0],
+                                         ctx->saved_data["increasing_stride"].toBool());
+    return {std::get<0>(r), std::get<1>(r), std::get<2>(r), Tensor(), Tensor()};
+  }
+};
+
+Tensor butterfly_multiply_base4(const Tensor& twiddle4, const Tensor& twiddle2, const Tensor& input,
+                                bool increasing_stride, c10::optional<int64_t> output_size) {
+  return ButterflyMultiplyBase4::apply(twiddle4, twiddle2, input, increasing_stride, output_size);
+}
+
+// The reference's import-time check (torch_butterfly/__init__.py:13-31) compares this
+// with torch.version.cuda, so report the CUDA runtime torch itself runs on.
+int64_t cuda_version() { return at::detail::getCUDAHooks().versionCUDART(); }
+
+int64_t launch_count() { return bfly_launch_count(); }
+
+}  // namespace
+
+TORCH_LIBRARY(torch_butterfly, m) {
+  m.def("butterfly_multiply_fw(Tensor twiddle, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
+        butterfly_multiply_fw);
+  m.def("butterfly_multiply_bw(Tensor twiddle, Tensor input, Tensor grad, bool increasing_stride) -> (Tensor, Tensor)",
+        butterfly_multiply_bw);
+  m.def("butterfly_multiply(Tensor twiddle, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
+        butterfly_multiply);
+  m.def("butterfly_multiply_base4_fw(Tensor twiddle4, Tensor twiddle2, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
+        butterfly_multiply_base4_fw);
+  m.def("butterfly_multiply_base4_bw(Tensor twiddle4, Tensor twiddle2, Tensor input, Tensor grad, bool increasing_stride) -> (Tensor, Tensor, Tensor)",
+        butterfly_multiply_base4_bw);
+  m.def("butterfly_multiply_base4(Tensor twiddle4, Tensor twiddle2, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
+        butterfly_multiply_base4);
+#ifndef BFLY_SEPARATE_VERSION_LIB
+  m.def("cuda_version() -> int", cuda_version);
+#endif
+  m.def("b200_launch_count() -> int", launch_count);
+}

@@ -1,0 +1,107 @@
+/* bfly.h -- C ABI of the B200 butterfly-multiply library (libbfly_b200.so).
+ *
+ * The library replaces the device side of HazyResearch/butterfly's `torch_butterfly`
+ * operators for CUDA tensors: the forward and backward of the product of
+ * nblocks*log2(n) sparse factors made of 2x2 "twiddle" blocks, and the radix-4
+ * ("base-4") variant.  Every entry point
+ *   - takes plain device pointers and sizes (no torch types),
+ *   - enqueues its kernels on `stream` (a cudaStream_t, NULL = default stream) and
+ *     returns without synchronising,
+ *   - never allocates device memory (scratch is passed in by the caller),
+ *   - returns 0 or a negative BFLY_E_* code (see bfly_strerror); it never throws.
+ * There is no CPU implementation behind these symbols.
+ *
+ * Layouts (all row-major, element type float or interleaved complex64):
+ *   twiddle   (nstacks, nblocks, log_n, n/2, 2, 2)   contiguous, 16-byte aligned
+ *   twiddle4  (nstacks, nblocks, log_n/2, n/4, 4, 4) contiguous, 16-byte aligned
+ *   twiddle2  (nstacks, nblocks, log_n%2, n/2, 2, 2) contiguous, 16-byte aligned
+ *   x         (batch, nstacks, input_size)  last dim contiguous; x_sB / x_sS are the
+ *             element strides of the batch and stack dims (x_sS may be 0: one row
+ *             broadcast to every stack, as Butterfly.pre_process's expand() produces)
+ *   out       (batch, nstacks, n) contiguous; only columns < output_size are written
+ *   grad      (batch, nstacks, output_size), strides g_sB / g_sS, last dim contiguous
+ *   d_x       (batch, nstacks, max(input_size, n)) contiguous; columns < input_size
+ *             hold the input gradient (columns >= n of them are zero)
+ * Input columns >= n are ignored, missing ones (input_size < n) read as zero, exactly as
+ * the reference pads (csrc/cpu/butterfly_cpu.cpp:47-49, csrc/cuda/butterfly_cuda.cu:148-149).
+ */
+#ifndef BFLY_H_
+#define BFLY_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BFLY_OK 0
+#define BFLY_E_ARG (-1)          /* inconsistent sizes or a null pointer */
+#define BFLY_E_UNSUPPORTED (-2)  /* shape outside what the kernels cover */
+#define BFLY_E_ALIGN (-3)        /* twiddle pointer not 16-byte aligned */
+#define BFLY_E_WORKSPACE (-4)    /* workspace missing, misaligned or too small */
+#define BFLY_E_CUDA (-5)         /* a CUDA runtime call or launch failed */
+#define BFLY_E_NODEVICE (-6)     /* no usable CUDA device */
+
+#define BFLY_F32 0
+#define BFLY_C64 1
+
+/* Human-readable text for a status code. */
+const char* bfly_strerror(int status);
+
+/* Library version (major*10000 + minor*100 + patch) and the CUDA toolkit version it was
+ * compiled with (CUDA_VERSION, e.g. 12090).  The latter backs the reference's
+ * `torch_butterfly::cuda_version` operator (csrc/version.cpp:14-23). */
+int bfly_version(void);
+int bfly_cuda_version(void);
+
+/* Forward: out = B_{nblocks-1} ... B_0 x.
+ * Replaces butterfly_multiply_fw_cuda (csrc/cuda/butterfly_cuda.h:6-9,
+ * csrc/cuda/butterfly_cuda.cu:349-416), reached from the operator
+ * torch_butterfly::butterfly_multiply_fw (csrc/butterfly.cpp:20-53). */
+int bfly_fw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out,
+                int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                int increasing_stride, void* stream);
+int bfly_fw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, void* out,
+                int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                int increasing_stride, void* stream);
+
+/* Scratch bytes bfly_bw_* needs for this shape (0 when the whole product is one
+ * backward phase).  dtype is BFLY_F32 or BFLY_C64.  Returns a negative status on error. */
+int64_t bfly_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks);
+
+/* Backward: d_twiddle (same layout as twiddle, overwritten) and d_x from grad.
+ * Replaces butterfly_multiply_bw_cuda (csrc/cuda/butterfly_cuda.h:11-15,
+ * csrc/cuda/butterfly_cuda.cu:534-646), reached from torch_butterfly::butterfly_multiply_bw
+ * (csrc/butterfly.cpp:56-93).  `workspace` (256-byte aligned, workspace_bytes long) takes
+ * the place of the reference's `intermediate_storage` tensor (butterfly_cuda.cu:554-555). */
+int bfly_bw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, const float* grad,
+                int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x, int batch, int nstacks,
+                int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                void* workspace, size_t workspace_bytes, void* stream);
+int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, const void* grad,
+                int64_t g_sB, int64_t g_sS, void* d_twiddle, void* d_x, int batch, int nstacks,
+                int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Base-4 forward / backward (float32).  The reference computes this product with
+ * PyTorch view/permute/sum ops only (torch_butterfly/multiply_base4.py:7-41,
+ * butterfly_multiply_base4_torch); these entry points are its native counterpart.
+ * twiddle2 may be NULL when log_n is even, twiddle4 may be NULL when log_n == 1. */
+int bfly4_fw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB,
+                 int64_t x_sS, float* out, int batch, int nstacks, int log_n, int nblocks,
+                 int input_size, int output_size, int increasing_stride, void* stream);
+int64_t bfly4_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks);
+int bfly4_bw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB,
+                 int64_t x_sS, const float* grad, int64_t g_sB, int64_t g_sS, float* d_twiddle4,
+                 float* d_twiddle2, float* d_x, int batch, int nstacks, int log_n, int nblocks,
+                 int input_size, int output_size, int increasing_stride, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/* Number of kernels the library has launched in this process so far (all entry points). */
+int64_t bfly_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BFLY_H_ */
