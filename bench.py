@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the butterfly multiply (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config cfg2]
+
+A "step" is one forward plus one backward of the operator over one batch of synthetic
+input (configs.py; default cfg2: real fp32, n=4096, two blocks, batch 16384 per GPU).
+With N > 1 (launched by torchrun, one rank per GPU) every rank processes its own batch of
+the same size (weak scaling), nothing crosses GPUs in the forward, and the backward ends
+with one NCCL all-reduce(sum) of the twiddle gradient.
+
+One JSON line is printed by rank 0:
+  value      algorithmic GB/s of fw+bw over all ranks, inputs resident in HBM
+  e2e        the same metric through the public torch operator with HOST buffers: every
+             step copies input and grad from pinned host memory and copies output,
+             input gradient and twiddle gradient back
+  roofline   the dominant kernel's algorithmic bytes per launch / its CUDA-event duration,
+             against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  cpu_baseline  the reference's CPU implementation timed on a bounded sample of the rows
+
+--impl reference times the reference's own CPU path (its compiled CPU operator when
+oracle/_ref holds it, else the C oracle) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------ CPU reference arm
+
+def _cpu_reference_runner():
+    """Returns (kind, fw_bw_callable).  Prefers the reference's own CPU operator."""
+    import oracle
+    if oracle.reference_available(cuda=False) or oracle.reference_available(cuda=True):
+        ops = oracle.load_reference_ops(cuda=not oracle.reference_available(cuda=False))
+
+        def run(tw, x, g, inc):
+            n = 1 << tw.shape[2]
+            y = ops.butterfly_multiply_fw(tw, x, inc, n)
+            d_tw, d_x = ops.butterfly_multiply_bw(tw, x, g, inc)
+            return y, d_tw, d_x
+        return "reference", run
+    oracle.build()
+
+    def run(tw, x, g, inc):
+        y = oracle.multiply_fw(tw, x, inc)
+        d_tw, d_x = oracle.multiply_bw(tw, x, g, inc)
+        return y, d_tw, d_x
+    return "port", run
+
+
+_CPU_INPUTS = {}
+
+
+def cpu_reference_time(cfg_name, rows, cores, reps=1):
+    """Times fw+bw of the reference CPU path on `rows` rows of the workload, split over `cores` threads.
+
+    The reference CPU kernels are single-threaded loops (csrc/cpu/butterfly_cpu.cpp:33-60);
+    rows are independent, so the sample is cut into `cores` row chunks that run concurrently
+    (the operator call releases the GIL) and the twiddle gradients of the chunks are summed.
+    """
+    from concurrent.futures import ThreadPoolExecutor
+    from butterfly_b200 import configs
+    kind, run = _cpu_reference_runner()
+    torch.set_num_threads(1)
+    if (cfg_name, rows) not in _CPU_INPUTS:
+        _CPU_INPUTS[(cfg_name, rows)] = configs.make_inputs(cfg_name, batch=rows)
+    d = _CPU_INPUTS[(cfg_name, rows)]
+    tw, x, g, inc = d["twiddle"], d["input"].contiguous(), d["grad"], d["increasing_stride"]
+    chunks = [c for c in torch.arange(rows).chunk(cores) if c.numel()]
+    pool = ThreadPoolExecutor(max_workers=len(chunks))
+
+    def work(idx):
+        return run(tw, x[idx[0]:idx[-1] + 1], g[idx[0]:idx[-1] + 1], inc)
+    run(tw, x[:2], g[:2], inc)  # warm-up (page in the library)
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        res = list(pool.map(work, chunks))
+        d_tw = res[0][1]
+        for r in res[1:]:
+            d_tw = d_tw + r[1]
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    pool.shutdown()
+    return kind, best, len(chunks)
+
+
+def run_reference_arm(args):
+    from butterfly_b200 import configs
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    rows = args.ref_rows
+    fwb, bwb = configs.algorithmic_bytes(args.config, batch=rows)
+    times = []
+    kind = None
+    for i in range(args.warmup + args.steps):
+        kind, t, used = cpu_reference_time(args.config, rows, cores)
+        if i >= args.warmup:
+            times.append(t)
+    tsum = sum(times)
+    n = configs.CONFIGS[args.config]
+    value = (fwb + bwb) * len(times) / tsum / 1e9
+    line = {
+        "impl": "reference", "metric": "fw+bw butterfly multiply GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * tsum / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if n["dtype"] == torch.float32 else "c64", "data": "synthetic",
+        "config": {"workload": args.config, "n": 1 << n["log_n"], "nblocks": n["nblocks"], "nstacks": n["nstacks"],
+                   "batch_per_step": rows, "note": "bounded sample of the workload's rows per step"},
+        "batch_n_per_s": rows * n["nstacks"] * (1 << n["log_n"]) * len(times) / tsum,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": used, "kind": kind,
+                         "sample": "%d of %d rows per step, fw+bw, %d row chunks on %d threads" % (rows, n["batch"], used, used)},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ GPU arm
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+    import butterfly_b200 as bb
+    from butterfly_b200 import abi, configs
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the GPU arm has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = configs.CONFIGS[args.config]
+    if cfg["base4"] or cfg.get("forward_only"):
+        raise SystemExit("bench.py times fw+bw of a radix-2 config (cfg2, cfg3, cfg5)")
+    d = configs.make_inputs(args.config, batch=args.batch, rank=rank, device=dev)
+    tw, x, g, inc = d["twiddle"], d["input"], d["grad"], d["increasing_stride"]
+    B, S, n = d["batch"], cfg["nstacks"], d["n"]
+    fwb, bwb = configs.algorithmic_bytes(args.config, batch=args.batch)
+    step_bytes = fwb + bwb
+
+    def step():
+        y = bb.butterfly_multiply_fw(tw, x, inc)
+        d_tw, d_x = bb.butterfly_multiply_bw(tw, x, g, inc)
+        if world > 1:
+            dist.all_reduce(d_tw)
+        return y, d_tw, d_x
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    nwarm = args.warmup if args.batch is not None else max(args.warmup, 3)  # small profiling cases may use fewer
+    for _ in range(nwarm):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    launches0 = abi.launch_count()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = abi.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-kernel durations (separate untimed steps, CUDA events around every launch)
+    abi.profile_enable(True)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    prof = abi.profile_collect()
+    abi.profile_enable(False)
+    peak, peak_src = measured_hbm_peak()
+    dom = max(prof, key=lambda k: prof[k][1])
+    dom_launches, dom_ms = prof[dom]
+    sz = 4 if cfg["dtype"] == torch.float32 else 8
+    tw_bytes = tw.numel() * sz
+    plane = B * S * n * sz
+    if dom == "bfly_bw_kernel":
+        # one phase launch reads the phase's input activation and the gradient, writes the
+        # gradient, and reads/accumulates its share of the twiddles
+        per_step = dom_launches // 3
+        alg = 3 * plane + 2 * tw_bytes / max(per_step, 1)
+    else:
+        per_step = dom_launches // 3
+        alg = 2 * plane + tw_bytes
+    avg_ms = dom_ms / max(dom_launches, 1)
+    achieved = alg / (avg_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_src,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launches_per_step": per_step,
+                "avg_launch_ms": avg_ms, "algorithmic_bytes_per_launch": alg,
+                "kernel_ms_per_step": {k: v[1] / 3 for k, v in prof.items()},
+                "op_frac_of_hbm_peak": (step_bytes / (ms_per_step * 1e-3) / 1e9) / peak}
+
+    # ---- end to end through the public operator with host buffers
+    e2e = None
+    if not args.no_e2e:
+        hx = torch.empty(x.shape if not cfg.get("broadcast_stacks") else (B, 1, n), dtype=x.dtype).pin_memory()
+        hx.copy_(x[:, :1] if cfg.get("broadcast_stacks") else x)
+        hg = torch.empty(g.shape, dtype=g.dtype).pin_memory(); hg.copy_(g)
+        hy = torch.empty((B, S, n), dtype=x.dtype).pin_memory()
+        hdx = torch.empty((B, S, n), dtype=x.dtype).pin_memory()
+        hdt = torch.empty(tw.shape, dtype=tw.dtype).pin_memory()
+
+        def e2e_step():
+            xd = hx.to(dev, non_blocking=True)
+            gd = hg.to(dev, non_blocking=True)
+            if cfg.get("broadcast_stacks"):
+                xd = xd.expand(B, S, n)
+            y = bb.butterfly_multiply_fw(tw, xd, inc)
+            d_tw, d_x = bb.butterfly_multiply_bw(tw, xd, gd, inc)
+            if world > 1:
+                dist.all_reduce(d_tw)
+            hy.copy_(y, non_blocking=True)
+            hdx.copy_(d_x, non_blocking=True)
+            hdt.copy_(d_tw, non_blocking=True)
+        h2d = hx.numel() * sz + hg.numel() * sz
+        d2h = (hy.numel() + hdx.numel() + hdt.numel()) * sz
+        e2e_steps = max(1, min(args.steps, 5))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record()
+        barrier()
+        ems = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ems], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ems = float(t.item())
+        e2e = {"value": step_bytes * world / (ems / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ems / e2e_steps,
+               "steps": e2e_steps}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        try:
+            rows = args.ref_rows
+            cores = os.cpu_count() or 1
+            kind, t, used = cpu_reference_time(args.config, rows, cores)
+            rfw, rbw = configs.algorithmic_bytes(args.config, batch=rows)
+            cpu_baseline = {"value": (rfw + rbw) / t / 1e9, "unit": "GB/s", "cores": used, "kind": kind,
+                            "sample": "%d of %d rows, one fw+bw, %d row chunks on %d threads, %.2f s"
+                                      % (rows, B, used, used, t)}
+        except Exception as e:  # the baseline is reported, never needed by the GPU path
+            cpu_baseline = {"value": None, "unit": "GB/s", "cores": 0, "kind": "unavailable", "sample": repr(e)}
+
+    if rank == 0:
+        line = {
+            "metric": "fw+bw butterfly multiply GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": nwarm, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32" if cfg["dtype"] == torch.float32 else "c64", "data": "synthetic",
+            "config": {"workload": args.config, "n": n, "nblocks": cfg["nblocks"], "nstacks": S,
+                       "batch_per_gpu": B, "global_batch": B * world, "parallelism": "batch-sharded x%d" % world,
+                       "l2": "inputs (%.0f MB per step per GPU) exceed the 126 MB L2; no flush" % (step_bytes / 1e6),
+                       "collective": "one NCCL all-reduce(sum) of d_twiddle per step" if world > 1 else "none"},
+            "batch_n_per_s": B * S * n * world / (ms_per_step * 1e-3),
+            "frac_of_hbm_peak": value / world / peak,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg5"])
+    ap.add_argument("--ref-rows", type=int, default=4096, help="rows of the bounded CPU sample")
+    ap.add_argument("--batch", type=int, default=None, help="override the batch per GPU (profiling a small case)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -19,7 +19,7 @@ F32, C64 = 0, 1
 SYMBOLS = (
     "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
-    "bfly4_bw_f32", "bfly_launch_count",
+    "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect",
 )
 
 _lib = None
@@ -168,3 +168,21 @@ def bw_base4(twiddle4, twiddle2, x, grad, increasing_stride=True, workspace=None
 
 def launch_count():
     return int(lib().bfly_launch_count())
+
+
+KERNEL_NAMES = ("bfly_fw_kernel", "bfly_bw_kernel")
+
+
+def profile_enable(on=True):
+    lib().bfly_profile_enable(int(bool(on)))
+
+
+def profile_collect():
+    """{kernel name: (launches, total device ms)} for the launches recorded since the last call."""
+    n = len(KERNEL_NAMES)
+    launches = (ctypes.c_int64 * n)()
+    total = (ctypes.c_double * n)()
+    rc = lib().bfly_profile_collect(launches, total, n)
+    if rc != 0:
+        raise BflyError(rc, "bfly_profile_collect")
+    return {KERNEL_NAMES[i]: (int(launches[i]), float(total[i])) for i in range(n)}

@@ -16,6 +16,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "../../include/bfly.h"
 #include "bfly_core.h"
@@ -92,6 +93,35 @@ __global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_const
 
 static std::atomic<int64_t> g_launches{0};
 
+// Optional per-launch timing (bfly_profile_*): while enabled, every kernel launch is
+// bracketed by a pair of CUDA events on the launching stream.
+enum KernelId : int { kKernFw = 0, kKernBw = 1, kNumKernelIds = 2 };
+struct ProfileRec { int id; cudaEvent_t a, b; };
+static std::mutex g_prof_mu;
+static bool g_prof_on = false;
+static std::vector<ProfileRec> g_prof;
+
+struct ProfileScope {
+  cudaStream_t stream;
+  bool on = false;
+  ProfileRec rec{};
+  ProfileScope(int id, cudaStream_t s) : stream(s) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    if (!g_prof_on) return;
+    if (cudaEventCreate(&rec.a) != cudaSuccess) return;
+    if (cudaEventCreate(&rec.b) != cudaSuccess) { cudaEventDestroy(rec.a); return; }
+    rec.id = id;
+    on = true;
+    cudaEventRecord(rec.a, stream);
+  }
+  ~ProfileScope() {
+    if (!on) return;
+    cudaEventRecord(rec.b, stream);
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof.push_back(rec);
+  }
+};
+
 struct DeviceInfo {
   int sms = 0;
   bool ok = false;
@@ -137,7 +167,10 @@ struct CudaExec {
     if (rc) return rc;
     const int64_t ntiles = fw_num_tiles(p);
     const int grid = (int)std::min<int64_t>(ntiles, dev.sms);
-    bfly_fw_kernel<T><<<grid, kThreads, smem, stream>>>(p);
+    {
+      ProfileScope prof(kKernFw, stream);
+      bfly_fw_kernel<T><<<grid, kThreads, smem, stream>>>(p);
+    }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
   }
@@ -146,7 +179,10 @@ struct CudaExec {
     const size_t smem = (size_t)(p.nsg + 1) * p.Rb * sizeof(T) << p.panel.logC;
     int rc = set_smem(bfly_bw_kernel<T, KW, NSG>, smem);
     if (rc) return rc;
-    bfly_bw_kernel<T, KW, NSG><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+    {
+      ProfileScope prof(kKernBw, stream);
+      bfly_bw_kernel<T, KW, NSG><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+    }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
   }
@@ -245,6 +281,33 @@ const char* bfly_strerror(int status) {
 int bfly_version(void) { return 100; }
 int bfly_cuda_version(void) { return CUDA_VERSION; }
 int64_t bfly_launch_count(void) { return g_launches.load(); }
+
+void bfly_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof_on = on != 0;
+}
+
+int bfly_profile_collect(int64_t* launches, double* total_ms, int n_ids) {
+  std::vector<ProfileRec> recs;
+  {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    recs.swap(g_prof);
+  }
+  for (int i = 0; i < n_ids; ++i) { launches[i] = 0; total_ms[i] = 0.0; }
+  int rc = BFLY_OK;
+  for (auto& r : recs) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(r.b) != cudaSuccess || cudaEventElapsedTime(&ms, r.a, r.b) != cudaSuccess) {
+      rc = BFLY_E_CUDA;
+    } else if (r.id >= 0 && r.id < n_ids) {
+      launches[r.id] += 1;
+      total_ms[r.id] += ms;
+    }
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  return rc;
+}
 
 int bfly_fw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, int batch,
                 int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,

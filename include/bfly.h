@@ -101,6 +101,16 @@ int bfly4_bw_f32(const float* twiddle4, const float* twiddle2, const float* x, i
 /* Number of kernels the library has launched in this process so far (all entry points). */
 int64_t bfly_launch_count(void);
 
+/* Per-kernel timing for benchmarks.  While enabled, every launch is bracketed by a pair of
+ * CUDA events on its stream.  bfly_profile_collect waits for the recorded launches, adds
+ * their count and device time into launches[id] / total_ms[id] (id 0 = forward kernel,
+ * 1 = backward-phase kernel; n_ids entries each) and forgets them.  Leave it disabled in
+ * production: the events serialise nothing but do cost host time. */
+#define BFLY_KERNEL_FW 0
+#define BFLY_KERNEL_BW 1
+void bfly_profile_enable(int on);
+int bfly_profile_collect(int64_t* launches, double* total_ms, int n_ids);
+
 #ifdef __cplusplus
 }
 #endif

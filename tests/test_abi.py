@@ -1,0 +1,90 @@
+"""The C-ABI library loads and exports every symbol include/bfly.h declares; calls that
+need no device behave as documented.  (No compute calls here: those are the GPU tests.)"""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "bfly.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bfly4?_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    from butterfly_b200 import abi
+    lib = abi.lib()
+    names = declared_symbols()
+    assert len(names) >= 12
+    for nm in names:
+        assert hasattr(lib, nm), nm
+    assert set(names) == set(abi.SYMBOLS)
+
+
+def test_status_text_and_versions():
+    from butterfly_b200 import abi
+    assert abi.strerror(0) == "success"
+    for rc in range(-6, 0):
+        assert abi.strerror(rc) and abi.strerror(rc) != "unknown status"
+    assert abi.strerror(-99) == "unknown status"
+    assert abi.lib().bfly_version() >= 100
+    assert abi.lib().bfly_cuda_version() >= 12000
+
+
+def test_workspace_query_and_argument_errors():
+    from butterfly_b200 import abi
+    assert abi.bw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 0
+    # n = 4096, two blocks: 2 snapshots when the first block runs with increasing stride, 3 otherwise;
+    # the query covers both directions
+    assert abi.bw_workspace_bytes(torch.float32, 16384, 1, 12, 2) == 3 * 16384 * 4096 * 4
+    assert abi.bw_workspace_bytes(torch.float32, 4, 1, 0, 1) == -1      # log_n < 1
+    assert abi.bw_workspace_bytes(torch.float32, 4, 0, 5, 1) == -1      # no stacks
+    assert abi.bw_workspace_bytes(torch.complex64, 4, 1, 5, 1, base4=True) == -2  # base-4 is float32 only
+    assert abi.launch_count() >= 0
+
+
+def test_torch_operators_are_registered_and_refuse_cpu_tensors():
+    import butterfly_b200 as bb
+    ops = torch.ops.torch_butterfly
+    for name in ("butterfly_multiply_fw", "butterfly_multiply_bw", "butterfly_multiply", "butterfly_multiply_base4_fw",
+                 "butterfly_multiply_base4_bw", "butterfly_multiply_base4", "cuda_version"):
+        assert hasattr(ops, name)
+    # the reference's import check compares this with torch.version.cuda (torch_butterfly/__init__.py:13-31)
+    v = ops.cuda_version()
+    major, minor = [int(s) for s in torch.version.cuda.split(".")]
+    assert v // 1000 == major and (v % 1000) // 10 == minor
+    tw = torch.randn(1, 1, 3, 4, 2, 2)
+    x = torch.randn(2, 1, 8)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        bb.butterfly_multiply(tw, x, True)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        bb.butterfly_multiply_bw(tw, x, x, True)
+
+
+def test_reference_package_imports_on_top_of_these_libraries(tmp_path):
+    """The reference's unmodified Python package loads `_version` and `_butterfly` from its own
+    directory (torch_butterfly/__init__.py:8-11); link its .py files beside our libraries and
+    import it in a fresh interpreter."""
+    ref = os.environ.get("BFLY_REFERENCE_DIR", "/root/reference")
+    pkg = os.path.join(ref, "torch_butterfly")
+    if not os.path.isdir(pkg):
+        pytest.skip("reference tree not present")
+    import subprocess
+    import sys
+    shim = tmp_path / "torch_butterfly"
+    shim.mkdir()
+    for f in os.listdir(pkg):
+        if f.endswith(".py"):
+            os.symlink(os.path.join(pkg, f), shim / f)
+    for f in ("_butterfly.so", "_version.so"):
+        os.symlink(os.path.join(ROOT, "butterfly_b200", f), shim / f)
+    code = ("import sys; sys.path.insert(0, %r); import torch, torch_butterfly; "
+            "b = torch_butterfly.Butterfly(16, 16); print('imported', torch_butterfly.butterfly_multiply is not None)" % str(tmp_path))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "imported True" in r.stdout

@@ -1,0 +1,140 @@
+"""Host logic without a GPU: the launch planner and the kernels' per-thread tile routines,
+executed thread by thread on the CPU by tests/emul/bfly_emul.cpp behind the same driver
+that plans the GPU launches, compared with the oracle.  This checks panels, unit
+decomposition, twiddle addressing, padding/slicing and the phase plan of the backward; it
+is a test of index arithmetic, not a CPU implementation of the product."""
+import ctypes
+import os
+import subprocess
+
+import pytest
+import torch
+
+from conftest import ROOT, golden_files, load_golden, rel_err
+
+EMUL_SRC = os.path.join(ROOT, "tests", "emul", "bfly_emul.cpp")
+EMUL_LIB = os.path.join(ROOT, "tests", "emul", "libbfly_emul.so")
+CSRC = os.path.join(ROOT, "butterfly_b200", "csrc")
+
+
+@pytest.fixture(scope="module")
+def emul():
+    deps = [EMUL_SRC] + [os.path.join(CSRC, f) for f in ("bfly_core.h", "bfly_types.h", "bfly_plan.h", "bfly_driver.h")]
+    if not os.path.exists(EMUL_LIB) or os.path.getmtime(EMUL_LIB) < max(os.path.getmtime(f) for f in deps):
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-unknown-pragmas", "-I", CSRC,
+                               EMUL_SRC, "-o", EMUL_LIB])
+    return ctypes.CDLL(EMUL_LIB)
+
+
+def P(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None and t.numel() else 0)
+
+
+I64 = ctypes.c_int64
+
+
+def emul_fw(lib, tw2, tw4, x, inc, out_size, log_n, nblocks, base4, threads=64):
+    B, S, insz = x.shape
+    n = 1 << log_n
+    out = torch.full((B, S, n), float("nan"), dtype=x.dtype)
+    rc = lib.bfly_emul_fw(int(x.is_complex()), int(base4), P(tw2), P(tw4), P(x), I64(x.stride(0)), I64(x.stride(1)),
+                          P(out), B, S, log_n, nblocks, insz, out_size, int(inc), threads)
+    assert rc == 0, rc
+    # columns >= out_size must stay untouched
+    assert torch.isnan(out[:, :, out_size:]).all()
+    return out[:, :, :out_size]
+
+
+def emul_bw(lib, tw2, tw4, x, g, inc, log_n, nblocks, base4, threads=64, sms=7):
+    B, S, insz = x.shape
+    n = 1 << log_n
+    d2 = torch.full_like(tw2, float("nan")) if tw2 is not None else None
+    d4 = torch.full_like(tw4, float("nan")) if tw4 is not None else None
+    dx = torch.full((B, S, max(insz, n)), float("nan"), dtype=x.dtype)
+    g = g.contiguous()
+    rc = lib.bfly_emul_bw(int(x.is_complex()), int(base4), P(tw2), P(tw4), P(x), I64(x.stride(0)), I64(x.stride(1)),
+                          P(g), I64(g.stride(0)), I64(g.stride(1)), P(d2), P(d4), P(dx), B, S, log_n, nblocks, insz,
+                          g.shape[2], int(inc), threads, sms)
+    assert rc == 0, rc
+    return d2, d4, dx[:, :, :insz]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
+@pytest.mark.parametrize("log_n", [1, 2, 3, 4, 5, 7, 9, 10, 11, 12])
+def test_radix2_plan_and_indexing(emul, oracle_mod, dtype, log_n):
+    torch.manual_seed(log_n)
+    n = 1 << log_n
+    shapes = [(n, n), (max(1, n // 2 - 1), max(1, n - 5)), (2 * n + 7, max(1, n // 2 - 2))] if log_n <= 7 else [(n, n)]
+    for nb, inc in [(1, True), (1, False), (2, True), (3, False)]:
+        if log_n >= 11 and nb == 3:
+            continue
+        S = 2 if log_n < 8 else 1
+        B = 5 if log_n < 10 else 3
+        for insz, outsz in shapes:
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+            x = torch.randn(B, S, insz, dtype=dtype)
+            g = torch.randn(B, S, outsz, dtype=dtype)
+            thr = 64 if log_n < 10 else 256
+            y = emul_fw(emul, tw, None, x, inc, outsz, log_n, nb, False, thr)
+            assert rel_err(y, oracle_mod.multiply_fw(tw, x, inc, outsz)) < 2e-5
+            d2, _, dx = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, thr)
+            dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+            assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
+
+
+@pytest.mark.parametrize("log_n", [1, 2, 3, 4, 5, 6, 7, 10, 11])
+def test_base4_plan_and_indexing(emul, oracle_mod, log_n):
+    torch.manual_seed(100 + log_n)
+    n = 1 << log_n
+    for nb, inc in [(1, True), (1, False), (2, True), (3, False)]:
+        S, B = 2, 4
+        for insz, outsz in [(n, n), (max(1, n // 2 - 1), max(1, n - 5)), (2 * n + 7, max(1, n // 2 - 2))]:
+            tw4 = torch.randn(S, nb, log_n // 2, n // 4, 4, 4) / 2
+            tw2 = torch.randn(S, nb, log_n % 2, n // 2, 2, 2) / 2 ** 0.5
+            x = torch.randn(B, S, insz)
+            g = torch.randn(B, S, outsz)
+            y = emul_fw(emul, tw2, tw4, x, inc, outsz, log_n, nb, True)
+            assert rel_err(y, oracle_mod.base4_fw(tw4, tw2, x, inc, outsz)) < 2e-5
+            d2, d4, dx = emul_bw(emul, tw2, tw4, x, g, inc, log_n, nb, True)
+            d4r, d2r, dxr = oracle_mod.base4_bw(tw4, tw2, x, g, inc)
+            assert rel_err(dx, dxr) < 2e-5
+            if tw4.numel():
+                assert rel_err(d4, d4r) < 2e-5
+            if tw2.numel():
+                assert rel_err(d2, d2r) < 2e-5
+
+
+def test_stack_broadcast_and_ragged_slices(emul, oracle_mod):
+    torch.manual_seed(7)
+    tw = torch.randn(3, 2, 6, 32, 2, 2) / 2 ** 0.5
+    x = torch.randn(11, 1, 64).expand(11, 3, 64)  # stride 0 over stacks
+    g = torch.randn(11, 3, 64)
+    y = emul_fw(emul, tw, None, x, True, 64, 6, 2, False)
+    assert rel_err(y, oracle_mod.multiply_fw(tw, x, True)) < 2e-5
+    for sms in (1, 3, 7, 64):  # different row-slice splits must give the same sums
+        d2, _, dx = emul_bw(emul, tw, None, x, g, True, 6, 2, False, sms=sms)
+        dtr, dxr = oracle_mod.multiply_bw(tw, x, g, True)
+        assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
+
+
+def test_backward_phase_plan_sizes(emul):
+    ws = ctypes.c_int64(0)
+    # one phase (no scratch) while all stages fit one panel of 1024 columns
+    assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 10, 1, 1, ctypes.byref(ws)) == 1 and ws.value == 0
+    # n = 4096, two blocks: three phases -> two (B,S,n) float snapshots
+    assert emul.bfly_emul_bw_plan(0, 0, 16384, 1, 12, 2, 1, ctypes.byref(ws)) == 3
+    assert ws.value == 2 * 16384 * 4096 * 4
+    # complex: panels of 512 columns
+    nph = emul.bfly_emul_bw_plan(1, 0, 8192, 1, 11, 1, 1, ctypes.byref(ws))
+    assert nph == 2 and ws.value == 8192 * 2048 * 8
+
+
+@pytest.mark.parametrize("path", golden_files("radix2")[::4], ids=lambda p: p.split("/")[-1])
+def test_emulated_kernels_on_golden(emul, path):
+    d = load_golden(path)
+    y = emul_fw(emul, d["twiddle"], None, d["input"], d["increasing_stride"], d["output_size"], d["log_n"],
+                d["nblocks"], False)
+    assert rel_err(y, d["output"]) < 2e-5
+    d2, _, dx = emul_bw(emul, d["twiddle"], None, d["input"], d["grad"], d["increasing_stride"], d["log_n"],
+                        d["nblocks"], False)
+    assert rel_err(d2, d["d_twiddle"]) < 2e-5 and rel_err(dx, d["d_input"]) < 2e-5

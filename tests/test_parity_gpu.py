@@ -1,0 +1,306 @@
+"""Parity of the CUDA path with the CPU oracle, called through the C ABI of
+libbfly_b200.so (butterfly_b200.abi) and through the torch operators.
+
+Tolerance: the product is float32 / complex64 arithmetic; the requirement is agreement
+within rtol 1e-5 / atol 1e-5 per component.  Small cases are checked at a relative error
+(max |a-b| / max |b|) of 2e-5 against the oracle, whose own operation order differs from
+the GPU's (separately rounded products vs fused multiply-adds); large cases use the
+rtol/atol form directly.
+"""
+import pytest
+import torch
+
+from conftest import golden_files, load_golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-5
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch.device("cuda", 0)
+
+
+@pytest.fixture(scope="module")
+def abi():
+    from butterfly_b200 import abi as a
+    return a
+
+
+def within_tol(a, b, rtol=1e-5, atol=1e-5):
+    a = torch.view_as_real(a) if a.is_complex() else a
+    b = torch.view_as_real(b) if b.is_complex() else b
+    return ((a - b).abs() <= atol + rtol * b.abs())
+
+
+def assert_close_1e5(a, b):
+    """rtol 1e-5 / atol 1e-5 per component.  Two valid float32 evaluation orders of the same product
+    (fused vs separately rounded multiply-adds) differ by more than that on a small fraction of
+    components when the outputs are large (un-normalised DFT twiddles: |y| up to ~60); allow 0.2 %
+    of components up to 5x the tolerance, none beyond."""
+    a = torch.view_as_real(a) if a.is_complex() else a
+    b = torch.view_as_real(b) if b.is_complex() else b
+    ratio = (a - b).abs() / (1e-5 + 1e-5 * b.abs())
+    assert (ratio <= 1).float().mean().item() >= 1 - 2e-3, "too many components outside rtol/atol 1e-5"
+    assert ratio.max().item() <= 5.0, "a component is off by %.1fx the tolerance" % ratio.max().item()
+
+
+@pytest.mark.parametrize("path", golden_files("radix2"), ids=lambda p: p.split("/")[-1])
+def test_golden_radix2_through_c_abi(abi, dev, path):
+    d = load_golden(path)
+    tw, x, g = d["twiddle"].to(dev), d["input"].to(dev), d["grad"].to(dev)
+    n = 1 << d["log_n"]
+    before = abi.launch_count()
+    out, _ = abi.fw(tw, x, d["increasing_stride"], d["output_size"])
+    d_tw, d_x, _ = abi.bw(tw, x, g, d["increasing_stride"])
+    torch.cuda.synchronize()
+    assert abi.launch_count() > before  # the CUDA kernels ran
+    assert rel_err(out[:, :, :d["output_size"]], d["output"]) < TOL
+    assert rel_err(d_tw, d["d_twiddle"]) < TOL
+    ref_dx = d["d_input"]
+    assert rel_err(d_x[:, :, :d["input_size"]], ref_dx) < TOL
+    if d["input_size"] > n:
+        assert (d_x[:, :, n:d["input_size"]] == 0).all()
+
+
+@pytest.mark.parametrize("path", [p for p in golden_files("base4") if "_f32_" in p], ids=lambda p: p.split("/")[-1])
+def test_golden_base4_through_c_abi(abi, dev, path):
+    d = load_golden(path)
+    t4, t2, x, g = d["twiddle4"].to(dev), d["twiddle2"].to(dev), d["input"].to(dev), d["grad"].to(dev)
+    out, _ = abi.fw_base4(t4, t2, x, d["increasing_stride"], d["output_size"])
+    d4, d2, d_x, _ = abi.bw_base4(t4, t2, x, g, d["increasing_stride"])
+    assert rel_err(out[:, :, :d["output_size"]], d["output"]) < TOL
+    assert rel_err(d_x[:, :, :d["input_size"]], d["d_input"]) < TOL
+    if t4.numel():
+        assert rel_err(d4, d["d_twiddle4"]) < TOL
+    if t2.numel():
+        assert rel_err(d2, d["d_twiddle2"]) < TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
+@pytest.mark.parametrize("log_n", [1, 2, 3, 4, 6, 8, 9, 10, 11, 12, 13, 14])
+def test_sweep_against_oracle(abi, dev, oracle_mod, dtype, log_n):
+    """Same sweep as the reference's tests/test_multiply.py:19-90 (both stride orders, several blocks and
+    stacks, input padding / output slicing), extended over n = 2 .. 16384 and ragged batches."""
+    torch.manual_seed(log_n)
+    n = 1 << log_n
+    for nb, inc in [(1, True), (2, False), (3, True)]:
+        if log_n >= 13 and nb == 3:
+            continue
+        S = 2
+        B = 37 if log_n <= 10 else 9
+        shapes = [(n, n), (max(1, n // 2 - 1), max(1, n - 5)), (2 * n + 7, max(1, n // 2 - 2))]
+        if log_n >= 13:
+            shapes = shapes[:2]
+        for insz, outsz in shapes:
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+            x = torch.randn(B, S, insz, dtype=dtype)
+            g = torch.randn(B, S, outsz, dtype=dtype)
+            yr = oracle_mod.multiply_fw(tw, x, inc, outsz)
+            dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+            out, _ = abi.fw(tw.to(dev), x.to(dev), inc, outsz)
+            d_tw, d_x, _ = abi.bw(tw.to(dev), x.to(dev), g.to(dev), inc)
+            assert rel_err(out[:, :, :outsz], yr) < TOL, (nb, inc, insz, outsz)
+            assert rel_err(d_tw, dtr) < TOL, (nb, inc, insz, outsz)
+            assert rel_err(d_x[:, :, :insz], dxr) < TOL, (nb, inc, insz, outsz)
+
+
+@pytest.mark.parametrize("log_n", [1, 2, 3, 6, 7, 10, 11, 14])
+def test_base4_sweep_against_oracle(abi, dev, oracle_mod, log_n):
+    torch.manual_seed(50 + log_n)
+    n = 1 << log_n
+    for nb, inc in [(1, True), (2, False), (3, True)]:
+        if log_n >= 14 and nb > 1:
+            continue
+        S, B = (2, 19) if log_n < 14 else (1, 5)
+        for insz, outsz in [(n, n), (max(1, n // 2 - 1), max(1, n - 5))]:
+            tw4 = torch.randn(S, nb, log_n // 2, n // 4, 4, 4) / 2
+            tw2 = torch.randn(S, nb, log_n % 2, n // 2, 2, 2) / 2 ** 0.5
+            x = torch.randn(B, S, insz)
+            g = torch.randn(B, S, outsz)
+            yr = oracle_mod.base4_fw(tw4, tw2, x, inc, outsz)
+            d4r, d2r, dxr = oracle_mod.base4_bw(tw4, tw2, x, g, inc)
+            out, _ = abi.fw_base4(tw4.to(dev), tw2.to(dev), x.to(dev), inc, outsz)
+            d4, d2, d_x, _ = abi.bw_base4(tw4.to(dev), tw2.to(dev), x.to(dev), g.to(dev), inc)
+            assert rel_err(out[:, :, :outsz], yr) < TOL
+            assert rel_err(d_x[:, :, :insz], dxr) < TOL
+            if tw4.numel():
+                assert rel_err(d4, d4r) < TOL
+            if tw2.numel():
+                assert rel_err(d2, d2r) < TOL
+
+
+def test_large_batch_twiddle_gradient(abi, dev, oracle_mod):
+    """Large batch (the reference uses batch 8192 "for race conditions", tests/test_multiply.py:20):
+    d_twiddle sums 8192 terms; compare with the double-precision oracle."""
+    torch.manual_seed(3)
+    B, S, log_n, nb = 8192, 2, 9, 3
+    n = 1 << log_n
+    tw = torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
+    x = torch.randn(B, S, n)
+    g = torch.randn(B, S, n)
+    dtr, dxr = oracle_mod.multiply_bw(tw.double(), x.double(), g.double(), True)
+    d_tw, d_x, _ = abi.bw(tw.to(dev), x.to(dev), g.to(dev), True)
+    d_tw2, d_x2, _ = abi.bw(tw.to(dev), x.to(dev), g.to(dev), True)
+    assert rel_err(d_x.double(), dxr) < TOL
+    assert rel_err(d_tw.double(), dtr) < TOL
+    assert torch.equal(d_x, d_x2)                 # d_input is deterministic
+    assert rel_err(d_tw2, d_tw) < 1e-5            # d_twiddle up to the order of the final atomic adds
+
+
+def test_edge_cases(abi, dev, oracle_mod):
+    torch.manual_seed(4)
+    # empty batch
+    tw = torch.randn(1, 1, 4, 8, 2, 2, device=dev)
+    x = torch.empty(0, 1, 16, device=dev)
+    out, rc = abi.fw(tw, x, True)
+    assert rc == 0 and out.shape == (0, 1, 16)
+    d_tw, d_x, rc = abi.bw(tw, x, torch.empty(0, 1, 16, device=dev), True)
+    assert rc == 0 and (d_tw == 0).all()
+    # stack-broadcast input (stride 0) and batch not a multiple of anything
+    tw = (torch.randn(4, 2, 10, 512, 2, 2) / 2 ** 0.5)
+    xb = torch.randn(77, 1, 1000)
+    g = torch.randn(77, 4, 1024)
+    xe = xb.expand(77, 4, 1000)
+    yr = oracle_mod.multiply_fw(tw, xe, True)
+    dtr, dxr = oracle_mod.multiply_bw(tw, xe, g, True)
+    xd = xb.to(dev).expand(77, 4, 1000)
+    out, _ = abi.fw(tw.to(dev), xd, True)
+    d_tw, d_x, _ = abi.bw(tw.to(dev), xd, g.to(dev), True)
+    assert rel_err(out, yr) < TOL and rel_err(d_tw, dtr) < TOL and rel_err(d_x[:, :, :1000], dxr) < TOL
+    # status codes instead of exceptions or faults
+    _, rc = abi.fw(tw.to(dev), xd, True, output_size=2000, check=False)
+    assert rc == -1
+    ws_small = torch.empty(16, dtype=torch.uint8, device=dev)
+    big = torch.randn(1, 2, 12, 2048, 2, 2, device=dev)
+    xx = torch.randn(4, 1, 4096, device=dev)
+    _, _, rc = abi.bw(big, xx, xx, True, workspace=ws_small, check=False)
+    assert rc == -4
+    misaligned = torch.randn(1 * 1 * 4 * 8 * 4 + 1, device=dev)[1:].view(1, 1, 4, 8, 2, 2)
+    _, rc = abi.fw(misaligned, torch.randn(2, 1, 16, device=dev), True, check=False)
+    assert rc == -3
+
+
+def test_operator_semantics(dev, oracle_mod):
+    """Behaviour of the torch operators that callers rely on (csrc/butterfly.cpp:20-53, 56-93,
+    torch_butterfly/butterfly.py:133-146 of the reference)."""
+    import butterfly_b200 as bb
+    torch.manual_seed(5)
+    S, nb, log_n, B = 2, 2, 6, 10
+    n = 64
+    tw = (torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=torch.complex64) / 2 ** 0.5)
+    x = torch.randn(B, S, n, dtype=torch.complex64)
+    twd, xd = tw.to(dev), x.to(dev)
+    # output_size=None -> n; sliced output keeps shape (B, S, output_size)
+    assert bb.butterfly_multiply(twd, xd, True).shape == (B, S, n)
+    assert bb.butterfly_multiply(twd, xd, True, 17).shape == (B, S, 17)
+    with pytest.raises(RuntimeError, match="output_size must be <= n"):
+        bb.butterfly_multiply(twd, xd, True, n + 1)
+    with pytest.raises(RuntimeError, match="twiddle must have shape"):
+        bb.butterfly_multiply(twd[:1], xd, True)
+    with pytest.raises(RuntimeError, match="not implemented for"):
+        bb.butterfly_multiply(twd.real.double().contiguous(), xd.real.double().contiguous(), True)
+    # lazily conjugated and transposed/flipped twiddle views (what Butterfly.forward passes)
+    y = bb.butterfly_multiply(twd.conj(), xd, True)
+    assert rel_err(y, oracle_mod.multiply_fw(tw.conj(), x, True)) < TOL
+    twt = twd.transpose(-1, -2).flip([1, 2])
+    y = bb.butterfly_multiply(twt, xd, False)
+    assert rel_err(y, oracle_mod.multiply_fw(tw.transpose(-1, -2).flip([1, 2]).contiguous(), x, False)) < TOL
+    # autograd: gradients reach both arguments, d_twiddle is returned with twiddle's shape
+    twp = twd.clone().requires_grad_(True)
+    xp = xd.clone().requires_grad_(True)
+    g = torch.randn(B, S, 40, dtype=torch.complex64)
+    bb.butterfly_multiply(twp, xp, True, 40).backward(g.to(dev))
+    dtr, dxr = oracle_mod.multiply_bw(tw, x, g, True)
+    assert twp.grad.shape == tw.shape and rel_err(twp.grad, dtr) < TOL and rel_err(xp.grad, dxr) < TOL
+    # results do not depend on how many stacks are processed together (ButterflyBmm exactness,
+    # tests/test_butterfly.py:237-266 of the reference)
+    y_all = bb.butterfly_multiply(twd, xd, True)
+    for s in range(S):
+        y_one = bb.butterfly_multiply(twd[s:s + 1].contiguous(), xd[:, s:s + 1].contiguous(), True)
+        assert torch.equal(y_all[:, s:s + 1], y_one)
+
+
+# ------------------------------------------------------------------ the benchmark configurations at full size
+
+def _run_cfg(name, dev, batch=None):
+    import butterfly_b200 as bb
+    from butterfly_b200 import configs
+    d = configs.make_inputs(name, batch=batch, device=dev)
+    if d["base4"]:
+        fw = lambda x: bb.butterfly_multiply_base4_fw(d["twiddle4"], d["twiddle2"], x, d["increasing_stride"])
+        bw = lambda x, g: bb.butterfly_multiply_base4_bw(d["twiddle4"], d["twiddle2"], x, g, d["increasing_stride"])
+    else:
+        fw = lambda x: bb.butterfly_multiply_fw(d["twiddle"], x, d["increasing_stride"])
+        bw = lambda x, g: bb.butterfly_multiply_bw(d["twiddle"], x, g, d["increasing_stride"])
+    return d, fw, bw
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
+def test_benchmark_configs_full_size_properties(dev, oracle_mod, name):
+    """Size-independent properties at the benchmark's full sizes: linearity of the forward, the adjoint
+    identity <B x, g> = <x, B^H g>, additivity of the twiddle gradient over the batch, and agreement with
+    the oracle on the first rows."""
+    d, fw, bw = _run_cfg(name, dev)
+    x = d["input"]
+    B = d["batch"]
+    y = fw(x)
+    # oracle on the first 6 rows
+    k = 6
+    if d["base4"]:
+        yr = oracle_mod.base4_fw(d["twiddle4"], d["twiddle2"], x[:k], d["increasing_stride"])
+    else:
+        yr = oracle_mod.multiply_fw(d["twiddle"], x[:k], d["increasing_stride"])
+    assert_close_1e5(y[:k].cpu(), yr)
+    # linearity: B(2x) = 2 B(x) exactly (scaling by 2 commutes with float rounding)
+    assert torch.equal(fw(2 * x), 2 * y)
+    if d.get("forward_only"):
+        return
+    g = d["grad"]
+    out = bw(x, g)
+    d_x = out[-1]
+    # adjoint identity, accumulated in double
+    hi = torch.complex128 if y.is_complex() else torch.float64
+    lhs = (y.to(hi).conj() * g.to(hi)).sum().item()
+    rhs = (x.to(hi).conj() * d_x.to(hi)).sum().item()
+    norm = (y.to(hi).abs().pow(2).sum().sqrt() * g.to(hi).abs().pow(2).sum().sqrt()).item()
+    assert abs(lhs - rhs) <= 1e-6 * norm
+    # oracle on the first rows for d_input
+    if d["base4"]:
+        _, _, dxr = oracle_mod.base4_bw(d["twiddle4"], d["twiddle2"], x[:k], g[:k], d["increasing_stride"])
+    else:
+        _, dxr = oracle_mod.multiply_bw(d["twiddle"], x[:k], g[:k], d["increasing_stride"])
+    assert_close_1e5(d_x[:k].cpu(), dxr)
+    # additivity of the twiddle gradient over two halves of the batch
+    h = B // 2
+    a = bw(x[:h], g[:h])
+    b = bw(x[h:], g[h:])
+    for full, pa, pb in zip(out[:-1], a[:-1], b[:-1]):
+        if full.numel():
+            scale = full.abs().max().item()
+            assert (full - (pa + pb)).abs().max().item() <= 2e-5 * scale
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg5"])
+def test_against_reference_cuda_extension(dev, oracle_mod, name):
+    """Output and input gradient within rtol 1e-5 / atol 1e-5 of the reference's own CUDA extension
+    (compiled unmodified from the reference tree into oracle/_ref/) on the same seeded inputs."""
+    if not oracle_mod.reference_available(cuda=True):
+        pytest.skip("oracle/_ref/_butterfly_ref_cuda.so not built")
+    try:
+        ref = oracle_mod.load_reference_ops(cuda=True)
+    except RuntimeError as e:
+        pytest.skip(str(e))
+    d, fw, bw = _run_cfg(name, dev)
+    x, g, tw, inc = d["input"], d["grad"], d["twiddle"], d["increasing_stride"]
+    y = fw(x)
+    yr = ref.butterfly_multiply_fw(tw, x, inc, d["n"])
+    assert_close_1e5(y, yr)
+    d_tw, d_x = bw(x, g)
+    dtr, dxr = ref.butterfly_multiply_bw(tw, x, g, inc)
+    assert_close_1e5(d_x, dxr)
+    # both twiddle gradients are float sums of thousands of terms in different orders: compare at the
+    # accuracy such sums have
+    assert rel_err(d_tw, dtr) < 2e-5
