@@ -5,9 +5,73 @@
 // checks the whole index arithmetic (panels, unit decomposition, twiddle addressing,
 // padding and slicing) on a machine without a GPU.
 #pragma once
+#include <type_traits>
+
 #include "bfly_types.h"
 
 namespace bfly {
+
+// Compile-time loop: f(std::integral_constant<int, J>) for J = 0 .. N-1.
+template <int J, int N, typename F>
+BFLY_HD void static_for(F&& f) {
+  if constexpr (J < N) {
+    f(std::integral_constant<int, J>{});
+    static_for<J + 1, N>(f);
+  }
+}
+
+// ------------------------------------------------------------------ shared-memory access
+//
+// Tile addresses are byte addresses in the shared state space (32-bit on the device, so
+// that address arithmetic is one integer add and row offsets fold into the instruction's
+// immediate field); on the host they are plain pointers.
+#if defined(__CUDA_ARCH__)
+typedef uint32_t smaddr_t;
+__device__ __forceinline__ smaddr_t sm_addr(const void* p) { return (smaddr_t)__cvta_generic_to_shared(p); }
+template <int IMM> __device__ __forceinline__ void sm_ld(smaddr_t a, float& v) {
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(IMM) : "memory");
+}
+template <int IMM> __device__ __forceinline__ void sm_ld(smaddr_t a, cf& v) {
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+%3];" : "=f"(v.re), "=f"(v.im) : "r"(a), "n"(IMM) : "memory");
+}
+template <int IMM> __device__ __forceinline__ void sm_st(smaddr_t a, float v) {
+  asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(a), "n"(IMM), "f"(v) : "memory");
+}
+template <int IMM> __device__ __forceinline__ void sm_st(smaddr_t a, cf v) {
+  asm volatile("st.shared.v2.f32 [%0+%1], {%2, %3};" ::"r"(a), "n"(IMM), "f"(v.re), "f"(v.im) : "memory");
+}
+// 16-byte chunk = 4 floats or 2 complex
+template <int IMM> __device__ __forceinline__ void sm_ld16(smaddr_t a, float* v) {
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(a), "n"(IMM) : "memory");
+}
+template <int IMM> __device__ __forceinline__ void sm_ld16(smaddr_t a, cf* v) {
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=f"(v[0].re), "=f"(v[0].im), "=f"(v[1].re), "=f"(v[1].im) : "r"(a), "n"(IMM) : "memory");
+}
+template <int IMM> __device__ __forceinline__ void sm_st16(smaddr_t a, const float* v) {
+  asm volatile("st.shared.v4.f32 [%0+%1], {%2, %3, %4, %5};" ::"r"(a), "n"(IMM), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+}
+template <int IMM> __device__ __forceinline__ void sm_st16(smaddr_t a, const cf* v) {
+  asm volatile("st.shared.v4.f32 [%0+%1], {%2, %3, %4, %5};" ::"r"(a), "n"(IMM), "f"(v[0].re), "f"(v[0].im), "f"(v[1].re), "f"(v[1].im) : "memory");
+}
+#else
+typedef uintptr_t smaddr_t;
+inline smaddr_t sm_addr(const void* p) { return (smaddr_t)p; }
+template <int IMM, typename T> inline void sm_ld(smaddr_t a, T& v) { v = *reinterpret_cast<const T*>(a + IMM); }
+template <int IMM, typename T> inline void sm_st(smaddr_t a, T v) { *reinterpret_cast<T*>(a + IMM) = v; }
+template <int IMM, typename T> inline void sm_ld16(smaddr_t a, T* v) {
+  for (int i = 0; i < (int)(16 / sizeof(T)); ++i) v[i] = reinterpret_cast<const T*>(a + IMM)[i];
+}
+template <int IMM, typename T> inline void sm_st16(smaddr_t a, const T* v) {
+  for (int i = 0; i < (int)(16 / sizeof(T)); ++i) reinterpret_cast<T*>(a + IMM)[i] = v[i];
+}
+#endif
+
+#if defined(__CUDA_ARCH__)
+__device__ __forceinline__ void unpack16(const float4& q, float* v) { v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+__device__ __forceinline__ void unpack16(const float4& q, cf* v) { v[0] = cf{q.x, q.y}; v[1] = cf{q.z, q.w}; }
+#endif
 
 // Scatter the bits of unit index u to the local bit positions listed in ubit.
 BFLY_HD int deposit_unit(int u, const uint8_t* ubit, int nubits) {
@@ -17,112 +81,141 @@ BFLY_HD int deposit_unit(int u, const uint8_t* ubit, int nubits) {
   return l;
 }
 
-template <typename T> struct Vec16 {};  // 16-byte global access
-template <> struct Vec16<float> { static constexpr int N = 4; };
-template <> struct Vec16<cf> { static constexpr int N = 2; };
-
-#if defined(__CUDA_ARCH__)
-__device__ __forceinline__ void unpack16(const float4& q, float* v) { v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
-__device__ __forceinline__ void unpack16(const float4& q, cf* v) { v[0] = cf{q.x, q.y}; v[1] = cf{q.z, q.w}; }
-__device__ __forceinline__ float4 pack16(const float* v) { return make_float4(v[0], v[1], v[2], v[3]); }
-__device__ __forceinline__ float4 pack16(const cf* v) { return make_float4(v[0].re, v[0].im, v[1].re, v[1].im); }
-#endif
-
 // ------------------------------------------------------------------ tile load / store
 
-// Copy rows [row0, row0+R) x panel columns from global memory into the swizzled tile.
-// Columns >= ncols and rows >= B read as zero.
+// Generic copy of rows [row0, row0+R) x panel columns from global memory into the swizzled
+// tile (any panel, any alignment).  Columns >= ncols and rows >= B read as zero.
 template <typename T>
 BFLY_HD void tile_load(const T* __restrict__ src, int64_t sB, int64_t sS, int ncols, int B, int stack,
-                       int row0, int R, const Panel& pn, int pbase, bool vec, T* __restrict__ sm,
-                       int tid, int nthr) {
-  constexpr int SW = SwBits<T>::value;
-  constexpr int V = Vec16<T>::N;
+                       int row0, int R, const Panel& pn, int pbase, T* __restrict__ sm, int tid, int nthr) {
   const int logC = pn.logC;
   const int C = 1 << logC;
-  if (vec && pn.lseg >= 2 && C >= V) {
-    const int per_row = C / V;
-    for (int e = tid; e < R * per_row; e += nthr) {
-      const int r = e / per_row;
-      const int l = (e - r * per_row) * V;
-      const int row = row0 + r;
-      const int col = pn.col(pbase, l);
-      T v[V];
-#pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = Ops<T>::zero();
-      if (row < B) {
-        const T* p = src + (int64_t)row * sB + (int64_t)stack * sS + col;
-        if (col + V <= ncols) {
-#if defined(__CUDA_ARCH__)
-          unpack16(*reinterpret_cast<const float4*>(p), v);
-#else
-          for (int j = 0; j < V; ++j) v[j] = p[j];
-#endif
-        } else {
-#pragma unroll
-          for (int j = 0; j < V; ++j)
-            if (col + j < ncols) v[j] = p[j];
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < V; ++j) sm[r * C + swz<SW>(l + j)] = v[j];
-    }
+  for (int e = tid; e < R * C; e += nthr) {
+    const int r = e >> logC;
+    const int l = e & (C - 1);
+    const int row = row0 + r;
+    const int col = pn.col(pbase, l);
+    T v = Ops<T>::zero();
+    if (row < B && col < ncols) v = src[(int64_t)row * sB + (int64_t)stack * sS + col];
+    sm[r * C + swzT<T>(l)] = v;
+  }
+}
+
+// Generic copy of the tile back to global memory; columns >= ncols and rows >= B are not written.
+template <typename T>
+BFLY_HD void tile_store(T* __restrict__ dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0,
+                        int R, const Panel& pn, int pbase, const T* __restrict__ sm, int tid, int nthr) {
+  const int logC = pn.logC;
+  const int C = 1 << logC;
+  for (int e = tid; e < R * C; e += nthr) {
+    const int r = e >> logC;
+    const int l = e & (C - 1);
+    const int row = row0 + r;
+    const int col = pn.col(pbase, l);
+    if (row < B && col < ncols) dst[(int64_t)row * sB + (int64_t)stack * sS + col] = sm[r * C + swzT<T>(l)];
+  }
+}
+
+// 16-byte-chunk variants for aligned tensors and panels whose segments hold whole chunks.
+// The swizzle moves whole chunks, so a chunk travels with one 16-byte access on both sides.
+// On the device the load is asynchronous (cp.async, zero-filling what lies outside the
+// tensor); tile_load_wait() must be called before the barrier that publishes the tile.
+// Work split of a chunk copy: a thread owns the same chunk columns in every row it touches,
+// so column mapping, range checks and swizzle are computed once per tile.
+struct ChunkSplit {
+  int nslot, c0, r0, rstep;
+};
+BFLY_HD ChunkSplit chunk_split(int lpr, int tid, int nthr) {
+  ChunkSplit s;
+  const int per_row = 1 << lpr;
+  if (per_row >= nthr) {
+    s.nslot = per_row / nthr; s.c0 = tid; s.r0 = 0; s.rstep = 1;
   } else {
-    for (int e = tid; e < R * C; e += nthr) {
-      const int r = e >> logC;
-      const int l = e & (C - 1);
+    s.nslot = 1; s.c0 = tid & (per_row - 1); s.r0 = tid >> lpr; s.rstep = nthr >> lpr;
+  }
+  return s;
+}
+
+template <typename T>
+BFLY_HD void tile_load_chunks(const T* __restrict__ src, int64_t sB, int64_t sS, int ncols, int B, int stack,
+                              int row0, int R, const Panel& pn, int pbase, T* __restrict__ sm, int tid, int nthr) {
+  constexpr int V = Vec16<T>::N;
+  constexpr int VL = Vec16<T>::LOG;
+  const int C = 1 << pn.logC;
+  const T* base = src + (int64_t)stack * sS;
+  const ChunkSplit cs = chunk_split(pn.logC - VL, tid, nthr);
+  for (int s = 0; s < cs.nslot; ++s) {
+    const int l = (cs.c0 + s * nthr) << VL;
+    const int col = pn.col(pbase, l);
+    int vcol = ncols - col;  // elements of this chunk that exist in a row of the tensor
+    vcol = vcol < 0 ? 0 : (vcol > V ? V : vcol);
+    T* d = sm + swzT<T>(l);
+    const T* q0 = base + col;
+    for (int r = cs.r0; r < R; r += cs.rstep) {
       const int row = row0 + r;
-      const int col = pn.col(pbase, l);
-      T v = Ops<T>::zero();
-      if (row < B && col < ncols) v = src[(int64_t)row * sB + (int64_t)stack * sS + col];
-      sm[r * C + swz<SW>(l)] = v;
+      const int valid = row < B ? vcol : 0;
+      const T* q = valid ? q0 + (int64_t)row * sB : base;
+#if defined(__CUDA_ARCH__)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sm_addr(d + r * C)), "l"(q), "r"(valid * (int)sizeof(T)) : "memory");
+#else
+      for (int i = 0; i < V; ++i) d[r * C + i] = i < valid ? q[i] : Ops<T>::zero();
+#endif
+    }
+  }
+}
+BFLY_HD void tile_load_wait() {
+#if defined(__CUDA_ARCH__)
+  asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+#endif
+}
+
+template <typename T>
+BFLY_HD void tile_store_chunks(T* __restrict__ dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0,
+                               int R, const Panel& pn, int pbase, const T* __restrict__ sm, int tid, int nthr) {
+  constexpr int V = Vec16<T>::N;
+  constexpr int VL = Vec16<T>::LOG;
+  const int C = 1 << pn.logC;
+  T* base = dst + (int64_t)stack * sS;
+  const ChunkSplit cs = chunk_split(pn.logC - VL, tid, nthr);
+  const int rend = (B - row0) < R ? (B - row0) : R;  // rows of the tile that exist
+  for (int s = 0; s < cs.nslot; ++s) {
+    const int l = (cs.c0 + s * nthr) << VL;
+    const int col = pn.col(pbase, l);
+    if (col >= ncols) continue;
+    const T* sp = sm + swzT<T>(l);
+    T* q0 = base + col;
+    if (col + V <= ncols) {
+      for (int r = cs.r0; r < rend; r += cs.rstep) {
+        T* q = q0 + (int64_t)(row0 + r) * sB;
+#if defined(__CUDA_ARCH__)
+        *reinterpret_cast<float4*>(q) = *reinterpret_cast<const float4*>(sp + r * C);
+#else
+        for (int i = 0; i < V; ++i) q[i] = sp[r * C + i];
+#endif
+      }
+    } else {
+      for (int r = cs.r0; r < rend; r += cs.rstep)
+        for (int i = 0; i < V; ++i)
+          if (col + i < ncols) q0[(int64_t)(row0 + r) * sB + i] = sp[r * C + i];
     }
   }
 }
 
-// Copy the tile back to global memory; columns >= ncols and rows >= B are not written.
 template <typename T>
-BFLY_HD void tile_store(T* __restrict__ dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0,
-                        int R, const Panel& pn, int pbase, bool vec, const T* __restrict__ sm, int tid,
-                        int nthr) {
-  constexpr int SW = SwBits<T>::value;
-  constexpr int V = Vec16<T>::N;
-  const int logC = pn.logC;
-  const int C = 1 << logC;
-  if (vec && pn.lseg >= 2 && C >= V) {
-    const int per_row = C / V;
-    for (int e = tid; e < R * per_row; e += nthr) {
-      const int r = e / per_row;
-      const int l = (e - r * per_row) * V;
-      const int row = row0 + r;
-      if (row >= B) continue;
-      const int col = pn.col(pbase, l);
-      if (col >= ncols) continue;
-      T v[V];
-#pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = sm[r * C + swz<SW>(l + j)];
-      T* p = dst + (int64_t)row * sB + (int64_t)stack * sS + col;
-      if (col + V <= ncols) {
-#if defined(__CUDA_ARCH__)
-        *reinterpret_cast<float4*>(p) = pack16(v);
-#else
-        for (int j = 0; j < V; ++j) p[j] = v[j];
-#endif
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; ++j)
-          if (col + j < ncols) p[j] = v[j];
-      }
-    }
-  } else {
-    for (int e = tid; e < R * C; e += nthr) {
-      const int r = e >> logC;
-      const int l = e & (C - 1);
-      const int row = row0 + r;
-      const int col = pn.col(pbase, l);
-      if (row < B && col < ncols) dst[(int64_t)row * sB + (int64_t)stack * sS + col] = sm[r * C + swz<SW>(l)];
-    }
-  }
+BFLY_HD void tile_load_auto(const T* src, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0, int R,
+                            const Panel& pn, int pbase, bool vec, T* sm, int tid, int nthr) {
+  if (vec && pn.lseg >= Vec16<T>::LOG)
+    tile_load_chunks<T>(src, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+  else
+    tile_load<T>(src, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+}
+template <typename T>
+BFLY_HD void tile_store_auto(T* dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0, int R,
+                             const Panel& pn, int pbase, bool vec, const T* sm, int tid, int nthr) {
+  if (vec && pn.lseg >= Vec16<T>::LOG)
+    tile_store_chunks<T>(dst, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+  else
+    tile_store<T>(dst, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
 }
 
 // ------------------------------------------------------------------ butterfly stages on a register window
@@ -180,34 +273,66 @@ BFLY_HD void fw_apply_stage(T* v, const T* tw) {
   if constexpr (PAT == kR4Inc) r4_stage_fw<T, K, 2 * S>(v, tw);
   if constexpr (PAT == kR4Dec) r4_stage_fw<T, K, K - 2 - 2 * S>(v, tw);
 }
+template <typename T, int K, int PAT>
+BFLY_HD void fw_apply_all(T* v, const T* tw) {
+  constexpr bool R4 = (PAT >= 2);
+  constexpr int NST = R4 ? K / 2 : K;
+  constexpr int PER = R4 ? (4 << K) : (2 << K);
+  if constexpr (NST > 0) fw_apply_stage<T, K, PAT, 0>(v, tw + 0 * PER);
+  if constexpr (NST > 1) fw_apply_stage<T, K, PAT, 1>(v, tw + 1 * PER);
+  if constexpr (NST > 2) fw_apply_stage<T, K, PAT, 2>(v, tw + 2 * PER);
+  if constexpr (NST > 3) fw_apply_stage<T, K, PAT, 3>(v, tw + 3 * PER);
+}
+
+// Tile position (with window bits zero) of every unit this thread owns in every group,
+// computed once per CTA into shared memory: tab[(g * slots + slot) * nthr + tid].
+template <typename T>
+BFLY_HD void fw_build_table(const FwParams<T>& p, uint16_t* tab, int tid, int nthr) {
+  const int C = 1 << p.panel.logC;
+  if (!p.use_table) return;
+  for (int g = 0; g < p.ngroups; ++g) {
+    const FwGroup& G = p.g[g];
+    const int U = C >> G.K;
+    for (int slot = 0; slot < p.tab_slots; ++slot) {
+      const int u = (U >= nthr) ? tid + slot * nthr : (tid & (U - 1));
+      tab[(g * p.tab_slots + slot) * nthr + tid] = (uint16_t)(u < U ? deposit_unit(u, G.ubit, G.nubits) : 0);
+    }
+  }
+}
 
 // One group of the forward kernel applied in place to the R rows of a tile.
-template <typename T, int K, int PAT>
-BFLY_HD void fw_group(const FwParams<T>& p, const FwGroup& g, T* __restrict__ sm, int R, int stack,
-                      int pbase, int tid, int nthr) {
-  constexpr int SW = SwBits<T>::value;
+//   LOGC > 0 fixes the tile width at compile time (row offsets become immediates).
+//   UNR rows are in flight per thread.
+//   VEC: the window starts at bit 0, so a unit is a run of 16-byte chunks (vector accesses).
+template <typename T, int K, int PAT, int LOGC, int ROWS, int UNR, bool VEC>
+BFLY_HD void fw_group(const FwParams<T>& p, int gi, T* __restrict__ sm, const uint16_t* __restrict__ tab, int R,
+                      int stack, int pbase, int tid, int nthr) {
   constexpr int E = 1 << K;
+  constexpr int V = Vec16<T>::N;
+  constexpr int NA = VEC ? E / V : E;  // shared-memory accesses per unit and row
   constexpr bool R4 = (PAT >= 2);
   constexpr int NST = R4 ? K / 2 : K;
   constexpr int PER = R4 ? E * 4 : E * 2;  // twiddle scalars of one stage for one unit
+  constexpr int SZ = (int)sizeof(T);
+  constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;  // compile-time row pitch in bytes
+  const FwGroup& g = p.g[gi];
   const Panel& pn = p.panel;
-  const int C = 1 << pn.logC;
+  const int C = LOGC > 0 ? (1 << LOGC) : (1 << pn.logC);
   const int U = C >> K;
-  int u0, ustep, r0, rstep;
+  int nslot, r0, rstep;
   if (U >= nthr) {
-    u0 = tid; ustep = nthr; r0 = 0; rstep = 1;
+    nslot = U / nthr; r0 = 0; rstep = 1;
   } else {
-    u0 = tid & (U - 1); ustep = U; r0 = tid / U; rstep = nthr / U;
+    nslot = 1; r0 = tid / U; rstep = nthr / U;
   }
-  const int lbit = g.lbit;
-  const int wg = pn.global_bit(lbit);
+  const int wg = pn.global_bit(g.lbit);
   const T* twbase = p.tw[g.which] + (int64_t)stack * p.tw_stack[g.which];
-  for (int u = u0; u < U; u += ustep) {
-    const int lbase = deposit_unit(u, g.ubit, g.nubits);
+  const smaddr_t sm0 = sm_addr(sm);
+  for (int slot = 0; slot < nslot; ++slot) {
+    const int lbase = p.use_table ? (int)tab[(gi * p.tab_slots + slot) * nthr + tid]
+                                  : deposit_unit(U >= nthr ? tid + slot * nthr : (tid & (U - 1)), g.ubit, g.nubits);
     const int col0 = pn.col(pbase, lbase);
-    int addr[E];
-#pragma unroll
-    for (int m = 0; m < E; ++m) addr[m] = swz<SW>(lbase | (m << lbit));
+    const int a0 = swzT<T>(lbase);
     T tw[NST * PER];
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
@@ -216,53 +341,139 @@ BFLY_HD void fw_group(const FwParams<T>& p, const FwGroup& g, T* __restrict__ sm
         const int ibase = delete_bit(col0, wg + q);
 #pragma unroll
         for (int pp = 0; pp < E / 2; ++pp)
-          load_tw<T, 4>(tw + s * PER + pp * 4, twbase + g.tw_off[s] + (int64_t)(ibase + (pp << wg)) * 4);
+          load_tw<T, 4>(tw + s * PER + pp * 4, twbase + g.tw_off[s] + (uint32_t)(ibase + (pp << wg)) * 4u);
       } else {
         const int q = (PAT == kR4Inc) ? 2 * s : K - 2 - 2 * s;
         const int ibase = delete_2bits(col0, wg + q);
 #pragma unroll
         for (int pp = 0; pp < E / 4; ++pp)
-          load_tw<T, 16>(tw + s * PER + pp * 16, twbase + g.tw_off[s] + (int64_t)(ibase + (pp << wg)) * 16);
+          load_tw<T, 16>(tw + s * PER + pp * 16, twbase + g.tw_off[s] + (uint32_t)(ibase + (pp << wg)) * 16u);
       }
     }
-    for (int r = r0; r < R; r += rstep) {
-      T* row = sm + r * C;
-      T v[E];
+    // byte offsets of the unit's elements (scalar path) or chunks (vector path) inside a tile row
+    int off[NA];
 #pragma unroll
-      for (int m = 0; m < E; ++m) v[m] = row[addr[m]];
-      if constexpr (NST > 0) fw_apply_stage<T, K, PAT, 0>(v, tw + 0 * PER);
-      if constexpr (NST > 1) fw_apply_stage<T, K, PAT, 1>(v, tw + 1 * PER);
-      if constexpr (NST > 2) fw_apply_stage<T, K, PAT, 2>(v, tw + 2 * PER);
-      if constexpr (NST > 3) fw_apply_stage<T, K, PAT, 3>(v, tw + 3 * PER);
+    for (int m = 0; m < NA; ++m) off[m] = (a0 ^ g.d[VEC ? m * V : m]) * SZ;
+    if (rstep == 1 && ROWS > 0 && LOGC > 0) {
+      // the whole tile height is known at compile time: every row offset is an immediate
+      if constexpr (ROWS > 0 && LOGC > 0) {
+        smaddr_t a[NA];
 #pragma unroll
-      for (int m = 0; m < E; ++m) row[addr[m]] = v[m];
+        for (int m = 0; m < NA; ++m) a[m] = sm0 + (smaddr_t)off[m];
+        static_for<0, ROWS / UNR>([&](auto ic) {
+          constexpr int rr = decltype(ic)::value * UNR;
+          T v[UNR][E];
+          static_for<0, UNR>([&](auto jc) {
+            constexpr int j = decltype(jc)::value;
+#pragma unroll
+            for (int m = 0; m < NA; ++m) {
+              if constexpr (VEC) sm_ld16<(rr + j) * ROWB>(a[m], v[j] + m * V);
+              else sm_ld<(rr + j) * ROWB>(a[m], v[j][m]);
+            }
+          });
+          static_for<0, UNR>([&](auto jc) {
+            constexpr int j = decltype(jc)::value;
+            fw_apply_all<T, K, PAT>(v[j], tw);
+#pragma unroll
+            for (int m = 0; m < NA; ++m) {
+              if constexpr (VEC) sm_st16<(rr + j) * ROWB>(a[m], v[j] + m * V);
+              else sm_st<(rr + j) * ROWB>(a[m], v[j][m]);
+            }
+          });
+        });
+      }
+    } else if (rstep == 1) {
+      for (int r = 0; r < R; r += UNR) {
+        const smaddr_t rb = sm0 + (smaddr_t)(r * C * SZ);
+        smaddr_t a[NA];
+#pragma unroll
+        for (int m = 0; m < NA; ++m) a[m] = rb + (smaddr_t)off[m];
+        T v[UNR][E];
+        static_for<0, UNR>([&](auto jc) {
+          constexpr int j = decltype(jc)::value;
+          if (r + j < R) {
+            const smaddr_t ro = LOGC > 0 ? 0 : (smaddr_t)(j * C * SZ);
+#pragma unroll
+            for (int m = 0; m < NA; ++m) {
+              if constexpr (VEC) sm_ld16<j * ROWB>(a[m] + ro, v[j] + m * V);
+              else sm_ld<j * ROWB>(a[m] + ro, v[j][m]);
+            }
+          }
+        });
+        static_for<0, UNR>([&](auto jc) {
+          constexpr int j = decltype(jc)::value;
+          if (r + j < R) {
+            fw_apply_all<T, K, PAT>(v[j], tw);
+            const smaddr_t ro = LOGC > 0 ? 0 : (smaddr_t)(j * C * SZ);
+#pragma unroll
+            for (int m = 0; m < NA; ++m) {
+              if constexpr (VEC) sm_st16<j * ROWB>(a[m] + ro, v[j] + m * V);
+              else sm_st<j * ROWB>(a[m] + ro, v[j][m]);
+            }
+          }
+        });
+      }
+    } else {
+      // fewer units than threads: several rows are processed side by side
+      for (int r = r0; r < R; r += rstep) {
+        const smaddr_t rb = sm0 + (smaddr_t)(r * C * SZ);
+        T v[E];
+#pragma unroll
+        for (int m = 0; m < NA; ++m) {
+          if constexpr (VEC) sm_ld16<0>(rb + (smaddr_t)off[m], v + m * V);
+          else sm_ld<0>(rb + (smaddr_t)off[m], v[m]);
+        }
+        fw_apply_all<T, K, PAT>(v, tw);
+#pragma unroll
+        for (int m = 0; m < NA; ++m) {
+          if constexpr (VEC) sm_st16<0>(rb + (smaddr_t)off[m], v + m * V);
+          else sm_st<0>(rb + (smaddr_t)off[m], v[m]);
+        }
+      }
     }
   }
 }
 
-// Dispatch on the (uniform) window width and pattern of a group.
-template <typename T>
-BFLY_HD void fw_group_dispatch(const FwParams<T>& p, const FwGroup& g, T* sm, int R, int stack, int pbase,
-                               int tid, int nthr) {
-  const int K = g.K, pat = g.pattern;
-  if (K == 1) { fw_group<T, 1, kR2Inc>(p, g, sm, R, stack, pbase, tid, nthr); return; }
+template <typename T, int K, int PAT, int LOGC, int ROWS, int UNR>
+BFLY_HD void fw_group_v(const FwParams<T>& p, int gi, T* sm, const uint16_t* tab, int R, int stack, int pbase,
+                        int tid, int nthr) {
+  if constexpr ((1 << K) >= Vec16<T>::N) {
+    if (p.g[gi].vec) {
+      fw_group<T, K, PAT, LOGC, ROWS, UNR, true>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+      return;
+    }
+  }
+  fw_group<T, K, PAT, LOGC, ROWS, UNR, false>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+}
+
+// Dispatch on the (uniform) window width and pattern of a group.  KMAX is the widest window
+// this kernel instance was compiled for (it sets the register budget of the kernel).
+template <typename T, int KMAX, int LOGC, int ROWS>
+BFLY_HD void fw_group_dispatch(const FwParams<T>& p, int gi, T* sm, const uint16_t* tab, int R, int stack,
+                               int pbase, int tid, int nthr) {
+  const int K = p.g[gi].K, pat = p.g[gi].pattern;
+  constexpr int U2 = 2;
+  constexpr int U3 = (sizeof(T) == 4) ? 2 : 1;
+  if (K == 1) { fw_group_v<T, 1, kR2Inc, LOGC, ROWS, U2>(p, gi, sm, tab, R, stack, pbase, tid, nthr); return; }
   if (K == 2) {
-    if (pat == kR2Inc) fw_group<T, 2, kR2Inc>(p, g, sm, R, stack, pbase, tid, nthr);
-    else if (pat == kR2Dec) fw_group<T, 2, kR2Dec>(p, g, sm, R, stack, pbase, tid, nthr);
-    else fw_group<T, 2, kR4Inc>(p, g, sm, R, stack, pbase, tid, nthr);
+    if (pat == kR2Inc) fw_group_v<T, 2, kR2Inc, LOGC, ROWS, U2>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+    else if (pat == kR2Dec) fw_group_v<T, 2, kR2Dec, LOGC, ROWS, U2>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+    else fw_group_v<T, 2, kR4Inc, LOGC, ROWS, U2>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
     return;
   }
-  if (K == 3) {
-    if (pat == kR2Inc) fw_group<T, 3, kR2Inc>(p, g, sm, R, stack, pbase, tid, nthr);
-    else fw_group<T, 3, kR2Dec>(p, g, sm, R, stack, pbase, tid, nthr);
-    return;
+  if constexpr (KMAX >= 3) {
+    if (K == 3) {
+      if (pat == kR2Inc) fw_group_v<T, 3, kR2Inc, LOGC, ROWS, U3>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+      else fw_group_v<T, 3, kR2Dec, LOGC, ROWS, U3>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+      return;
+    }
   }
-  if constexpr (sizeof(T) == 4) {  // 4-bit windows only for 4-byte elements (register budget)
+  if constexpr (KMAX >= 4 && sizeof(T) == 4) {  // 4-bit windows only for 4-byte elements (register budget)
     if (K == 4) {
-      if (pat == kR2Inc) fw_group<T, 4, kR2Inc>(p, g, sm, R, stack, pbase, tid, nthr);
-      else if (pat == kR2Dec) fw_group<T, 4, kR2Dec>(p, g, sm, R, stack, pbase, tid, nthr);
-      else if (pat == kR4Inc) fw_group<T, 4, kR4Inc>(p, g, sm, R, stack, pbase, tid, nthr);
-      else fw_group<T, 4, kR4Dec>(p, g, sm, R, stack, pbase, tid, nthr);
+      if (pat == kR2Inc) fw_group_v<T, 4, kR2Inc, LOGC, ROWS, 1>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+      else if (pat == kR2Dec) fw_group_v<T, 4, kR2Dec, LOGC, ROWS, 1>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+      else if (pat == kR4Inc) fw_group_v<T, 4, kR4Inc, LOGC, ROWS, 1>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
+      else fw_group_v<T, 4, kR4Dec, LOGC, ROWS, 1>(p, gi, sm, tab, R, stack, pbase, tid, nthr);
     }
   }
 }
@@ -281,17 +492,23 @@ BFLY_HD void fw_tile_coords(const FwParams<T>& p, int64_t tile, int& row0, int& 
 template <typename T> BFLY_HD int64_t fw_num_tiles(const FwParams<T>& p) {
   return (int64_t)((p.B + p.R - 1) / p.R) * p.S * (1 << p.panel.npanels_log);
 }
+// shared memory of one forward CTA: the tile followed by the unit table
+template <typename T> BFLY_HD size_t fw_tile_bytes(const FwParams<T>& p) { return ((size_t)p.R * sizeof(T)) << p.panel.logC; }
+template <typename T> BFLY_HD size_t fw_smem_bytes(const FwParams<T>& p, int nthr) {
+  return fw_tile_bytes(p) + (p.use_table ? (size_t)p.ngroups * p.tab_slots * nthr * sizeof(uint16_t) : 0);
+}
 
 // ------------------------------------------------------------------ backward phase
 
 // Per-thread state of a backward phase: the twiddles of the thread's unit in every
-// sub-group and the matching gradient accumulators.  They live in registers for the
-// whole kernel (all loops over them are fully unrolled with constant indices).
-// KW = window bits: a unit has 2^KW elements; TWN = twiddle scalars per unit and sub-group.
+// sub-group, the matching gradient accumulators, and the unit's tile position.  They live
+// in registers for the whole kernel (all loops over them are fully unrolled with constant
+// indices).  KW = window bits: a unit has 2^KW elements.
 template <int KW> struct BwTwn { static constexpr int value = (KW == 2) ? 16 : 4; };
 template <typename T, int KW, int NSG> struct BwState {
   T tw[NSG][BwTwn<KW>::value];
   T acc[NSG][BwTwn<KW>::value];
+  int a0[NSG];  // swizzled tile index of the unit (window bits zero)
 };
 
 // Radix-2 stage with a runtime bit offset q on a 2^KW-element window.
@@ -365,12 +582,11 @@ template <int KW> BFLY_HD BwThread bw_thread(int logC, int tid, int nthr) {
   return t;
 }
 
-// Visit the twiddle blocks of the thread's unit in sub-group J: calls f(slot, element_offset,
+// Visit the twiddle blocks of the thread's unit in a sub-group: calls f(slot, element_offset,
 // count) for every contiguous run of `count` twiddle scalars, `slot` being the index into
 // the per-thread state array.
 template <typename T, int KW, typename F>
-BFLY_HD void bw_for_each_tw(const BwParams<T>& p, const BwSg& sg, int u, int stack, int pbase, F&& f) {
-  const int lbase = deposit_unit(u, sg.ubit, sg.nubits);
+BFLY_HD void bw_for_each_tw(const BwParams<T>& p, const BwSg& sg, int lbase, int stack, int pbase, F&& f) {
   const int col0 = p.panel.col(pbase, lbase);
   const int wg = p.panel.global_bit(sg.lbit);
   const int64_t sbase = (int64_t)stack * p.tw_stack[sg.which];
@@ -400,11 +616,14 @@ BFLY_HD void bw_load_state(const BwParams<T>& p, BwState<T, KW, NSG>& st, int st
   for (int j = 0; j < NSG; ++j) {
 #pragma unroll
     for (int e = 0; e < BwTwn<KW>::value; ++e) { st.tw[j][e] = Ops<T>::zero(); st.acc[j][e] = Ops<T>::zero(); }
+    st.a0[j] = 0;
     if (j < p.nsg) {
       const BwSg& sg = p.sg[j];
+      const int lbase = deposit_unit(th.u, sg.ubit, sg.nubits);
+      st.a0[j] = swzT<T>(lbase);
       const T* twp = p.tw[sg.which];
       T* dst = st.tw[j];
-      bw_for_each_tw<T, KW>(p, sg, th.u, stack, pbase, [&](int slot, int64_t off, int cnt) {
+      bw_for_each_tw<T, KW>(p, sg, lbase, stack, pbase, [&](int slot, int64_t off, int cnt) {
         if (cnt == 16) load_tw<T, 16>(dst + slot, twp + off);
         else load_tw<T, 4>(dst + slot, twp + off);
       });
@@ -432,9 +651,10 @@ BFLY_HD void bw_flush_state(const BwParams<T>& p, const BwState<T, KW, NSG>& st,
   for (int j = 0; j < NSG; ++j) {
     if (j < p.nsg) {
       const BwSg& sg = p.sg[j];
+      const int lbase = deposit_unit(th.u, sg.ubit, sg.nubits);
       T* dtw = p.dtw[sg.which];
       const T* src = st.acc[j];
-      bw_for_each_tw<T, KW>(p, sg, th.u, stack, pbase, [&](int slot, int64_t off, int cnt) {
+      bw_for_each_tw<T, KW>(p, sg, lbase, stack, pbase, [&](int slot, int64_t off, int cnt) {
 #pragma unroll
         for (int e = 0; e < 16; ++e)
           if (e < cnt) atomic_add_el(dtw + off + e, src[slot + e]);
@@ -443,26 +663,56 @@ BFLY_HD void bw_flush_state(const BwParams<T>& p, const BwState<T, KW, NSG>& st,
   }
 }
 
+// Load / store the thread's unit of one tile row (16-byte accesses when the window starts
+// at bit 0 and the unit is a whole number of chunks).
+template <typename T, int KW>
+BFLY_HD void bw_unit_ld(smaddr_t rowbase, const int* off, bool vec, T* v) {
+  constexpr int E = 1 << KW;
+  constexpr int V = Vec16<T>::N;
+  if constexpr (E >= V) {
+    if (vec) {
+#pragma unroll
+      for (int h = 0; h < E / V; ++h) sm_ld16<0>(rowbase + (smaddr_t)off[h * V], v + h * V);
+      return;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < E; ++m) sm_ld<0>(rowbase + (smaddr_t)off[m], v[m]);
+}
+template <typename T, int KW>
+BFLY_HD void bw_unit_st(smaddr_t rowbase, const int* off, bool vec, const T* v) {
+  constexpr int E = 1 << KW;
+  constexpr int V = Vec16<T>::N;
+  if constexpr (E >= V) {
+    if (vec) {
+#pragma unroll
+      for (int h = 0; h < E / V; ++h) sm_st16<0>(rowbase + (smaddr_t)off[h * V], v + h * V);
+      return;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < E; ++m) sm_st<0>(rowbase + (smaddr_t)off[m], v[m]);
+}
+
 // Forward recompute of sub-group j: reads the thread's unit of every row from snapshot j,
 // applies the sub-group's stages, writes snapshot j+1.
 template <typename T, int KW, int NSG>
 BFLY_HD void bw_sg_forward(const BwParams<T>& p, const BwState<T, KW, NSG>& st, int j, T* __restrict__ smX,
                            int R, int tid, int nthr) {
-  constexpr int SW = SwBits<T>::value;
   constexpr int E = 1 << KW;
+  constexpr int SZ = (int)sizeof(T);
   const BwSg& sg = p.sg[j];
   const int C = 1 << p.panel.logC;
   const BwThread th = bw_thread<KW>(p.panel.logC, tid, nthr);
-  const int lbase = deposit_unit(th.u, sg.ubit, sg.nubits);
-  int addr[E];
+  int off[E];
 #pragma unroll
-  for (int m = 0; m < E; ++m) addr[m] = swz<SW>(lbase | (m << sg.lbit));
-  const T* src = smX + (size_t)j * p.Rb * C;
-  T* dst = smX + (size_t)(j + 1) * p.Rb * C;
+  for (int m = 0; m < E; ++m) off[m] = (st.a0[j] ^ sg.d[m]) * SZ;
+  const smaddr_t src = sm_addr(smX + (size_t)j * p.Rb * C);
+  const smaddr_t dst = sm_addr(smX + (size_t)(j + 1) * p.Rb * C);
+  const bool vec = sg.vec != 0;
   for (int r = th.r0; r < R; r += th.rstep) {
     T v[E];
-#pragma unroll
-    for (int m = 0; m < E; ++m) v[m] = src[r * C + addr[m]];
+    bw_unit_ld<T, KW>(src + (smaddr_t)(r * C * SZ), off, vec, v);
     if constexpr (KW == 2) {
       if (sg.radix == 4) {
         r4_stage_fw<T, 2, 0>(v, st.tw[j]);
@@ -473,8 +723,7 @@ BFLY_HD void bw_sg_forward(const BwParams<T>& p, const BwState<T, KW, NSG>& st, 
     } else {
       r2_fw_rt<T, 1>(v, st.tw[j], 0);
     }
-#pragma unroll
-    for (int m = 0; m < E; ++m) dst[r * C + addr[m]] = v[m];
+    bw_unit_st<T, KW>(dst + (smaddr_t)(r * C * SZ), off, vec, v);
   }
 }
 
@@ -483,20 +732,21 @@ BFLY_HD void bw_sg_forward(const BwParams<T>& p, const BwState<T, KW, NSG>& st, 
 template <typename T, int KW, int NSG>
 BFLY_HD void bw_sg_backward(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, const T* __restrict__ smX,
                             T* __restrict__ smG, int R, int tid, int nthr) {
-  constexpr int SW = SwBits<T>::value;
   constexpr int E = 1 << KW;
+  constexpr int SZ = (int)sizeof(T);
   const BwSg& sg = p.sg[j];
   const int C = 1 << p.panel.logC;
   const BwThread th = bw_thread<KW>(p.panel.logC, tid, nthr);
-  const int lbase = deposit_unit(th.u, sg.ubit, sg.nubits);
-  int addr[E];
+  int off[E];
 #pragma unroll
-  for (int m = 0; m < E; ++m) addr[m] = swz<SW>(lbase | (m << sg.lbit));
-  const T* src = smX + (size_t)j * p.Rb * C;
+  for (int m = 0; m < E; ++m) off[m] = (st.a0[j] ^ sg.d[m]) * SZ;
+  const smaddr_t src = sm_addr(smX + (size_t)j * p.Rb * C);
+  const smaddr_t gb = sm_addr(smG);
+  const bool vec = sg.vec != 0;
   for (int r = th.r0; r < R; r += th.rstep) {
     T x[E], g[E];
-#pragma unroll
-    for (int m = 0; m < E; ++m) { x[m] = src[r * C + addr[m]]; g[m] = smG[r * C + addr[m]]; }
+    bw_unit_ld<T, KW>(src + (smaddr_t)(r * C * SZ), off, vec, x);
+    bw_unit_ld<T, KW>(gb + (smaddr_t)(r * C * SZ), off, vec, g);
     if constexpr (KW == 2) {
       if (sg.radix == 4) {
         r4_bw4<T>(g, x, st.tw[j], st.acc[j]);
@@ -513,8 +763,7 @@ BFLY_HD void bw_sg_backward(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j
     } else {
       r2_bw_rt<T, 1>(g, x, st.tw[j], st.acc[j], 0);
     }
-#pragma unroll
-    for (int m = 0; m < E; ++m) smG[r * C + addr[m]] = g[m];
+    bw_unit_st<T, KW>(gb + (smaddr_t)(r * C * SZ), off, vec, g);
   }
 }
 
@@ -534,11 +783,5 @@ BFLY_HD void bw_cta_coords(const BwParams<T>& p, int cta, int& pbase, int& stack
 template <typename T> BFLY_HD int bw_num_ctas(const BwParams<T>& p) {
   return (1 << p.panel.npanels_log) * p.S * p.nslices;
 }
-
-// The whole per-CTA body of a backward phase between barriers is:
-//   load state; for each row batch { load X0,G | sync | sg fwd 0..nsg-2 (sync each) |
-//   sg bwd nsg-1..0 (sync each) | store G | sync }; flush state.
-// `Sync` is __syncthreads() on the device; the host emulator runs each step for all
-// threads before the next.
 
 }  // namespace bfly

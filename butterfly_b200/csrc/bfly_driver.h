@@ -3,28 +3,51 @@
 //
 // Executor concept (E):
 //   int  num_sms() const;
+//   int  threads() const;                                  // threads per CTA of its kernels
 //   int  run_fw(const FwParams<T>&);                       // one forward launch
 //   int  run_bw(const BwParams<T>&, int KW);               // one backward-phase launch
 //   int  zero(void* ptr, size_t bytes);                    // async memset
 //   int  zero2d(void* ptr, size_t pitch_bytes, size_t width_bytes, size_t rows);
 #pragma once
+#include <cstdlib>
+
 #include "bfly_plan.h"
 
 namespace bfly {
 
 template <typename T> struct KernelCfg;
 template <> struct KernelCfg<float> {
-  static constexpr int kFwKmax = 4;
+  static constexpr int kFwKmaxTwoCtas = 3;  // widest window that still fits two CTAs per SM
+  static constexpr int kFwKmaxOneCta = 4;   // widest window at one CTA per SM
   static constexpr int kThreads = 256;
   static int bw_kw(int log_n) { return log_n >= 2 ? 2 : 1; }
   static int bw_max_sg(int kw) { return kw == 2 ? 5 : 10; }
 };
 template <> struct KernelCfg<cf> {
-  static constexpr int kFwKmax = 3;
+  static constexpr int kFwKmaxTwoCtas = 2;
+  static constexpr int kFwKmaxOneCta = 3;
   static constexpr int kThreads = 256;
   static int bw_kw(int) { return 1; }
   static int bw_max_sg(int) { return 10; }
 };
+
+// Launch shape of the forward kernel.  The defaults (two CTAs per SM, windows of up to 3 bits
+// for float / 2 for complex) can be overridden for experiments with the environment variables
+// BFLY_FW_KMAX (window bits) and BFLY_FW_ROWS (rows per tile).
+struct FwTuning { int kmax, ctas_per_sm, max_rows; };
+template <typename T> inline FwTuning fw_tuning() {
+  FwTuning t{KernelCfg<T>::kFwKmaxTwoCtas, 2, 16};
+  if (const char* e = std::getenv("BFLY_FW_KMAX")) {
+    const int k = std::atoi(e);
+    if (k >= 1 && k <= KernelCfg<T>::kFwKmaxOneCta) t.kmax = k;
+  }
+  if (t.kmax > KernelCfg<T>::kFwKmaxTwoCtas) t.ctas_per_sm = 1;
+  if (const char* e = std::getenv("BFLY_FW_ROWS")) {
+    const int r = std::atoi(e);
+    if (r >= 1 && r <= 64) t.max_rows = r;
+  }
+  return t;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 template <typename T> inline bool vec_ok(const void* p, int64_t sB, int64_t sS) {
@@ -68,7 +91,8 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
   if (((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;
   const Panel pn = full_row_panel(q.log_n);
   std::vector<FwGroup> groups;
-  if (!plan_fw_groups(st, t0, t1, cuts, pn, SwBits<T>::value, KernelCfg<T>::kFwKmax, groups))
+  const FwTuning tune = fw_tuning<T>();
+  if (!plan_fw_groups(st, t0, t1, cuts, pn, Vec16<T>::LOG, tune.kmax, groups))
     return BFLY_E_UNSUPPORTED;
   int64_t stk[2];
   twiddle_stack_sizes(q, stk);
@@ -91,12 +115,26 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
     p.out_cols = last ? out_cols : (int)n;
     for (int i = 0; i < kMaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
     p.B = q.B; p.S = q.S; p.log_n = q.log_n;
-    p.R = fw_rows_per_tile<T>(q.log_n, q.B);
+    p.R = fw_rows_per_tile<T>(q.log_n, q.B, tune.ctas_per_sm, tune.max_rows);
     p.vec_in = vec_ok<T>(p.x, p.x_sB, p.x_sS);
     p.vec_out = out ? vec_ok<T>(out, out_sB, out_sS) : 1;
     p.panel = pn;
     p.ngroups = (int)(g1 - g0);
-    for (size_t g = g0; g < g1; ++g) p.g[g - g0] = groups[g];
+    p.tab_slots = 1;
+    for (size_t g = g0; g < g1; ++g) {
+      p.g[g - g0] = groups[g];
+      const int U = (1 << pn.logC) >> groups[g].K;
+      p.tab_slots = std::max(p.tab_slots, U / ex.threads());
+    }
+    // the unit table follows the tile in shared memory when it is small; give it room
+    {
+      const size_t budget = tune.ctas_per_sm <= 1 ? (size_t)kSmemMax : (size_t)(228 * 1024) / tune.ctas_per_sm - 1024;
+      const size_t tab = (size_t)p.ngroups * p.tab_slots * ex.threads() * sizeof(uint16_t);
+      const size_t row_bytes = sizeof(T) << pn.logC;
+      p.use_table = tab <= 16 * 1024 && row_bytes + tab <= budget;
+      if (p.use_table)
+        while (p.R > 1 && (size_t)p.R * row_bytes + tab > budget) --p.R;
+    }
     const int rc = ex.run_fw(p);
     if (rc != BFLY_OK) return rc;
     g0 = g1;
@@ -131,7 +169,7 @@ int plan_bw(const Problem& q, BwLayout<T>& lay) {
   lay.kw = KernelCfg<T>::bw_kw(q.log_n);
   int logCmax = 0;
   while ((1 << logCmax) < (KernelCfg<T>::kThreads << lay.kw)) ++logCmax;
-  lay.phases = plan_bw_phases(st, q.log_n, logCmax, lay.kw, KernelCfg<T>::bw_max_sg(lay.kw), SwBits<T>::value);
+  lay.phases = plan_bw_phases(st, q.log_n, logCmax, lay.kw, KernelCfg<T>::bw_max_sg(lay.kw), Vec16<T>::LOG);
   if (lay.phases.empty()) return BFLY_E_UNSUPPORTED;
   if ((int)lay.phases.size() - 1 > kMaxSnap) return BFLY_E_UNSUPPORTED;
   if (lay.phases.size() > 1 && ((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;

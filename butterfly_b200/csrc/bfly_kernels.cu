@@ -26,28 +26,39 @@ namespace bfly {
 
 constexpr int kThreads = 256;
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) bfly_fw_kernel(const __grid_constant__ FwParams<T> p) {
+// KMAX: widest register window compiled in (it sets the register budget: windows of up to 3
+// bits fit 128 registers and two CTAs per SM, 4-bit windows need one CTA per SM).
+// LOGC: compile-time log2 of the tile width, 0 = read from the parameters.
+template <typename T, int KMAX> struct FwOcc {
+  static constexpr int kMinBlocks = (sizeof(T) == 4 ? (KMAX <= 3 ? 2 : 1) : (KMAX <= 2 ? 2 : 1));
+};
+
+template <typename T, int KMAX, int LOGC, int ROWS>
+__global__ void __launch_bounds__(kThreads, (FwOcc<T, KMAX>::kMinBlocks))
+bfly_fw_kernel(const __grid_constant__ FwParams<T> p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* sm = reinterpret_cast<T*>(smem_raw);
+  uint16_t* tab = reinterpret_cast<uint16_t*>(smem_raw + fw_tile_bytes(p));
   const int tid = threadIdx.x;
   const int64_t ntiles = fw_num_tiles(p);
   const int64_t n = (int64_t)1 << p.log_n;
+  fw_build_table<T>(p, tab, tid, kThreads);  // read only by the thread that wrote it
   for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     int row0, stack, pbase;
     fw_tile_coords(p, tile, row0, stack, pbase);
-    tile_load<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
+    tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
+    tile_load_wait();
     __syncthreads();
     for (int g = 0; g < p.ngroups; ++g) {
-      fw_group_dispatch<T>(p, p.g[g], sm, p.R, stack, pbase, tid, kThreads);
+      fw_group_dispatch<T, KMAX, LOGC, ROWS>(p, g, sm, tab, p.R, stack, pbase, tid, kThreads);
       __syncthreads();
       if (p.g[g].emit) {
-        tile_store<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm, tid, kThreads);
+        tile_store_auto<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm, tid, kThreads);
         __syncthreads();
       }
     }
     if (p.out) {
-      tile_store<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm, tid, kThreads);
+      tile_store_auto<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm, tid, kThreads);
       __syncthreads();
     }
   }
@@ -66,8 +77,9 @@ __global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_const
   bw_load_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
   for (int row0 = row_begin; row0 < row_end; row0 += p.Rb) {
     const int R = p.Rb;
-    tile_load<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
-    tile_load<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
+    tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
+    tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
+    tile_load_wait();
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < NSG - 1; ++j) {
@@ -83,7 +95,7 @@ __global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_const
         __syncthreads();
       }
     }
-    tile_store<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
+    tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
     __syncthreads();
   }
   bw_flush_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
@@ -153,6 +165,11 @@ static int set_smem(K kernel, size_t bytes) {
       return BFLY_E_CUDA;
     }
   }
+  // ask for the largest shared-memory carve-out so that two CTAs of up to 113 KB share an SM
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+    cudaGetLastError();
+    return BFLY_E_CUDA;
+  }
   return BFLY_OK;
 }
 
@@ -160,19 +177,36 @@ struct CudaExec {
   cudaStream_t stream;
   DeviceInfo dev;
   int num_sms() const { return dev.sms; }
+  int threads() const { return kThreads; }
 
-  template <typename T> int run_fw(const FwParams<T>& p) {
-    const size_t smem = (size_t)p.R * sizeof(T) << p.panel.logC;
-    int rc = set_smem(bfly_fw_kernel<T>, smem);
+  template <typename T, int KMAX, int LOGC, int ROWS> int launch_fw(const FwParams<T>& p) {
+    const size_t smem = fw_smem_bytes(p, kThreads);
+    int rc = set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS>, smem);
     if (rc) return rc;
     const int64_t ntiles = fw_num_tiles(p);
-    const int grid = (int)std::min<int64_t>(ntiles, dev.sms);
+    const int grid = (int)std::min<int64_t>(ntiles, (int64_t)dev.sms * FwOcc<T, KMAX>::kMinBlocks);
     {
       ProfileScope prof(kKernFw, stream);
-      bfly_fw_kernel<T><<<grid, kThreads, smem, stream>>>(p);
+      bfly_fw_kernel<T, KMAX, LOGC, ROWS><<<grid, kThreads, smem, stream>>>(p);
     }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+  }
+  // Instances with the tile shape fixed at compile time exist for the shapes the row planner
+  // picks for n = 4096 and n = 1024 float rows at two CTAs per SM; everything else runs the
+  // generic instance.
+  template <typename T, int KMAX> int launch_fw_shape(const FwParams<T>& p) {
+    if constexpr (sizeof(T) == 4 && KMAX == KernelCfg<T>::kFwKmaxTwoCtas) {
+      if (p.panel.logC == 12 && p.R == 6) return launch_fw<T, KMAX, 12, 6>(p);
+      if (p.panel.logC == 10 && p.R == 16) return launch_fw<T, KMAX, 10, 16>(p);
+    }
+    return launch_fw<T, KMAX, 0, 0>(p);
+  }
+  template <typename T> int run_fw(const FwParams<T>& p) {
+    int kmax = 1;
+    for (int g = 0; g < p.ngroups; ++g) kmax = std::max<int>(kmax, p.g[g].K);
+    if (kmax <= KernelCfg<T>::kFwKmaxTwoCtas) return launch_fw_shape<T, KernelCfg<T>::kFwKmaxTwoCtas>(p);
+    return launch_fw_shape<T, KernelCfg<T>::kFwKmaxOneCta>(p);
   }
 
   template <typename T, int KW, int NSG> int launch_bw(const BwParams<T>& p) {

@@ -49,18 +49,24 @@ inline std::vector<Stage> make_stages_r4(int log_n, int nblocks, bool inc) {
   return st;
 }
 
-// Order the non-window local bits of a tile so that the first five (the lane bits of a
-// warp) hit 32 different shared-memory banks under swz<SW>: a bank bit p that lies
-// inside the window is replaced by bit p+SW, which the swizzle folds onto p.
-inline int choose_unit_bits(int logC, int lbit, int K, int SW, uint8_t* ubit) {
+// Order the non-window local bits of a tile row so that the lane bits of a warp (the first
+// five unit-index bits; four for 8-byte elements, where a wavefront is half a warp) hit
+// different banks under swz<VB>.  The bank of element l is decided by bits [0, VB+3) of
+// swz(l): bits below VB are l's own, bit p in [VB, VB+3) is l[p] ^ l[p+3].  So a non-window
+// bit below VB+3 is a good lane bit as it is, and a bank bit p >= VB that lies inside the
+// window is replaced by bit p+3, which the swizzle folds onto it.  Windows that start at bit
+// 0 are read with 16-byte accesses instead (`vec`): there the natural order is conflict-free.
+inline int choose_unit_bits(int logC, int lbit, int K, int vb, bool vec, uint8_t* ubit) {
   std::vector<int> order;
   std::vector<bool> used(32, false);
   auto in_window = [&](int b) { return b >= lbit && b < lbit + K; };
-  for (int p = 0; p < SW && p < logC; ++p) {
-    int cand = -1;
-    if (!in_window(p)) cand = p;
-    else if (p + SW < logC && !in_window(p + SW)) cand = p + SW;
-    if (cand >= 0 && !used[cand]) { order.push_back(cand); used[cand] = true; }
+  if (!vec) {
+    for (int p = 0; p < vb + 3 && p < logC; ++p) {
+      int cand = -1;
+      if (!in_window(p)) cand = p;
+      else if (p >= vb && p + 3 < logC && !in_window(p + 3)) cand = p + 3;
+      if (cand >= 0 && !used[cand]) { order.push_back(cand); used[cand] = true; }
+    }
   }
   for (int b = 0; b < logC; ++b)
     if (!in_window(b) && !used[b]) { order.push_back(b); used[b] = true; }
@@ -79,7 +85,7 @@ inline Panel full_row_panel(int log_n) { return Panel{log_n, log_n, log_n, 0}; }
 // crosses a change of radix or direction, nor a stage index listed in `cuts` (a snapshot
 // is emitted after the group that ends at cuts[i], into slot i).
 inline bool plan_fw_groups(const std::vector<Stage>& st, int t0, int t1, const std::vector<int>& cuts,
-                           const Panel& pn, int sw, int kmax, std::vector<FwGroup>& out) {
+                           const Panel& pn, int vb, int kmax, std::vector<FwGroup>& out) {
   auto local_bit = [&](int gb) { return gb < pn.lseg ? gb : gb - pn.pb + pn.lseg; };
   int t = t0;
   while (t < t1) {
@@ -111,7 +117,9 @@ inline bool plan_fw_groups(const std::vector<Stage>& st, int t0, int t1, const s
       g.pattern = (uint8_t)(radix == 4 ? (dec ? kR4Dec : kR4Inc) : (dec ? kR2Dec : kR2Inc));
       g.which = (uint8_t)st[first].which;
       for (int s = 0; s < cnt; ++s) g.tw_off[s] = st[first + s].tw_off;
-      g.nubits = (uint8_t)choose_unit_bits(pn.logC, g.lbit, g.K, sw, g.ubit);
+      g.vec = (uint8_t)(g.lbit == 0 && (1 << g.K) >= (1 << vb) && pn.lseg >= g.K);
+      g.nubits = (uint8_t)choose_unit_bits(pn.logC, g.lbit, g.K, vb, g.vec != 0, g.ubit);
+      for (int m = 0; m < (1 << g.K); ++m) g.d[m] = (uint16_t)swz_rt(m << g.lbit, vb);
       for (size_t ci = 0; ci < cuts.size(); ++ci)
         if (cuts[ci] == last + 1) g.emit = (uint8_t)(ci + 1);
       out.push_back(g);
@@ -122,11 +130,15 @@ inline bool plan_fw_groups(const std::vector<Stage>& st, int t0, int t1, const s
   return true;
 }
 
+// Rows per forward tile: as many as fit the shared memory one CTA may use when `ctas` CTAs
+// share an SM (1 KB per CTA is reserved by the system), capped by max_rows and the batch.
 template <typename T>
-inline int fw_rows_per_tile(int logC, int B) {
+inline int fw_rows_per_tile(int logC, int B, int ctas, int max_rows) {
   const int row_bytes = (int)sizeof(T) << logC;
-  int R = kSmemMax / row_bytes;
-  if (R > 16) R = 16;
+  const int budget = ctas <= 1 ? kSmemMax : (228 * 1024) / ctas - 1024;
+  int R = budget / row_bytes;
+  if (R < 1) R = kSmemMax / row_bytes;  // a row that only fits alone: one CTA per SM after all
+  if (R > max_rows) R = max_rows;
   if (R > B) R = B;
   return R;
 }
@@ -146,7 +158,7 @@ struct BwPhase {
 // Inside a phase, sub-groups are windows of KW bits holding up to KW radix-2 stages (or one
 // radix-4 stage when KW == 2).
 inline std::vector<BwPhase> plan_bw_phases(const std::vector<Stage>& st, int log_n, int logCmax, int KW,
-                                           int max_sg, int sw) {
+                                           int max_sg, int vb) {
   std::vector<BwPhase> phases;
   const int L = (int)st.size();
   const int lc = std::min(logCmax, log_n);
@@ -176,6 +188,9 @@ inline std::vector<BwPhase> plan_bw_phases(const std::vector<Stage>& st, int log
           const int b = st[e + cnt].bit;
           const int nlo = std::min(wlo, b), nhi = std::max(whi, b);
           if (nhi - nlo + 1 > KW) break;
+          // keep two-bit windows on even bits: a window starting at bit 1 cannot be made
+          // bank-conflict free (bank bits 0 and 1 have no substitute)
+          if (nhi != nlo && (nlo & 1)) break;
           wlo = nlo; whi = nhi;
           ++cnt;
         }
@@ -221,7 +236,9 @@ inline std::vector<BwPhase> plan_bw_phases(const std::vector<Stage>& st, int log
         sg.q[k] = (uint8_t)(st[s.first + k].bit - wg);
         sg.tw_off[k] = st[s.first + k].tw_off;
       }
-      sg.nubits = (uint8_t)choose_unit_bits(ph.panel.logC, wl, width, sw, sg.ubit);
+      sg.vec = (uint8_t)(wl == 0 && (1 << width) >= (1 << vb) && ph.panel.lseg >= width);
+      sg.nubits = (uint8_t)choose_unit_bits(ph.panel.logC, wl, width, vb, sg.vec != 0, sg.ubit);
+      for (int m = 0; m < (1 << width); ++m) sg.d[m] = (uint16_t)swz_rt(m << wl, vb);
     }
     phases.push_back(ph);
     t = e;

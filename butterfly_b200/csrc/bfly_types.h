@@ -115,12 +115,20 @@ BFLY_HD int insert_zeros(int x, int pos, int nbits) {
   return ((x & ~low) << nbits) | (x & low);
 }
 
-// Shared-memory placement of local column l of a tile row: the low SW bits (the bank
-// index of a 4-byte word for SW=5, of an 8-byte word within a half-warp for SW=4) are
-// XORed with the next SW bits, so that every access pattern "32 lanes differ in 5 chosen
-// bits of l" used by the kernels is free of bank conflicts.
-template <int SW> BFLY_HD int swz(int l) { return l ^ ((l >> SW) & ((1 << SW) - 1)); }
-template <typename T> struct SwBits { static constexpr int value = (sizeof(T) == 4) ? 5 : 4; };
+// Elements per 16-byte chunk.
+template <typename T> struct Vec16 {};
+template <> struct Vec16<float> { static constexpr int N = 4; static constexpr int LOG = 2; };
+template <> struct Vec16<cf> { static constexpr int N = 2; static constexpr int LOG = 1; };
+
+// Shared-memory placement of local column l of a tile row.  Rows are stored as 16-byte
+// chunks (2^VB elements); the low three bits of the chunk index (which select one of the
+// eight 16-byte bank groups of a 128-byte wavefront) are XORed with the next three, so whole
+// chunks move (16-byte copies stay possible) and every access pattern the kernels use --
+// 32 lanes that differ in five chosen bits of l, or 8 lanes reading consecutive chunks --
+// is free of bank conflicts.
+template <int VB> BFLY_HD int swz(int l) { return l ^ (((l >> (VB + 3)) & 7) << VB); }
+template <typename T> BFLY_HD int swzT(int l) { return swz<Vec16<T>::LOG>(l); }
+inline int swz_rt(int l, int vb) { return l ^ (((l >> (vb + 3)) & 7) << vb); }
 
 // ---------------------------------------------------------------- descriptors
 
@@ -156,9 +164,11 @@ struct FwGroup {
   uint8_t lbit, K, pattern, which;  // which: twiddle tensor (0 radix-2, 1 radix-4)
   uint8_t nubits;                   // log2(units per tile row) = logC - K
   uint8_t emit;                     // 1 + snapshot slot to write after this group, 0 = none
-  uint8_t pad_[2];
+  uint8_t vec;                      // window starts at bit 0 and spans whole chunks: 16-byte accesses
+  uint8_t pad_;
   uint32_t tw_off[kMaxK];           // element offset of each stage's twiddle inside one stack
   uint8_t ubit[kMaxUnitBits];       // local bit position of unit-index bit j
+  uint16_t d[1 << kMaxK];           // swz(m << lbit): element m of a unit sits at swz(unit) ^ d[m]
 };
 
 template <typename T> struct FwParams {
@@ -173,6 +183,8 @@ template <typename T> struct FwParams {
   T* snap[8];                // snapshot buffers, (B,S,n) contiguous
   int B, S, log_n;
   int R;                     // rows per tile
+  int tab_slots;             // units per thread and group (max over groups)
+  int use_table;             // unit positions come from a per-CTA table in shared memory
   int vec_in, vec_out;       // 16-byte global accesses allowed
   Panel panel;
   int ngroups;
@@ -185,9 +197,10 @@ template <typename T> struct FwParams {
 struct BwSg {
   uint8_t lbit, nst, radix, which;
   uint8_t q[2];                // bit offset of each stage inside the window
-  uint8_t nubits, pad_;
+  uint8_t nubits, vec;
   uint32_t tw_off[2];
   uint8_t ubit[kMaxUnitBits];
+  uint16_t d[4];               // swz(m << lbit)
 };
 
 template <typename T> struct BwParams {

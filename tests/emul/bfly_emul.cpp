@@ -17,29 +17,32 @@ namespace {
 
 struct EmulExec {
   int sms = 7;       // odd on purpose: exercises ragged row slices
-  int threads = 64;  // simulated block size (any power of two)
+  int threads_ = 64;  // simulated block size (any power of two)
   int num_sms() const { return sms; }
+  int threads() const { return threads_; }
 
   template <typename T> int run_fw(const FwParams<T>& p) {
     const int C = 1 << p.panel.logC;
     std::vector<T> sm((size_t)p.R * C);
+    std::vector<uint16_t> tab((size_t)p.ngroups * p.tab_slots * threads_ + 1);
+    for (int tid = 0; tid < threads_; ++tid) fw_build_table<T>(p, tab.data(), tid, threads_);
     const int64_t ntiles = fw_num_tiles(p);
     const int64_t n = (int64_t)1 << p.log_n;
     for (int64_t tile = 0; tile < ntiles; ++tile) {
       int row0, stack, pbase;
       fw_tile_coords(p, tile, row0, stack, pbase);
-      for (int tid = 0; tid < threads; ++tid)
-        tile_load<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm.data(), tid, threads);
+      for (int tid = 0; tid < threads_; ++tid)
+        tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm.data(), tid, threads_);
       for (int g = 0; g < p.ngroups; ++g) {
-        for (int tid = 0; tid < threads; ++tid)
-          fw_group_dispatch<T>(p, p.g[g], sm.data(), p.R, stack, pbase, tid, threads);
+        for (int tid = 0; tid < threads_; ++tid)
+          fw_group_dispatch<T, 4, 0, 0>(p, g, sm.data(), tab.data(), p.R, stack, pbase, tid, threads_);
         if (p.g[g].emit)
-          for (int tid = 0; tid < threads; ++tid)
-            tile_store<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm.data(), tid, threads);
+          for (int tid = 0; tid < threads_; ++tid)
+            tile_store_auto<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm.data(), tid, threads_);
       }
       if (p.out)
-        for (int tid = 0; tid < threads; ++tid)
-          tile_store<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm.data(), tid, threads);
+        for (int tid = 0; tid < threads_; ++tid)
+          tile_store_auto<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm.data(), tid, threads_);
     }
     return BFLY_OK;
   }
@@ -48,7 +51,7 @@ struct EmulExec {
     constexpr int NSG = kMaxSg;
     const int C = 1 << p.panel.logC;
     // the device kernel uses exactly one thread per unit (or a power-of-two multiple)
-    int nthr = threads;
+    int nthr = threads_;
     const int U = C >> KW;
     if (U > nthr) nthr = U;
     std::vector<T> smX((size_t)p.nsg * p.Rb * C), smG((size_t)p.Rb * C);
@@ -61,15 +64,15 @@ struct EmulExec {
       for (int row0 = rb; row0 < re; row0 += p.Rb) {
         const int R = p.Rb;
         for (int tid = 0; tid < nthr; ++tid) {
-          tile_load<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, re, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX.data(), tid, nthr);
-          tile_load<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, re, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG.data(), tid, nthr);
+          tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, re, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX.data(), tid, nthr);
+          tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, re, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG.data(), tid, nthr);
         }
         for (int j = 0; j + 1 < p.nsg; ++j)
           for (int tid = 0; tid < nthr; ++tid) bw_sg_forward<T, KW, NSG>(p, st[tid], j, smX.data(), R, tid, nthr);
         for (int j = p.nsg - 1; j >= 0; --j)
           for (int tid = 0; tid < nthr; ++tid) bw_sg_backward<T, KW, NSG>(p, st[tid], j, smX.data(), smG.data(), R, tid, nthr);
         for (int tid = 0; tid < nthr; ++tid)
-          tile_store<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, re, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG.data(), tid, nthr);
+          tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, re, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG.data(), tid, nthr);
       }
       for (int tid = 0; tid < nthr; ++tid) bw_flush_state<T, KW, NSG>(p, st[tid], stack, pbase, tid, nthr);
     }
@@ -87,13 +90,13 @@ struct EmulExec {
 
 template <typename T>
 int emul_fw(const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS, void* out, Problem q, int threads) {
-  EmulExec ex; ex.threads = threads;
+  EmulExec ex; ex.threads_ = threads;
   return drive_fw<T>(ex, q, (const T*)tw2, (const T*)tw4, (const T*)x, x_sB, x_sS, (T*)out);
 }
 template <typename T>
 int emul_bw(const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS, const void* g, int64_t g_sB, int64_t g_sS,
             void* d2, void* d4, void* dx, Problem q, int threads, int sms) {
-  EmulExec ex; ex.threads = threads; ex.sms = sms;
+  EmulExec ex; ex.threads_ = threads; ex.sms = sms;
   BwLayout<T> lay;
   int rc = check_problem(q);
   if (rc) return rc;
@@ -106,7 +109,69 @@ int emul_bw(const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64
 
 }  // namespace
 
+// Worst shared-memory bank-conflict degree (1 = conflict-free) of the accesses a 256-thread CTA
+// makes to one tile row: per group / sub-group, per warp, per element of the unit.  An access of
+// `bytes` per lane is served in phases of 128/bytes lanes; the degree of a phase is the largest
+// number of distinct 4-byte words that fall into one of the 32 banks.
+static int conflict_degree(const std::vector<long>& byte_addr, int bytes) {
+  const int lanes_per_phase = 128 / bytes;
+  int worst = 1;
+  for (size_t p0 = 0; p0 < byte_addr.size(); p0 += lanes_per_phase) {
+    std::vector<std::vector<long>> bank(32);
+    for (size_t i = p0; i < p0 + lanes_per_phase && i < byte_addr.size(); ++i)
+      for (int w = 0; w < bytes / 4; ++w) {
+        const long word = byte_addr[i] / 4 + w;
+        auto& b = bank[word % 32];
+        if (std::find(b.begin(), b.end(), word) == b.end()) b.push_back(word);
+      }
+    for (auto& b : bank) worst = std::max<int>(worst, (int)b.size());
+  }
+  return worst;
+}
+
+template <typename T>
+static int window_conflicts(int logC, int lbit, int K, bool vec, const uint8_t* ubit, int nubits, const uint16_t* d) {
+  const int nthr = 256, C = 1 << logC, U = C >> K;
+  if (U < 32) return 1;  // tiny rows: several rows share a warp, not analysed
+  int worst = 1;
+  const int V = Vec16<T>::N, E = 1 << K;
+  for (int warp = 0; warp < std::min(nthr, U) / 32; ++warp)
+    for (int m = 0; m < (vec ? E / V : E); ++m) {
+      std::vector<long> addr;
+      for (int lane = 0; lane < 32; ++lane) {
+        const int u = warp * 32 + lane;
+        const int a0 = swzT<T>(deposit_unit(u, ubit, nubits));
+        addr.push_back((long)(a0 ^ d[vec ? m * V : m]) * (long)sizeof(T));
+      }
+      worst = std::max(worst, conflict_degree(addr, vec ? 16 : (int)sizeof(T)));
+    }
+  return worst;
+}
+
+template <typename T>
+static int max_conflicts(const Problem& q, int kmax) {
+  const std::vector<Stage> st = problem_stages(q);
+  int worst = 1;
+  std::vector<FwGroup> groups;
+  const Panel pn = full_row_panel(q.log_n);
+  if (!plan_fw_groups(st, 0, (int)st.size(), {}, pn, Vec16<T>::LOG, kmax, groups)) return -1;
+  for (auto& g : groups) worst = std::max(worst, window_conflicts<T>(pn.logC, g.lbit, g.K, g.vec != 0, g.ubit, g.nubits, g.d));
+  BwLayout<T> lay;
+  if (plan_bw<T>(q, lay) != BFLY_OK) return -1;
+  for (auto& ph : lay.phases)
+    for (int j = 0; j < ph.nsg; ++j) {
+      const BwSg& sg = ph.sg[j];
+      const int width = sg.radix == 4 ? 2 : lay.kw;
+      worst = std::max(worst, window_conflicts<T>(ph.panel.logC, sg.lbit, width, sg.vec != 0, sg.ubit, sg.nubits, sg.d));
+    }
+  return worst;
+}
+
 extern "C" {
+int bfly_emul_max_conflicts(int dtype, int base4, int log_n, int nblocks, int inc, int kmax) {
+  Problem q{4, 1, log_n, nblocks, 1 << log_n, 1 << log_n, inc != 0, base4 != 0};
+  return dtype == 0 ? max_conflicts<float>(q, kmax) : max_conflicts<cf>(q, kmax);
+}
 // dtype: 0 float32, 1 complex64.  base4: tw2 = twiddle2, tw4 = twiddle4; else tw2 = twiddle.
 int bfly_emul_fw(int dtype, int base4, const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS, void* out,
                  int B, int S, int log_n, int nblocks, int in_size, int out_size, int inc, int threads) {

@@ -138,3 +138,17 @@ def test_emulated_kernels_on_golden(emul, path):
     d2, _, dx = emul_bw(emul, d["twiddle"], None, d["input"], d["grad"], d["increasing_stride"], d["log_n"],
                         d["nblocks"], False)
     assert rel_err(d2, d["d_twiddle"]) < 2e-5 and rel_err(dx, d["d_input"]) < 2e-5
+
+
+def test_shared_memory_accesses_are_bank_conflict_free(emul):
+    """With 256 threads per CTA, every register-window access of the planned groups (forward) and
+    sub-groups (backward) must hit 32 distinct banks per wavefront, for the window widths the
+    kernels use by default (3 bits float / 2 bits complex) at the benchmark sizes."""
+    for dtype, kmax in ((0, 3), (1, 2)):
+        for log_n in (10, 11, 12, 13):
+            for nblocks, inc in ((1, 1), (2, 1), (2, 0)):
+                deg = emul.bfly_emul_max_conflicts(dtype, 0, log_n, nblocks, inc, kmax)
+                assert deg == 1, (dtype, log_n, nblocks, inc, deg)
+    # base-4 (float): radix-4 windows of 2 bits
+    for log_n in (10, 12, 14):
+        assert emul.bfly_emul_max_conflicts(0, 1, log_n, 1, 1, 2) == 1
