@@ -664,106 +664,196 @@ BFLY_HD void bw_flush_state(const BwParams<T>& p, const BwState<T, KW, NSG>& st,
 }
 
 // Load / store the thread's unit of one tile row (16-byte accesses when the window starts
-// at bit 0 and the unit is a whole number of chunks).
-template <typename T, int KW>
-BFLY_HD void bw_unit_ld(smaddr_t rowbase, const int* off, bool vec, T* v) {
+// at bit 0 and the unit is a whole number of chunks).  IMM is a compile-time byte offset.
+template <typename T, int KW, bool VEC, int IMM>
+BFLY_HD void bw_unit_ld(smaddr_t rowbase, const int* off, T* v) {
   constexpr int E = 1 << KW;
   constexpr int V = Vec16<T>::N;
-  if constexpr (E >= V) {
-    if (vec) {
+  if constexpr (VEC && E >= V) {
 #pragma unroll
-      for (int h = 0; h < E / V; ++h) sm_ld16<0>(rowbase + (smaddr_t)off[h * V], v + h * V);
-      return;
-    }
+    for (int h = 0; h < E / V; ++h) sm_ld16<IMM>(rowbase + (smaddr_t)off[h * V], v + h * V);
+  } else {
+#pragma unroll
+    for (int m = 0; m < E; ++m) sm_ld<IMM>(rowbase + (smaddr_t)off[m], v[m]);
   }
-#pragma unroll
-  for (int m = 0; m < E; ++m) sm_ld<0>(rowbase + (smaddr_t)off[m], v[m]);
 }
-template <typename T, int KW>
-BFLY_HD void bw_unit_st(smaddr_t rowbase, const int* off, bool vec, const T* v) {
+template <typename T, int KW, bool VEC, int IMM>
+BFLY_HD void bw_unit_st(smaddr_t rowbase, const int* off, const T* v) {
   constexpr int E = 1 << KW;
   constexpr int V = Vec16<T>::N;
-  if constexpr (E >= V) {
-    if (vec) {
+  if constexpr (VEC && E >= V) {
 #pragma unroll
-      for (int h = 0; h < E / V; ++h) sm_st16<0>(rowbase + (smaddr_t)off[h * V], v + h * V);
-      return;
-    }
+    for (int h = 0; h < E / V; ++h) sm_st16<IMM>(rowbase + (smaddr_t)off[h * V], v + h * V);
+  } else {
+#pragma unroll
+    for (int m = 0; m < E; ++m) sm_st<IMM>(rowbase + (smaddr_t)off[m], v[m]);
   }
-#pragma unroll
-  for (int m = 0; m < E; ++m) sm_st<0>(rowbase + (smaddr_t)off[m], v[m]);
 }
 
-// Forward recompute of sub-group j: reads the thread's unit of every row from snapshot j,
-// applies the sub-group's stages, writes snapshot j+1.
-template <typename T, int KW, int NSG>
-BFLY_HD void bw_sg_forward(const BwParams<T>& p, const BwState<T, KW, NSG>& st, int j, T* __restrict__ smX,
-                           int R, int tid, int nthr) {
+// Stage pattern of a sub-group, resolved once per sub-group step (not per row):
+//   KW == 2, radix 2: two stages on bits (q0, q1) -> q0*2 + q1 ; one stage on bit q -> 4 + q
+//   KW == 2, radix 4: 6          KW == 1: 0
+BFLY_HD int bw_pattern(const BwSg& sg, int KW) {
+  if (KW == 1) return 0;
+  if (sg.radix == 4) return 6;
+  return sg.nst == 2 ? sg.q[0] * 2 + sg.q[1] : 4 + sg.q[0];
+}
+
+template <typename T, int KW, int PATID>
+BFLY_HD void bw_apply_fw(T* v, const T* tw) {
+  if constexpr (KW == 1) {
+    r2_stage_fw<T, 1, 0>(v, tw);
+  } else if constexpr (PATID == 6) {
+    r4_stage_fw<T, 2, 0>(v, tw);
+  } else if constexpr (PATID >= 4) {
+    r2_stage_fw<T, 2, PATID - 4>(v, tw);
+  } else {
+    r2_stage_fw<T, 2, PATID / 2>(v, tw);
+    r2_stage_fw<T, 2, PATID % 2>(v, tw + 8);
+  }
+}
+template <typename T, int KW, int PATID>
+BFLY_HD void bw_apply_bw(T* g, const T* x, const T* tw, T* acc) {
+  if constexpr (KW == 1) {
+    r2_bw_q<T, 1, 0>(g, x, tw, acc);
+  } else if constexpr (PATID == 6) {
+    r4_bw4<T>(g, x, tw, acc);
+  } else if constexpr (PATID >= 4) {
+    r2_bw_q<T, 2, PATID - 4>(g, x, tw, acc);
+  } else {
+    T x1[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) x1[m] = x[m];
+    r2_stage_fw<T, 2, PATID / 2>(x1, tw);
+    r2_bw_q<T, 2, PATID % 2>(g, x1, tw + 8, acc + 8);
+    r2_bw_q<T, 2, PATID / 2>(g, x, tw, acc);
+  }
+}
+
+// Forward recompute of sub-group j over the rows of a batch: reads the thread's unit of every
+// row from snapshot j, applies the sub-group's stages, writes snapshot j+1.
+// LOGC / RB > 0 fix the panel width and the batch height at compile time.
+template <typename T, int KW, int NSG, int LOGC, int RB, int PATID, bool VEC>
+BFLY_HD void bw_sg_forward_rows(const BwParams<T>& p, const BwState<T, KW, NSG>& st, int j, T* __restrict__ smX,
+                                int R, int tid, int nthr) {
   constexpr int E = 1 << KW;
   constexpr int SZ = (int)sizeof(T);
+  constexpr int UNR = 2;
+  constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;
   const BwSg& sg = p.sg[j];
-  const int C = 1 << p.panel.logC;
+  const int C = LOGC > 0 ? (1 << LOGC) : (1 << p.panel.logC);
+  const int Rb = RB > 0 ? RB : p.Rb;
   const BwThread th = bw_thread<KW>(p.panel.logC, tid, nthr);
   int off[E];
 #pragma unroll
   for (int m = 0; m < E; ++m) off[m] = (st.a0[j] ^ sg.d[m]) * SZ;
-  const smaddr_t src = sm_addr(smX + (size_t)j * p.Rb * C);
-  const smaddr_t dst = sm_addr(smX + (size_t)(j + 1) * p.Rb * C);
-  const bool vec = sg.vec != 0;
-  for (int r = th.r0; r < R; r += th.rstep) {
-    T v[E];
-    bw_unit_ld<T, KW>(src + (smaddr_t)(r * C * SZ), off, vec, v);
-    if constexpr (KW == 2) {
-      if (sg.radix == 4) {
-        r4_stage_fw<T, 2, 0>(v, st.tw[j]);
-      } else {
-        r2_fw_rt<T, 2>(v, st.tw[j], sg.q[0]);
-        if (sg.nst > 1) r2_fw_rt<T, 2>(v, st.tw[j] + 8, sg.q[1]);
+  const smaddr_t src = sm_addr(smX) + (smaddr_t)(j * Rb * C * SZ);
+  const smaddr_t dst = src + (smaddr_t)(Rb * C * SZ);
+  if (LOGC > 0 && RB > 0 && th.rstep == 1) {
+    if constexpr (LOGC > 0 && RB > 0) {
+      // a real loop (not unrolled: the body is reused from the instruction cache) over row
+      // pairs; inside the body the second row is an immediate offset
+#pragma unroll 1
+      for (int rr = 0; rr < RB; rr += UNR) {
+        const smaddr_t so = (smaddr_t)(rr * ROWB);
+        T v[UNR][E];
+        static_for<0, UNR>([&](auto jc) {
+          constexpr int jj = decltype(jc)::value;
+          bw_unit_ld<T, KW, VEC, jj * ROWB>(src + so, off, v[jj]);
+        });
+        static_for<0, UNR>([&](auto jc) {
+          constexpr int jj = decltype(jc)::value;
+          bw_apply_fw<T, KW, PATID>(v[jj], st.tw[j]);
+          bw_unit_st<T, KW, VEC, jj * ROWB>(dst + so, off, v[jj]);
+        });
       }
-    } else {
-      r2_fw_rt<T, 1>(v, st.tw[j], 0);
     }
-    bw_unit_st<T, KW>(dst + (smaddr_t)(r * C * SZ), off, vec, v);
+  } else {
+    for (int r = th.r0; r < R; r += th.rstep) {
+      T v[E];
+      bw_unit_ld<T, KW, VEC, 0>(src + (smaddr_t)(r * C * SZ), off, v);
+      bw_apply_fw<T, KW, PATID>(v, st.tw[j]);
+      bw_unit_st<T, KW, VEC, 0>(dst + (smaddr_t)(r * C * SZ), off, v);
+    }
   }
 }
 
-// Backward of sub-group j: reads snapshot j and the gradient tile, accumulates the twiddle
-// gradient of the thread's unit and replaces the gradient in place.
-template <typename T, int KW, int NSG>
-BFLY_HD void bw_sg_backward(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, const T* __restrict__ smX,
-                            T* __restrict__ smG, int R, int tid, int nthr) {
+// Backward of sub-group j over the rows of a batch: reads snapshot j and the gradient tile,
+// accumulates the twiddle gradient of the thread's unit and replaces the gradient in place.
+template <typename T, int KW, int NSG, int LOGC, int RB, int PATID, bool VEC>
+BFLY_HD void bw_sg_backward_rows(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, const T* __restrict__ smX,
+                                 T* __restrict__ smG, int R, int tid, int nthr) {
   constexpr int E = 1 << KW;
   constexpr int SZ = (int)sizeof(T);
+  constexpr int UNR = 2;
+  constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;
   const BwSg& sg = p.sg[j];
-  const int C = 1 << p.panel.logC;
+  const int C = LOGC > 0 ? (1 << LOGC) : (1 << p.panel.logC);
+  const int Rb = RB > 0 ? RB : p.Rb;
   const BwThread th = bw_thread<KW>(p.panel.logC, tid, nthr);
   int off[E];
 #pragma unroll
   for (int m = 0; m < E; ++m) off[m] = (st.a0[j] ^ sg.d[m]) * SZ;
-  const smaddr_t src = sm_addr(smX + (size_t)j * p.Rb * C);
+  const smaddr_t src = sm_addr(smX) + (smaddr_t)(j * Rb * C * SZ);
   const smaddr_t gb = sm_addr(smG);
-  const bool vec = sg.vec != 0;
-  for (int r = th.r0; r < R; r += th.rstep) {
-    T x[E], g[E];
-    bw_unit_ld<T, KW>(src + (smaddr_t)(r * C * SZ), off, vec, x);
-    bw_unit_ld<T, KW>(gb + (smaddr_t)(r * C * SZ), off, vec, g);
-    if constexpr (KW == 2) {
-      if (sg.radix == 4) {
-        r4_bw4<T>(g, x, st.tw[j], st.acc[j]);
-      } else if (sg.nst == 1) {
-        r2_bw_rt<T, 2>(g, x, st.tw[j], st.acc[j], sg.q[0]);
-      } else {
-        T x1[E];
-#pragma unroll
-        for (int m = 0; m < E; ++m) x1[m] = x[m];
-        r2_fw_rt<T, 2>(x1, st.tw[j], sg.q[0]);
-        r2_bw_rt<T, 2>(g, x1, st.tw[j] + 8, st.acc[j] + 8, sg.q[1]);
-        r2_bw_rt<T, 2>(g, x, st.tw[j], st.acc[j], sg.q[0]);
+  if (LOGC > 0 && RB > 0 && th.rstep == 1) {
+    if constexpr (LOGC > 0 && RB > 0) {
+#pragma unroll 1
+      for (int rr = 0; rr < RB; rr += UNR) {
+        const smaddr_t so = (smaddr_t)(rr * ROWB);
+        T x[UNR][E], g[UNR][E];
+        static_for<0, UNR>([&](auto jc) {
+          constexpr int jj = decltype(jc)::value;
+          bw_unit_ld<T, KW, VEC, jj * ROWB>(src + so, off, x[jj]);
+          bw_unit_ld<T, KW, VEC, jj * ROWB>(gb + so, off, g[jj]);
+        });
+        static_for<0, UNR>([&](auto jc) {
+          constexpr int jj = decltype(jc)::value;
+          bw_apply_bw<T, KW, PATID>(g[jj], x[jj], st.tw[j], st.acc[j]);
+          bw_unit_st<T, KW, VEC, jj * ROWB>(gb + so, off, g[jj]);
+        });
       }
-    } else {
-      r2_bw_rt<T, 1>(g, x, st.tw[j], st.acc[j], 0);
     }
-    bw_unit_st<T, KW>(gb + (smaddr_t)(r * C * SZ), off, vec, g);
+  } else {
+    for (int r = th.r0; r < R; r += th.rstep) {
+      T x[E], g[E];
+      bw_unit_ld<T, KW, VEC, 0>(src + (smaddr_t)(r * C * SZ), off, x);
+      bw_unit_ld<T, KW, VEC, 0>(gb + (smaddr_t)(r * C * SZ), off, g);
+      bw_apply_bw<T, KW, PATID>(g, x, st.tw[j], st.acc[j]);
+      bw_unit_st<T, KW, VEC, 0>(gb + (smaddr_t)(r * C * SZ), off, g);
+    }
+  }
+}
+
+// Resolve the (uniform) stage pattern and access kind of sub-group j, then run the rows.
+template <typename T, int KW, int NSG, int LOGC, int RB, bool FORWARD>
+BFLY_HD void bw_sg_step(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, T* __restrict__ smX,
+                        T* __restrict__ smG, int R, int tid, int nthr) {
+  const BwSg& sg = p.sg[j];
+  const int pat = bw_pattern(sg, KW);
+  const bool vec = sg.vec != 0;
+  auto run = [&](auto pc, auto vc) {
+    constexpr int PATID = decltype(pc)::value;
+    constexpr bool VEC = decltype(vc)::value;
+    if constexpr (FORWARD) bw_sg_forward_rows<T, KW, NSG, LOGC, RB, PATID, VEC>(p, st, j, smX, R, tid, nthr);
+    else bw_sg_backward_rows<T, KW, NSG, LOGC, RB, PATID, VEC>(p, st, j, smX, smG, R, tid, nthr);
+  };
+  auto with_vec = [&](auto pc) {
+    if (vec) run(pc, std::true_type{});
+    else run(pc, std::false_type{});
+  };
+  if constexpr (KW == 1) {
+    with_vec(std::integral_constant<int, 0>{});
+  } else {
+    switch (pat) {
+      case 0: with_vec(std::integral_constant<int, 0>{}); break;
+      case 1: with_vec(std::integral_constant<int, 1>{}); break;
+      case 2: with_vec(std::integral_constant<int, 2>{}); break;
+      case 3: with_vec(std::integral_constant<int, 3>{}); break;
+      case 4: with_vec(std::integral_constant<int, 4>{}); break;
+      case 5: with_vec(std::integral_constant<int, 5>{}); break;
+      default: with_vec(std::integral_constant<int, 6>{}); break;
+    }
   }
 }
 

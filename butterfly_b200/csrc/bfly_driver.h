@@ -235,11 +235,12 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     int Rb = (int)(kSmemMax / row_bytes);
     if (Rb > 16) Rb = 16;
     if (Rb < 1) return BFLY_E_UNSUPPORTED;
+    if (Rb > 2) Rb &= ~1;  // even batch heights: the kernels walk the rows two at a time
     // rows that run in parallel inside a CTA when the panel has fewer units than threads
     const int U = (1 << P.panel.logC) >> lay.kw;
     const int par = U >= KernelCfg<T>::kThreads ? 1 : KernelCfg<T>::kThreads / std::max(U, 1);
     if (Rb < par && (size_t)par * row_bytes <= (size_t)kSmemMax) Rb = par;
-    if (Rb > q.B) Rb = std::max(q.B, 1);
+    if (Rb > q.B && q.B < 8) Rb = std::max(q.B, 1);  // tiny batches; otherwise rows past the batch are zero rows
     p.Rb = Rb;
     const int groups = (1 << P.panel.npanels_log) * q.S;
     int nslices = std::max(1, ex.num_sms() / groups);

@@ -64,7 +64,8 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p) {
   }
 }
 
-template <typename T, int KW, int NSG>
+// LOGC / RB: compile-time panel width (log2) and rows per batch, 0 = read from the parameters.
+template <typename T, int KW, int NSG, int LOGC, int RB>
 __global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_constant__ BwParams<T> p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* smX = reinterpret_cast<T*>(smem_raw);
@@ -84,14 +85,14 @@ __global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_const
 #pragma unroll
     for (int j = 0; j < NSG - 1; ++j) {
       if (j + 1 < p.nsg) {
-        bw_sg_forward<T, KW, NSG>(p, st, j, smX, R, tid, kThreads);
+        bw_sg_step<T, KW, NSG, LOGC, RB, true>(p, st, j, smX, smG, R, tid, kThreads);
         __syncthreads();
       }
     }
 #pragma unroll
     for (int j = NSG - 1; j >= 0; --j) {
       if (j < p.nsg) {
-        bw_sg_backward<T, KW, NSG>(p, st, j, smX, smG, R, tid, kThreads);
+        bw_sg_step<T, KW, NSG, LOGC, RB, false>(p, st, j, smX, smG, R, tid, kThreads);
         __syncthreads();
       }
     }
@@ -209,24 +210,38 @@ struct CudaExec {
     return launch_fw_shape<T, KernelCfg<T>::kFwKmaxOneCta>(p);
   }
 
-  template <typename T, int KW, int NSG> int launch_bw(const BwParams<T>& p) {
+  template <typename T, int KW, int NSG, int LOGC, int RB> int launch_bw(const BwParams<T>& p) {
     const size_t smem = (size_t)(p.nsg + 1) * p.Rb * sizeof(T) << p.panel.logC;
-    int rc = set_smem(bfly_bw_kernel<T, KW, NSG>, smem);
+    int rc = set_smem(bfly_bw_kernel<T, KW, NSG, LOGC, RB>, smem);
     if (rc) return rc;
     {
       ProfileScope prof(kKernBw, stream);
-      bfly_bw_kernel<T, KW, NSG><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+      bfly_bw_kernel<T, KW, NSG, LOGC, RB><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
     }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
   }
+  // Instances with the panel shape fixed at compile time cover full 1024-column float panels
+  // (512-column complex panels) with the batch heights the planner picks; the rest is generic.
   int run_bw(const BwParams<float>& p, int KW) {
-    if (KW == 2) return p.nsg <= 3 ? launch_bw<float, 2, 3>(p) : launch_bw<float, 2, 5>(p);
-    return launch_bw<float, 1, 10>(p);
+    if (KW == 2) {
+      if (p.panel.logC == 10) {
+        if (p.nsg == 5 && p.Rb == 8) return launch_bw<float, 2, 5, 10, 8>(p);
+        if (p.nsg == 4 && p.Rb == 10) return launch_bw<float, 2, 5, 10, 10>(p);
+        if (p.nsg == 3 && p.Rb == 14) return launch_bw<float, 2, 3, 10, 14>(p);
+        if (p.nsg <= 2 && p.Rb == 16) return launch_bw<float, 2, 3, 10, 16>(p);
+      }
+      return p.nsg <= 3 ? launch_bw<float, 2, 3, 0, 0>(p) : launch_bw<float, 2, 5, 0, 0>(p);
+    }
+    return launch_bw<float, 1, 10, 0, 0>(p);
   }
   int run_bw(const BwParams<cf>& p, int KW) {
     if (KW != 1) return BFLY_E_UNSUPPORTED;
-    return p.nsg <= 5 ? launch_bw<cf, 1, 5>(p) : launch_bw<cf, 1, 10>(p);
+    if (p.panel.logC == 9) {
+      if (p.nsg >= 9 && p.Rb == 4) return launch_bw<cf, 1, 10, 9, 4>(p);
+      if (p.nsg <= 2 && p.Rb == 16) return launch_bw<cf, 1, 5, 9, 16>(p);
+    }
+    return p.nsg <= 5 ? launch_bw<cf, 1, 5, 0, 0>(p) : launch_bw<cf, 1, 10, 0, 0>(p);
   }
   int zero(void* ptr, size_t bytes) {
     if (bytes == 0) return BFLY_OK;
