@@ -19,8 +19,10 @@ F32, C64 = 0, 1
 SYMBOLS = (
     "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
-    "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect",
+    "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
 )
+
+NOALLOC_SCRATCH_BYTES = 32 << 20
 
 _lib = None
 
@@ -116,6 +118,34 @@ def bw(twiddle, x, grad, increasing_stride=True, workspace=None, d_twiddle=None,
             int(out_size), int(bool(increasing_stride)), _p(workspace), ctypes.c_size_t(ws_bytes), _stream())
     if check and rc != 0:
         raise BflyError(rc, "bfly_bw")
+    return d_twiddle, d_x, rc
+
+
+def bw_noalloc(twiddle, x, grad, increasing_stride=True, d_twiddle=None, d_x=None, check=True):
+    """``bfly_bw_f32_noalloc``: the float32 backward with the library's built-in scratch buffer.
+
+    For hosts that cannot hand the library any device scratch at the call site.  The outputs are
+    passed in by the caller as usual (allocated here only when omitted, for convenience in tests);
+    the call itself allocates nothing.  Returns (d_twiddle, d_x buffer, status); status is
+    ``-7`` (BFLY_E_TOOLARGE) when the shape needs more than ``NOALLOC_SCRATCH_BYTES``.
+    """
+    _check_rows(x)
+    _check_rows(grad)
+    assert x.dtype == torch.float32
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    out_size = grad.shape[2]
+    if d_twiddle is None:
+        d_twiddle = torch.empty_like(twiddle)
+    if d_x is None:
+        d_x = torch.empty(B, S, max(in_size, n), dtype=x.dtype, device=x.device)
+    rc = lib().bfly_bw_f32_noalloc(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(grad),
+                                   _i64(grad.stride(0)), _i64(grad.stride(1)), _p(d_twiddle), _p(d_x), int(B),
+                                   int(S), int(log_n), int(nblocks), int(in_size), int(out_size),
+                                   int(bool(increasing_stride)), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_bw_f32_noalloc")
     return d_twiddle, d_x, rc
 
 

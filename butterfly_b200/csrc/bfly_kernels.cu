@@ -308,6 +308,31 @@ static int64_t ws_entry(bool base4, int dtype, int B, int S, int log_n, int nblo
   return BFLY_E_UNSUPPORTED;
 }
 
+// ------------------------------------------------------------------ no-allocation backward
+//
+// Scratch for bfly_bw_f32_noalloc: part of the library image, resident on every GPU that
+// loads it.  In host code the name below is only a handle; the address the kernels need is
+// looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BFLY_NOALLOC_SCRATCH_BYTES];
+
+static int noalloc_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static void* cache[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BFLY_E_NODEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return BFLY_E_CUDA;
+    }
+    cache[dev] = p;
+  }
+  *out = cache[dev];
+  return BFLY_OK;
+}
+
 }  // namespace bfly
 
 using namespace bfly;
@@ -323,6 +348,7 @@ const char* bfly_strerror(int status) {
     case BFLY_E_WORKSPACE: return "workspace missing, misaligned or too small";
     case BFLY_E_CUDA: return "CUDA runtime call or kernel launch failed";
     case BFLY_E_NODEVICE: return "no usable CUDA device";
+    case BFLY_E_TOOLARGE: return "problem needs more scratch than the built-in buffer of the no-allocation entry point holds";
     default: return "unknown status";
   }
 }
@@ -388,6 +414,26 @@ int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, 
   return bw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x, batch,
                       nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
                       workspace_bytes, stream);
+}
+int bfly_bw_f32_noalloc(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, const float* grad,
+                        int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x, int batch, int nstacks, int log_n,
+                        int nblocks, int input_size, int output_size, int increasing_stride, void* stream) {
+  // how much scratch this very call needs (direction known here, unlike the workspace query)
+  Problem q{batch, nstacks, log_n, nblocks, input_size, output_size, increasing_stride != 0, false};
+  int rc = check_problem(q);
+  if (rc) return rc;
+  BwLayout<float> lay;
+  rc = plan_bw<float>(q, lay);
+  if (rc) return rc;
+  if (lay.ws_bytes > (size_t)BFLY_NOALLOC_SCRATCH_BYTES) return BFLY_E_TOOLARGE;
+  void* scratch = nullptr;
+  if (lay.ws_bytes > 0) {
+    rc = noalloc_scratch_ptr(&scratch);
+    if (rc) return rc;
+  }
+  return bw_entry<float>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x,
+                         batch, nstacks, log_n, nblocks, input_size, output_size, increasing_stride, scratch,
+                         lay.ws_bytes, stream);
 }
 int bfly4_fw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB, int64_t x_sS,
                  float* out, int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,

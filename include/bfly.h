@@ -42,6 +42,7 @@ extern "C" {
 #define BFLY_E_WORKSPACE (-4)    /* workspace missing, misaligned or too small */
 #define BFLY_E_CUDA (-5)         /* a CUDA runtime call or launch failed */
 #define BFLY_E_NODEVICE (-6)     /* no usable CUDA device */
+#define BFLY_E_TOOLARGE (-7)     /* needs more scratch than the built-in buffer of the no-allocation entry point */
 
 #define BFLY_F32 0
 #define BFLY_C64 1
@@ -83,6 +84,37 @@ int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, 
                 int64_t g_sB, int64_t g_sS, void* d_twiddle, void* d_x, int batch, int nstacks,
                 int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward for callers that cannot give the library scratch memory.  (No counterpart in the
+ * reference: its backward always allocates its `intermediate_storage` through torch.)
+ *
+ * Same arguments and results as bfly_bw_f32, minus the workspace: the snapshots of the
+ * activation that the backward writes between its phases go into a buffer that is part of
+ * the library image itself, a fixed BFLY_NOALLOC_SCRATCH_BYTES per GPU that stays resident
+ * from the moment the library is loaded on that GPU until the process exits.  It exists for
+ * hosts where a device allocation is not an option at the call site: code running inside a
+ * CUDA-graph capture or a real-time loop where cudaMalloc would synchronise the device, a
+ * plugin whose host framework owns all device memory and hands out none, a process whose
+ * memory budget was fixed at start-up.  The call makes no cudaMalloc / cudaFree and uses no
+ * allocating library routine.
+ *
+ * Limits and rules:
+ *  - the shape must need at most BFLY_NOALLOC_SCRATCH_BYTES of scratch (what
+ *    bfly_bw_workspace_bytes reports); larger problems return BFLY_E_TOOLARGE and do nothing.
+ *    Shapes whose backward is a single phase (nblocks * log_n <= 10 with n <= 1024) need none.
+ *  - the first call on each GPU looks up the buffer's device address (one
+ *    cudaGetSymbolAddress with that GPU current); make that first call outside any stream
+ *    capture.
+ *  - every call on a GPU shares the one buffer, and the buffer keeps the previous call's
+ *    contents.  Nothing in it needs clearing (each snapshot is written in full before it is
+ *    read), but two calls whose kernels overlap on the GPU -- different streams, different
+ *    host threads -- race on it: serialise them.
+ */
+#define BFLY_NOALLOC_SCRATCH_BYTES (32u << 20)
+int bfly_bw_f32_noalloc(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS,
+                        const float* grad, int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x,
+                        int batch, int nstacks, int log_n, int nblocks, int input_size,
+                        int output_size, int increasing_stride, void* stream);
 
 /* Base-4 forward / backward (float32).  The reference computes this product with
  * PyTorch view/permute/sum ops only (torch_butterfly/multiply_base4.py:7-41,
