@@ -295,18 +295,14 @@ def run_gpu_arm(args):
         hdx = torch.empty((B, S, n), dtype=x.dtype).pin_memory()
         hdt = torch.empty(tw.shape, dtype=tw.dtype).pin_memory()
 
+        from butterfly_b200.host import HostPipeline
+        pipe = HostPipeline(dev, chunks=args.e2e_chunks)
+
         def e2e_step():
-            xd = hx.to(dev, non_blocking=True)
-            gd = hg.to(dev, non_blocking=True)
-            if cfg.get("broadcast_stacks"):
-                xd = xd.expand(B, S, n)
-            y = bb.butterfly_multiply_fw(tw, xd, inc)
-            d_tw, d_x = bb.butterfly_multiply_bw(tw, xd, gd, inc)
+            # public host-side API: chunked upload / fw+bw / download on three streams
+            d_tw = pipe.fw_bw(tw, hx, hg, inc, hy, hdx, hdt)
             if world > 1:
                 dist.all_reduce(d_tw)
-            hy.copy_(y, non_blocking=True)
-            hdx.copy_(d_x, non_blocking=True)
-            hdt.copy_(d_tw, non_blocking=True)
         h2d = hx.numel() * sz + hg.numel() * sz
         d2h = (hy.numel() + hdx.numel() + hdt.numel()) * sz
         e2e_steps = max(1, min(args.steps, 5))
@@ -326,7 +322,7 @@ def run_gpu_arm(args):
             ems = float(t.item())
         e2e = {"value": step_bytes * world / (ems / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ems / e2e_steps,
-               "steps": e2e_steps}
+               "steps": e2e_steps, "api": "butterfly_b200.host.HostPipeline.fw_bw (%d row chunks, 3 streams)" % args.e2e_chunks}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -370,6 +366,7 @@ def main():
     ap.add_argument("--config", default="cfg2", choices=["cfg2", "cfg3", "cfg5"])
     ap.add_argument("--ref-rows", type=int, default=4096, help="rows of the bounded CPU sample")
     ap.add_argument("--batch", type=int, default=None, help="override the batch per GPU (profiling a small case)")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="row chunks of the host-memory pipeline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -40,7 +40,7 @@ from .multiply_base4 import (  # noqa: E402,F401
 )
 from . import abi  # noqa: E402,F401
 from .butterfly import Butterfly, ButterflyUnitary, ButterflyBmm, ButterflyBase4  # noqa: E402,F401
-from . import permutation, special  # noqa: E402,F401
+from . import permutation, special, host, distributed  # noqa: E402,F401
 
 __all__ = [
     "butterfly_multiply", "butterfly_multiply_fw", "butterfly_multiply_bw",

@@ -503,12 +503,16 @@ template <typename T> BFLY_HD size_t fw_smem_bytes(const FwParams<T>& p, int nth
 // Per-thread state of a backward phase: the twiddles of the thread's unit in every
 // sub-group, the matching gradient accumulators, and the unit's tile position.  They live
 // in registers for the whole kernel (all loops over them are fully unrolled with constant
-// indices).  KW = window bits: a unit has 2^KW elements.
+// indices).  KW = window bits: a unit has 2^KW elements.  The twiddles themselves are not
+// kept: they are re-read from L2 (where the whole twiddle tensor stays resident) one
+// sub-group step ahead of their use, which frees registers for more rows in flight.
 template <int KW> struct BwTwn { static constexpr int value = (KW == 2) ? 16 : 4; };
 template <typename T, int KW, int NSG> struct BwState {
-  T tw[NSG][BwTwn<KW>::value];
-  T acc[NSG][BwTwn<KW>::value];
-  int a0[NSG];  // swizzled tile index of the unit (window bits zero)
+  T tw[2][BwTwn<KW>::value];     // twiddles of the sub-group being processed (buffer j & 1) and of
+                                 // the next one (the other buffer), fetched one step ahead
+  T acc[NSG][BwTwn<KW>::value];  // gradient accumulators of every sub-group of the phase
+  int a0[NSG];                   // swizzled tile index of the unit (window bits zero)
+  uint32_t twi[NSG][KW];         // element offset of the unit's first twiddle block per stage
 };
 
 // Radix-2 stage with a runtime bit offset q on a 2^KW-element window.
@@ -582,27 +586,22 @@ template <int KW> BFLY_HD BwThread bw_thread(int logC, int tid, int nthr) {
   return t;
 }
 
-// Visit the twiddle blocks of the thread's unit in a sub-group: calls f(slot, element_offset,
-// count) for every contiguous run of `count` twiddle scalars, `slot` being the index into
-// the per-thread state array.
-template <typename T, int KW, typename F>
-BFLY_HD void bw_for_each_tw(const BwParams<T>& p, const BwSg& sg, int lbase, int stack, int pbase, F&& f) {
-  const int col0 = p.panel.col(pbase, lbase);
-  const int wg = p.panel.global_bit(sg.lbit);
-  const int64_t sbase = (int64_t)stack * p.tw_stack[sg.which];
+// Fetch the twiddles of sub-group j (of the thread's unit) into buffer j & 1.
+template <typename T, int KW, int NSG>
+BFLY_HD void bw_fetch_tw(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, int stack) {
+  const BwSg& sg = p.sg[j];
+  const T* twp = p.tw[sg.which] + (int64_t)stack * p.tw_stack[sg.which];
+  T* dst = st.tw[j & 1];
   if (sg.radix == 4) {
-    if constexpr (KW == 2) {
-      const int i = delete_2bits(col0, wg);
-      f(0, sbase + sg.tw_off[0] + (int64_t)i * 16, 16);
-    }
+    if constexpr (KW == 2) load_tw<T, 16>(dst, twp + st.twi[j][0]);
   } else {
+    const int wg = p.panel.global_bit(sg.lbit);
 #pragma unroll
     for (int s = 0; s < KW; ++s) {
       if (s < sg.nst) {
-        const int i = delete_bit(col0, wg + sg.q[s]);
 #pragma unroll
         for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
-          f(s * (1 << (KW - 1)) * 4 + pp * 4, sbase + sg.tw_off[s] + (int64_t)(i + (pp << wg)) * 4, 4);
+          load_tw<T, 4>(dst + s * (1 << (KW - 1)) * 4 + pp * 4, twp + st.twi[j][s] + (uint32_t)((pp << wg) * 4));
       }
     }
   }
@@ -613,22 +612,32 @@ BFLY_HD void bw_load_state(const BwParams<T>& p, BwState<T, KW, NSG>& st, int st
                            int nthr) {
   const BwThread th = bw_thread<KW>(p.panel.logC, tid, nthr);
 #pragma unroll
+  for (int b = 0; b < 2; ++b)
+#pragma unroll
+    for (int e = 0; e < BwTwn<KW>::value; ++e) st.tw[b][e] = Ops<T>::zero();
+#pragma unroll
   for (int j = 0; j < NSG; ++j) {
 #pragma unroll
-    for (int e = 0; e < BwTwn<KW>::value; ++e) { st.tw[j][e] = Ops<T>::zero(); st.acc[j][e] = Ops<T>::zero(); }
+    for (int e = 0; e < BwTwn<KW>::value; ++e) st.acc[j][e] = Ops<T>::zero();
     st.a0[j] = 0;
+#pragma unroll
+    for (int s = 0; s < KW; ++s) st.twi[j][s] = 0;
     if (j < p.nsg) {
       const BwSg& sg = p.sg[j];
       const int lbase = deposit_unit(th.u, sg.ubit, sg.nubits);
       st.a0[j] = swzT<T>(lbase);
-      const T* twp = p.tw[sg.which];
-      T* dst = st.tw[j];
-      bw_for_each_tw<T, KW>(p, sg, lbase, stack, pbase, [&](int slot, int64_t off, int cnt) {
-        if (cnt == 16) load_tw<T, 16>(dst + slot, twp + off);
-        else load_tw<T, 4>(dst + slot, twp + off);
-      });
+      const int col0 = p.panel.col(pbase, lbase);
+      const int wg = p.panel.global_bit(sg.lbit);
+      if (sg.radix == 4) {
+        st.twi[j][0] = sg.tw_off[0] + (uint32_t)delete_2bits(col0, wg) * 16u;
+      } else {
+#pragma unroll
+        for (int s = 0; s < KW; ++s)
+          if (s < sg.nst) st.twi[j][s] = sg.tw_off[s] + (uint32_t)delete_bit(col0, wg + sg.q[s]) * 4u;
+      }
     }
   }
+  bw_fetch_tw<T, KW, NSG>(p, st, 0, stack);
 }
 
 BFLY_HD void atomic_add_el(float* dst, float v) {
@@ -646,19 +655,30 @@ BFLY_HD void atomic_add_el(cf* dst, cf v) {
 template <typename T, int KW, int NSG>
 BFLY_HD void bw_flush_state(const BwParams<T>& p, const BwState<T, KW, NSG>& st, int stack, int pbase,
                             int tid, int nthr) {
-  const BwThread th = bw_thread<KW>(p.panel.logC, tid, nthr);
 #pragma unroll
   for (int j = 0; j < NSG; ++j) {
     if (j < p.nsg) {
       const BwSg& sg = p.sg[j];
-      const int lbase = deposit_unit(th.u, sg.ubit, sg.nubits);
-      T* dtw = p.dtw[sg.which];
-      const T* src = st.acc[j];
-      bw_for_each_tw<T, KW>(p, sg, lbase, stack, pbase, [&](int slot, int64_t off, int cnt) {
+      T* dtw = p.dtw[sg.which] + (int64_t)stack * p.tw_stack[sg.which];
+      if (sg.radix == 4) {
+        if constexpr (KW == 2) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e)
-          if (e < cnt) atomic_add_el(dtw + off + e, src[slot + e]);
-      });
+          for (int e = 0; e < 16; ++e) atomic_add_el(dtw + st.twi[j][0] + e, st.acc[j][e]);
+        }
+      } else {
+        const int wg = p.panel.global_bit(sg.lbit);
+#pragma unroll
+        for (int s = 0; s < KW; ++s) {
+          if (s < sg.nst) {
+#pragma unroll
+            for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                atomic_add_el(dtw + st.twi[j][s] + (uint32_t)((pp << wg) * 4) + e,
+                              st.acc[j][s * (1 << (KW - 1)) * 4 + pp * 4 + e]);
+          }
+        }
+      }
     }
   }
 }
@@ -738,7 +758,7 @@ BFLY_HD void bw_sg_forward_rows(const BwParams<T>& p, const BwState<T, KW, NSG>&
                                 int R, int tid, int nthr) {
   constexpr int E = 1 << KW;
   constexpr int SZ = (int)sizeof(T);
-  constexpr int UNR = 2;
+  constexpr int UNR = (RB > 0 && RB % 4 == 0 && sizeof(T) == 4) ? 4 : 2;  // rows in flight per thread
   constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;
   const BwSg& sg = p.sg[j];
   const int C = LOGC > 0 ? (1 << LOGC) : (1 << p.panel.logC);
@@ -763,7 +783,7 @@ BFLY_HD void bw_sg_forward_rows(const BwParams<T>& p, const BwState<T, KW, NSG>&
         });
         static_for<0, UNR>([&](auto jc) {
           constexpr int jj = decltype(jc)::value;
-          bw_apply_fw<T, KW, PATID>(v[jj], st.tw[j]);
+          bw_apply_fw<T, KW, PATID>(v[jj], st.tw[j & 1]);
           bw_unit_st<T, KW, VEC, jj * ROWB>(dst + so, off, v[jj]);
         });
       }
@@ -772,7 +792,7 @@ BFLY_HD void bw_sg_forward_rows(const BwParams<T>& p, const BwState<T, KW, NSG>&
     for (int r = th.r0; r < R; r += th.rstep) {
       T v[E];
       bw_unit_ld<T, KW, VEC, 0>(src + (smaddr_t)(r * C * SZ), off, v);
-      bw_apply_fw<T, KW, PATID>(v, st.tw[j]);
+      bw_apply_fw<T, KW, PATID>(v, st.tw[j & 1]);
       bw_unit_st<T, KW, VEC, 0>(dst + (smaddr_t)(r * C * SZ), off, v);
     }
   }
@@ -785,7 +805,7 @@ BFLY_HD void bw_sg_backward_rows(const BwParams<T>& p, BwState<T, KW, NSG>& st, 
                                  T* __restrict__ smG, int R, int tid, int nthr) {
   constexpr int E = 1 << KW;
   constexpr int SZ = (int)sizeof(T);
-  constexpr int UNR = 2;
+  constexpr int UNR = (RB > 0 && RB % 4 == 0 && sizeof(T) == 4) ? 4 : 2;  // rows in flight per thread
   constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;
   const BwSg& sg = p.sg[j];
   const int C = LOGC > 0 ? (1 << LOGC) : (1 << p.panel.logC);
@@ -809,7 +829,7 @@ BFLY_HD void bw_sg_backward_rows(const BwParams<T>& p, BwState<T, KW, NSG>& st, 
         });
         static_for<0, UNR>([&](auto jc) {
           constexpr int jj = decltype(jc)::value;
-          bw_apply_bw<T, KW, PATID>(g[jj], x[jj], st.tw[j], st.acc[j]);
+          bw_apply_bw<T, KW, PATID>(g[jj], x[jj], st.tw[j & 1], st.acc[j]);
           bw_unit_st<T, KW, VEC, jj * ROWB>(gb + so, off, g[jj]);
         });
       }
@@ -819,7 +839,7 @@ BFLY_HD void bw_sg_backward_rows(const BwParams<T>& p, BwState<T, KW, NSG>& st, 
       T x[E], g[E];
       bw_unit_ld<T, KW, VEC, 0>(src + (smaddr_t)(r * C * SZ), off, x);
       bw_unit_ld<T, KW, VEC, 0>(gb + (smaddr_t)(r * C * SZ), off, g);
-      bw_apply_bw<T, KW, PATID>(g, x, st.tw[j], st.acc[j]);
+      bw_apply_bw<T, KW, PATID>(g, x, st.tw[j & 1], st.acc[j]);
       bw_unit_st<T, KW, VEC, 0>(gb + (smaddr_t)(r * C * SZ), off, g);
     }
   }
@@ -827,9 +847,14 @@ BFLY_HD void bw_sg_backward_rows(const BwParams<T>& p, BwState<T, KW, NSG>& st, 
 
 // Resolve the (uniform) stage pattern and access kind of sub-group j, then run the rows.
 template <typename T, int KW, int NSG, int LOGC, int RB, bool FORWARD>
-BFLY_HD void bw_sg_step(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, T* __restrict__ smX,
+BFLY_HD void bw_sg_step(const BwParams<T>& p, BwState<T, KW, NSG>& st, int j, int stack, T* __restrict__ smX,
                         T* __restrict__ smG, int R, int tid, int nthr) {
   const BwSg& sg = p.sg[j];
+  // twiddles of the step that follows go into the other buffer while this step computes:
+  // forward steps walk j upwards (the last one hands over to the backward of nsg-1),
+  // backward steps walk j downwards (j = 0 is followed by the forward of j = 0: same twiddles)
+  if (FORWARD) bw_fetch_tw<T, KW, NSG>(p, st, j + 1, stack);
+  else if (j > 0) bw_fetch_tw<T, KW, NSG>(p, st, j - 1, stack);
   const int pat = bw_pattern(sg, KW);
   const bool vec = sg.vec != 0;
   auto run = [&](auto pc, auto vc) {

@@ -21,7 +21,14 @@ template <> struct KernelCfg<float> {
   static constexpr int kFwKmaxOneCta = 4;   // widest window at one CTA per SM
   static constexpr int kThreads = 256;
   static int bw_kw(int log_n) { return log_n >= 2 ? 2 : 1; }
-  static int bw_max_sg(int kw) { return kw == 2 ? 5 : 10; }
+  static int bw_max_sg(int kw) {
+    if (kw != 2) return 10;
+    if (const char* e = std::getenv("BFLY_BW_MAXSG")) {  // experiments: shorter phases
+      const int v = std::atoi(e);
+      if (v >= 1 && v <= 5) return v;
+    }
+    return 5;
+  }
 };
 template <> struct KernelCfg<cf> {
   static constexpr int kFwKmaxTwoCtas = 2;
@@ -233,9 +240,14 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     for (int j = 0; j < P.nsg; ++j) p.sg[j] = P.sg[j];
     const size_t row_bytes = (size_t)(P.nsg + 1) * sizeof(T) << P.panel.logC;
     int Rb = (int)(kSmemMax / row_bytes);
+    if (const char* e = std::getenv("BFLY_BW_ROWS")) {  // experiments: rows per batch
+      const int v = std::atoi(e);
+      if (v >= 1 && v < Rb) Rb = v;
+    }
     if (Rb > 16) Rb = 16;
     if (Rb < 1) return BFLY_E_UNSUPPORTED;
-    if (Rb > 2) Rb &= ~1;  // even batch heights: the kernels walk the rows two at a time
+    if (Rb >= 4) Rb &= ~3;       // batch heights in multiples of four: the kernels keep four rows in flight
+    else if (Rb > 2) Rb &= ~1;
     // rows that run in parallel inside a CTA when the panel has fewer units than threads
     const int U = (1 << P.panel.logC) >> lay.kw;
     const int par = U >= KernelCfg<T>::kThreads ? 1 : KernelCfg<T>::kThreads / std::max(U, 1);

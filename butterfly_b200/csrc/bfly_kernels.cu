@@ -65,8 +65,13 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p) {
 }
 
 // LOGC / RB: compile-time panel width (log2) and rows per batch, 0 = read from the parameters.
+// Phases of at most three sub-groups keep little enough state for two CTAs per SM.
+template <typename T, int KW, int NSG> struct BwOcc {
+  static constexpr int kMinBlocks = (sizeof(T) == 4 && KW == 2 && NSG <= 3) ? 2 : 1;
+};
+
 template <typename T, int KW, int NSG, int LOGC, int RB>
-__global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_constant__ BwParams<T> p) {
+__global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks)) bfly_bw_kernel(const __grid_constant__ BwParams<T> p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* smX = reinterpret_cast<T*>(smem_raw);
   const int C = 1 << p.panel.logC;
@@ -85,14 +90,14 @@ __global__ void __launch_bounds__(kThreads, 1) bfly_bw_kernel(const __grid_const
 #pragma unroll
     for (int j = 0; j < NSG - 1; ++j) {
       if (j + 1 < p.nsg) {
-        bw_sg_step<T, KW, NSG, LOGC, RB, true>(p, st, j, smX, smG, R, tid, kThreads);
+        bw_sg_step<T, KW, NSG, LOGC, RB, true>(p, st, j, stack, smX, smG, R, tid, kThreads);
         __syncthreads();
       }
     }
 #pragma unroll
     for (int j = NSG - 1; j >= 0; --j) {
       if (j < p.nsg) {
-        bw_sg_step<T, KW, NSG, LOGC, RB, false>(p, st, j, smX, smG, R, tid, kThreads);
+        bw_sg_step<T, KW, NSG, LOGC, RB, false>(p, st, j, stack, smX, smG, R, tid, kThreads);
         __syncthreads();
       }
     }
@@ -226,9 +231,9 @@ struct CudaExec {
   int run_bw(const BwParams<float>& p, int KW) {
     if (KW == 2) {
       if (p.panel.logC == 10) {
-        if (p.nsg == 5 && p.Rb == 8) return launch_bw<float, 2, 5, 10, 8>(p);
-        if (p.nsg == 4 && p.Rb == 10) return launch_bw<float, 2, 5, 10, 10>(p);
-        if (p.nsg == 3 && p.Rb == 14) return launch_bw<float, 2, 3, 10, 14>(p);
+        if (p.nsg >= 4 && p.Rb == 8) return launch_bw<float, 2, 5, 10, 8>(p);
+        if (p.nsg == 3 && p.Rb == 12) return launch_bw<float, 2, 3, 10, 12>(p);
+        if (p.nsg <= 3 && p.Rb == 4) return launch_bw<float, 2, 3, 10, 4>(p);
         if (p.nsg <= 2 && p.Rb == 16) return launch_bw<float, 2, 3, 10, 16>(p);
       }
       return p.nsg <= 3 ? launch_bw<float, 2, 3, 0, 0>(p) : launch_bw<float, 2, 5, 0, 0>(p);

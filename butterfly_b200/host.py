@@ -1,0 +1,75 @@
+"""Forward + backward of the butterfly multiply for operands that live in HOST memory.
+
+A caller whose tensors sit in (pinned) host memory -- the situation of a CPU-resident
+pipeline that offloads this operator to the GPU -- pays for two PCIe transfers per step that
+dwarf the kernels.  `HostPipeline` cuts the batch into row chunks and runs three CUDA streams
+(host->device copies, the operators, device->host copies) so that uploads, compute and
+downloads of different chunks overlap and both PCIe directions are busy at once.  The twiddle
+gradient is additive over rows, so the chunks' partial gradients are summed on the device.
+"""
+import torch
+
+from .multiply import butterfly_multiply_bw, butterfly_multiply_fw
+
+
+class HostPipeline:
+    """fw+bw over host-resident input / grad / outputs.
+
+        pipe = HostPipeline(device, chunks=8)
+        pipe.fw_bw(twiddle_dev, x_host, grad_host, increasing_stride, out_host, d_x_host, d_twiddle_host)
+
+    x_host (B, Sx, n) with Sx = 1 (one row shared by all stacks) or Sx = nstacks; grad_host,
+    out_host, d_x_host (B, nstacks, n); all pinned.  Returns after the last download finished.
+    """
+
+    def __init__(self, device, chunks=8):
+        self.device = torch.device(device)
+        self.chunks = chunks
+        self.s_in = torch.cuda.Stream(self.device)
+        self.s_comp = torch.cuda.Stream(self.device)
+        self.s_out = torch.cuda.Stream(self.device)
+
+    def fw_bw(self, twiddle, x_host, grad_host, increasing_stride, out_host, d_x_host, d_twiddle_host):
+        B = x_host.shape[0]
+        S = grad_host.shape[1]
+        n = grad_host.shape[2]
+        dev = self.device
+        cur = torch.cuda.current_stream(dev)
+        for s in (self.s_in, self.s_comp, self.s_out):
+            s.wait_stream(cur)
+        bounds = [(B * c // self.chunks, B * (c + 1) // self.chunks) for c in range(self.chunks)]
+        d_tw_total = None
+        keep = []  # device tensors stay referenced until their stream is done
+        for lo, hi in bounds:
+            if hi == lo:
+                continue
+            with torch.cuda.stream(self.s_in):
+                xd = x_host[lo:hi].to(dev, non_blocking=True)
+                gd = grad_host[lo:hi].to(dev, non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(self.s_in)
+            with torch.cuda.stream(self.s_comp):
+                self.s_comp.wait_event(ev_in)
+                xd.record_stream(self.s_comp)
+                gd.record_stream(self.s_comp)
+                xr = xd.expand(hi - lo, S, n) if xd.shape[1] != S else xd
+                y = butterfly_multiply_fw(twiddle, xr, increasing_stride)
+                d_tw, d_x = butterfly_multiply_bw(twiddle, xr, gd, increasing_stride)
+                d_tw_total = d_tw if d_tw_total is None else d_tw_total.add_(d_tw)
+                ev_c = torch.cuda.Event()
+                ev_c.record(self.s_comp)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_c)
+                y.record_stream(self.s_out)
+                d_x.record_stream(self.s_out)
+                out_host[lo:hi].copy_(y, non_blocking=True)
+                d_x_host[lo:hi].copy_(d_x[:, :, :d_x_host.shape[2]], non_blocking=True)
+            keep.append((xd, gd, y, d_x))
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_stream(self.s_comp)
+            if d_tw_total is not None:
+                d_tw_total.record_stream(self.s_out)
+                d_twiddle_host.copy_(d_tw_total, non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_comp)
+        return d_tw_total

@@ -68,9 +68,9 @@ struct EmulExec {
           tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, re, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG.data(), tid, nthr);
         }
         for (int j = 0; j + 1 < p.nsg; ++j)
-          for (int tid = 0; tid < nthr; ++tid) bw_sg_step<T, KW, NSG, 0, 0, true>(p, st[tid], j, smX.data(), smG.data(), R, tid, nthr);
+          for (int tid = 0; tid < nthr; ++tid) bw_sg_step<T, KW, NSG, 0, 0, true>(p, st[tid], j, stack, smX.data(), smG.data(), R, tid, nthr);
         for (int j = p.nsg - 1; j >= 0; --j)
-          for (int tid = 0; tid < nthr; ++tid) bw_sg_step<T, KW, NSG, 0, 0, false>(p, st[tid], j, smX.data(), smG.data(), R, tid, nthr);
+          for (int tid = 0; tid < nthr; ++tid) bw_sg_step<T, KW, NSG, 0, 0, false>(p, st[tid], j, stack, smX.data(), smG.data(), R, tid, nthr);
         for (int tid = 0; tid < nthr; ++tid)
           tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, re, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG.data(), tid, nthr);
       }
