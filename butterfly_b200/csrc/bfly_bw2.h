@@ -1,0 +1,287 @@
+// Backward phase, second generation: the same twiddle-stationary-accumulator scheme as
+// bfly_core.h's backward, restructured so that two CTAs share an SM.
+//
+//  * The twiddles and the gradient accumulators of all sub-groups (up to four) do not live in
+//    registers: each thread keeps them in its private slice of TENSOR MEMORY (TMEM, 256 KB per
+//    SM on sm_100, otherwise unused by this library) and pulls the 16 twiddles and 16
+//    accumulators of the sub-group it is working on into registers with one tcgen05.ld each,
+//    pushing the accumulators back with one tcgen05.st.  That cuts the register need to under
+//    100 per thread and keeps the twiddles one short hop away (no L2 latency per step).
+//  * Sub-group steps are a runtime loop over one generic routine per stage pattern (no
+//    per-sub-group code copies): the hot code is a few KB.
+//  * A batch is four rows, all in flight per thread (no row loop); the two CTAs of an SM
+//    overlap each other's load / barrier / store latencies.
+//
+// On the host (test emulator) the accumulator store is a plain array.
+#pragma once
+#include "bfly_core.h"
+
+namespace bfly {
+
+constexpr int kBw2Rows = 4;  // rows per batch
+
+// ---------------------------------------------------------------- accumulator store
+template <typename T, int KW> struct AccStore {
+  static constexpr int N = BwTwn<KW>::value;               // accumulators (elements of T) per sub-group
+  static constexpr int NF = N * (int)(sizeof(T) / 4);      // 32-bit columns per sub-group
+  // a thread's 128 columns: accumulators of sub-group j at j * NF, its twiddles at kTwBase + j * NF
+  static constexpr int kTwBase = 64;
+#if defined(__CUDA_ARCH__)
+  uint32_t taddr;  // TMEM address (lane << 16 | column) of this thread's first column
+  __device__ __forceinline__ void ld_tw(int j, T* tw) const { ld_at(kTwBase + j * NF, tw); }
+  __device__ __forceinline__ void st_tw(int j, const T* tw) const { st_at(kTwBase + j * NF, tw); }
+  __device__ __forceinline__ void ld(int j, T* acc) const { ld_at(j * NF, acc); }
+  __device__ __forceinline__ void st(int j, const T* acc) const { st_at(j * NF, acc); }
+  __device__ __forceinline__ void ld_at(int col, T* acc) const {
+    float* r = reinterpret_cast<float*>(acc);
+    const uint32_t a = taddr + (uint32_t)col;
+    if constexpr (NF == 16) {
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+          : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]),
+            "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15])
+          : "r"(a) : "memory");
+    } else if constexpr (NF == 8) {
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7])
+                   : "r"(a) : "memory");
+    } else {
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]) : "r"(a) : "memory");
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  }
+  __device__ __forceinline__ void st_at(int col, const T* acc) const {
+    const float* r = reinterpret_cast<const float*>(acc);
+    const uint32_t a = taddr + (uint32_t)col;
+    if constexpr (NF == 16) {
+      asm volatile(
+          "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+          ::"r"(a), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]), "f"(r[8]), "f"(r[9]),
+            "f"(r[10]), "f"(r[11]), "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15]) : "memory");
+    } else if constexpr (NF == 8) {
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                   ::"r"(a), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]) : "memory");
+    } else {
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                   ::"r"(a), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]) : "memory");
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  }
+#else
+  T* mem;  // 2 * kMaxSg * N elements: accumulators, then twiddles
+  void ld(int j, T* acc) const { for (int e = 0; e < N; ++e) acc[e] = mem[j * N + e]; }
+  void st(int j, const T* acc) const { for (int e = 0; e < N; ++e) mem[j * N + e] = acc[e]; }
+  void ld_tw(int j, T* tw) const { for (int e = 0; e < N; ++e) tw[e] = mem[(kMaxSg + j) * N + e]; }
+  void st_tw(int j, const T* tw) const { for (int e = 0; e < N; ++e) mem[(kMaxSg + j) * N + e] = tw[e]; }
+#endif
+};
+
+// Per-thread, per-sub-group constants kept in shared memory: meta[(j * 3 + k) * nthr + tid],
+// k = 0: swizzled tile index of the unit, k = 1, 2: element offsets of the unit's twiddles.
+constexpr int kBw2Meta = 3;
+
+template <typename T, int KW>
+BFLY_HD void bw2_build_meta(const BwParams<T>& p, uint32_t* meta, int pbase, int tid, int nthr) {
+  for (int j = 0; j < p.nsg; ++j) {
+    const BwSg& sg = p.sg[j];
+    const int lbase = deposit_unit(tid, sg.ubit, sg.nubits);
+    const int col0 = p.panel.col(pbase, lbase);
+    const int wg = p.panel.global_bit(sg.lbit);
+    uint32_t t0 = 0, t1 = 0;
+    if (sg.radix == 4) {
+      t0 = sg.tw_off[0] + (uint32_t)delete_2bits(col0, wg) * 16u;
+    } else {
+      t0 = sg.tw_off[0] + (uint32_t)delete_bit(col0, wg + sg.q[0]) * 4u;
+      if (KW > 1 && sg.nst > 1) t1 = sg.tw_off[1] + (uint32_t)delete_bit(col0, wg + sg.q[1]) * 4u;
+    }
+    meta[(j * kBw2Meta + 0) * nthr + tid] = (uint32_t)swzT<T>(lbase);
+    meta[(j * kBw2Meta + 1) * nthr + tid] = t0;
+    meta[(j * kBw2Meta + 2) * nthr + tid] = t1;
+  }
+}
+
+// Twiddles of sub-group j for this thread's unit, from global memory (L2).
+template <typename T, int KW>
+BFLY_HD void bw2_fetch_tw(const BwParams<T>& p, const uint32_t* meta, int j, int stack, int tid, int nthr, T* dst) {
+  const BwSg& sg = p.sg[j];
+  const T* twp = p.tw[sg.which] + (int64_t)stack * p.tw_stack[sg.which];
+  const uint32_t t0 = meta[(j * kBw2Meta + 1) * nthr + tid];
+  if (sg.radix == 4) {
+    if constexpr (KW == 2) load_tw<T, 16>(dst, twp + t0);
+  } else {
+    const int wg = p.panel.global_bit(sg.lbit);
+#pragma unroll
+    for (int pp = 0; pp < (1 << (KW - 1)); ++pp) load_tw<T, 4>(dst + pp * 4, twp + t0 + (uint32_t)((pp << wg) * 4));
+    if constexpr (KW > 1) {
+      if (sg.nst > 1) {
+        const uint32_t t1 = meta[(j * kBw2Meta + 2) * nthr + tid];
+#pragma unroll
+        for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
+          load_tw<T, 4>(dst + (1 << (KW - 1)) * 4 + pp * 4, twp + t1 + (uint32_t)((pp << wg) * 4));
+      }
+    }
+  }
+}
+
+// One sub-group step over the four rows of a batch.
+//   FORWARD: snapshot j -> stages -> snapshot j+1.   else: accumulate and propagate the gradient.
+template <typename T, int KW, int LOGC, int PATID, bool VEC, bool FORWARD>
+BFLY_HD void bw2_rows(const BwParams<T>& p, int j, const T* tw, T* acc, int a0, T* __restrict__ smX, T* __restrict__ smG) {
+  constexpr int E = 1 << KW;
+  constexpr int SZ = (int)sizeof(T);
+  constexpr int R = kBw2Rows;
+  constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;
+  const BwSg& sg = p.sg[j];
+  const int C = LOGC > 0 ? (1 << LOGC) : (1 << p.panel.logC);
+  int off[E];
+#pragma unroll
+  for (int m = 0; m < E; ++m) off[m] = (a0 ^ sg.d[m]) * SZ;
+  const smaddr_t src = sm_addr(smX) + (smaddr_t)(j * R * C * SZ);
+  if constexpr (FORWARD) {
+    const smaddr_t dst = src + (smaddr_t)(R * C * SZ);
+    T v[R][E];
+    static_for<0, R>([&](auto rc) {
+      constexpr int r = decltype(rc)::value;
+      bw_unit_ld<T, KW, VEC, r * ROWB>(src + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, v[r]);
+    });
+    static_for<0, R>([&](auto rc) {
+      constexpr int r = decltype(rc)::value;
+      bw_apply_fw<T, KW, PATID>(v[r], tw);
+      bw_unit_st<T, KW, VEC, r * ROWB>(dst + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, v[r]);
+    });
+  } else {
+    const smaddr_t gb = sm_addr(smG);
+    // two rows at a time: x, g and the recomputed intermediate of four rows would not fit the
+    // register budget of two CTAs per SM
+    static_for<0, R / 2>([&](auto hc) {
+      constexpr int h = decltype(hc)::value * 2;
+      T x[2][E], g[2][E];
+      static_for<0, 2>([&](auto rc) {
+        constexpr int r = h + decltype(rc)::value;
+        bw_unit_ld<T, KW, VEC, r * ROWB>(src + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, x[r - h]);
+        bw_unit_ld<T, KW, VEC, r * ROWB>(gb + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, g[r - h]);
+      });
+      static_for<0, 2>([&](auto rc) {
+        constexpr int r = h + decltype(rc)::value;
+        bw_apply_bw<T, KW, PATID>(g[r - h], x[r - h], tw, acc);
+        bw_unit_st<T, KW, VEC, r * ROWB>(gb + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, g[r - h]);
+      });
+    });
+  }
+}
+
+template <typename T, int KW, int LOGC, bool FORWARD>
+BFLY_HD void bw2_step(const BwParams<T>& p, int j, const T* tw, T* acc, int a0, T* smX, T* smG) {
+  const BwSg& sg = p.sg[j];
+  const int pat = bw_pattern(sg, KW);
+  const bool vec = sg.vec != 0;
+  auto run = [&](auto pc, auto vc) {
+    bw2_rows<T, KW, LOGC, decltype(pc)::value, decltype(vc)::value, FORWARD>(p, j, tw, acc, a0, smX, smG);
+  };
+  auto with_vec = [&](auto pc) {
+    if (vec) run(pc, std::true_type{});
+    else run(pc, std::false_type{});
+  };
+  if constexpr (KW == 1) {
+    with_vec(std::integral_constant<int, 0>{});
+  } else {
+    switch (pat) {
+      case 0: with_vec(std::integral_constant<int, 0>{}); break;
+      case 1: with_vec(std::integral_constant<int, 1>{}); break;
+      case 2: with_vec(std::integral_constant<int, 2>{}); break;
+      case 3: with_vec(std::integral_constant<int, 3>{}); break;
+      case 4: with_vec(std::integral_constant<int, 4>{}); break;
+      case 5: with_vec(std::integral_constant<int, 5>{}); break;
+      default: with_vec(std::integral_constant<int, 6>{}); break;
+    }
+  }
+}
+
+// One forward-recompute step (sub-group j, 0 <= j <= nsg-2) of a batch for one thread.  A
+// block-wide barrier must follow.
+template <typename T, int KW, int LOGC>
+BFLY_HD void bw2_fw_step(const BwParams<T>& p, const AccStore<T, KW>& accs, const uint32_t* meta, int j, T* smX,
+                         T* smG, int tid, int nthr) {
+  constexpr int N = BwTwn<KW>::value;
+  T tw[N];
+  accs.ld_tw(j, tw);
+  const int a0 = (int)meta[(j * kBw2Meta + 0) * nthr + tid];
+  bw2_step<T, KW, LOGC, true>(p, j, tw, (T*)nullptr, a0, smX, smG);
+}
+
+// One reverse step (sub-group j, nsg-1 >= j >= 0).  A block-wide barrier must follow.
+template <typename T, int KW, int LOGC>
+BFLY_HD void bw2_bw_step(const BwParams<T>& p, const AccStore<T, KW>& accs, const uint32_t* meta, int j, T* smX,
+                         T* smG, int tid, int nthr) {
+  constexpr int N = BwTwn<KW>::value;
+  T tw[N], acc[N];
+  accs.ld_tw(j, tw);
+  accs.ld(j, acc);
+  const int a0 = (int)meta[(j * kBw2Meta + 0) * nthr + tid];
+  bw2_step<T, KW, LOGC, false>(p, j, tw, acc, a0, smX, smG);
+  accs.st(j, acc);
+}
+
+// Per-thread set-up: zero accumulators, and the twiddles of the thread's unit in every sub-group
+// from global memory into the private store (they stay there for the life of the CTA).
+template <typename T, int KW>
+BFLY_HD void bw2_init(const BwParams<T>& p, const AccStore<T, KW>& accs, const uint32_t* meta, int stack, int tid,
+                      int nthr) {
+  constexpr int N = BwTwn<KW>::value;
+  T z[N];
+#pragma unroll
+  for (int e = 0; e < N; ++e) z[e] = Ops<T>::zero();
+  for (int j = 0; j < p.nsg; ++j) {
+    T tw[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) tw[e] = Ops<T>::zero();
+    bw2_fetch_tw<T, KW>(p, meta, j, stack, tid, nthr, tw);
+    accs.st_tw(j, tw);
+    accs.st(j, z);
+  }
+}
+
+// Add this thread's accumulators to d_twiddle.
+template <typename T, int KW>
+BFLY_HD void bw2_flush(const BwParams<T>& p, const AccStore<T, KW>& accs, const uint32_t* meta, int stack, int tid,
+                       int nthr) {
+  constexpr int N = BwTwn<KW>::value;
+  for (int j = 0; j < p.nsg; ++j) {
+    const BwSg& sg = p.sg[j];
+    T acc[N];
+    accs.ld(j, acc);
+    T* dtw = p.dtw[sg.which] + (int64_t)stack * p.tw_stack[sg.which];
+    const uint32_t t0 = meta[(j * kBw2Meta + 1) * nthr + tid];
+    if (sg.radix == 4) {
+      if constexpr (KW == 2) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) atomic_add_el(dtw + t0 + e, acc[e]);
+      }
+    } else {
+      const int wg = p.panel.global_bit(sg.lbit);
+      const uint32_t t1 = meta[(j * kBw2Meta + 2) * nthr + tid];
+#pragma unroll
+      for (int s = 0; s < KW; ++s) {
+        if (s < sg.nst) {
+#pragma unroll
+          for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              atomic_add_el(dtw + (s == 0 ? t0 : t1) + (uint32_t)((pp << wg) * 4) + e,
+                            acc[s * (1 << (KW - 1)) * 4 + pp * 4 + e]);
+        }
+      }
+    }
+  }
+}
+
+// shared memory of one CTA: (nsg + 1) tiles of four rows, then the meta table
+template <typename T> BFLY_HD size_t bw2_tile_bytes(const BwParams<T>& p) {
+  return ((size_t)(p.nsg + 1) * kBw2Rows * sizeof(T)) << p.panel.logC;
+}
+template <typename T> BFLY_HD size_t bw2_smem_bytes(const BwParams<T>& p, int nthr) {
+  return bw2_tile_bytes(p) + (size_t)p.nsg * kBw2Meta * nthr * sizeof(uint32_t);
+}
+
+}  // namespace bfly

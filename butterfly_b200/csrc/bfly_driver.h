@@ -3,6 +3,7 @@
 //
 // Executor concept (E):
 //   int  num_sms() const;
+//   bool has_bw2(size_t elem_size, int kw) const;          // second-generation backward kernel available
 //   int  threads() const;                                  // threads per CTA of its kernels
 //   int  run_fw(const FwParams<T>&);                       // one forward launch
 //   int  run_bw(const BwParams<T>&, int KW);               // one backward-phase launch
@@ -23,11 +24,11 @@ template <> struct KernelCfg<float> {
   static int bw_kw(int log_n) { return log_n >= 2 ? 2 : 1; }
   static int bw_max_sg(int kw) {
     if (kw != 2) return 10;
-    if (const char* e = std::getenv("BFLY_BW_MAXSG")) {  // experiments: shorter phases
+    if (const char* e = std::getenv("BFLY_BW_MAXSG")) {  // experiments: other phase lengths
       const int v = std::atoi(e);
       if (v >= 1 && v <= 5) return v;
     }
-    return 5;
+    return 4;  // 8 stages per phase: twiddles and accumulators of 4 sub-groups fill a thread's 128 TMEM columns
   }
 };
 template <> struct KernelCfg<cf> {
@@ -239,6 +240,11 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     p.nsg = P.nsg;
     for (int j = 0; j < P.nsg; ++j) p.sg[j] = P.sg[j];
     const size_t row_bytes = (size_t)(P.nsg + 1) * sizeof(T) << P.panel.logC;
+    const int U = (1 << P.panel.logC) >> lay.kw;
+    // second-generation kernel: full panels (one unit per thread), four-row batches, two CTAs per SM
+    const size_t v2_bytes = 4 * row_bytes + (size_t)P.nsg * 3 * KernelCfg<T>::kThreads * sizeof(uint32_t) + 16;
+    p.v2 = ex.has_bw2(sizeof(T), lay.kw) && P.nsg <= 4 && U == KernelCfg<T>::kThreads && v2_bytes <= (size_t)(228 * 1024) / 2 - 1024 &&
+           q.B >= 4;
     int Rb = (int)(kSmemMax / row_bytes);
     if (const char* e = std::getenv("BFLY_BW_ROWS")) {  // experiments: rows per batch
       const int v = std::atoi(e);
@@ -249,13 +255,13 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     if (Rb >= 4) Rb &= ~3;       // batch heights in multiples of four: the kernels keep four rows in flight
     else if (Rb > 2) Rb &= ~1;
     // rows that run in parallel inside a CTA when the panel has fewer units than threads
-    const int U = (1 << P.panel.logC) >> lay.kw;
     const int par = U >= KernelCfg<T>::kThreads ? 1 : KernelCfg<T>::kThreads / std::max(U, 1);
     if (Rb < par && (size_t)par * row_bytes <= (size_t)kSmemMax) Rb = par;
     if (Rb > q.B && q.B < 8) Rb = std::max(q.B, 1);  // tiny batches; otherwise rows past the batch are zero rows
+    if (p.v2) Rb = 4;
     p.Rb = Rb;
     const int groups = (1 << P.panel.npanels_log) * q.S;
-    int nslices = std::max(1, ex.num_sms() / groups);
+    int nslices = std::max(1, (p.v2 ? 2 : 1) * ex.num_sms() / groups);
     int rows = (q.B + nslices - 1) / nslices;
     rows = (rows + Rb - 1) / Rb * Rb;
     nslices = (q.B + rows - 1) / rows;

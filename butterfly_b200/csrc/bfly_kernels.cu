@@ -15,11 +15,13 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
 #include "../../include/bfly.h"
 #include "bfly_core.h"
+#include "bfly_bw2.h"
 #include "bfly_driver.h"
 
 namespace bfly {
@@ -107,6 +109,63 @@ __global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks)) bfl
   bw_flush_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
 }
 
+// Second-generation backward phase (bfly_bw2.h): accumulators in tensor memory, four-row
+// batches, two CTAs per SM.  Each CTA allocates 256 TMEM columns (two CTAs fill the SM's 512):
+// a thread owns the lane (32 * (warp % 4) + lane-in-warp) and, within it, the 128-column range
+// picked by warp / 4: 64 columns of accumulators and 64 of twiddles (4 sub-groups x 16).
+constexpr int kBw2TmemCols = 256;
+
+template <typename T, int KW, int LOGC>
+__global__ void __launch_bounds__(kThreads, 2) bfly_bw2_kernel(const __grid_constant__ BwParams<T> p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* smX = reinterpret_cast<T*>(smem_raw);
+  const int C = 1 << p.panel.logC;
+  T* smG = smX + (size_t)p.nsg * kBw2Rows * C;
+  uint32_t* meta = reinterpret_cast<uint32_t*>(smem_raw + bw2_tile_bytes(p));
+  uint32_t* tmem_slot = meta + (size_t)p.nsg * kBw2Meta * kThreads;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  int pbase, stack, row_begin, row_end;
+  bw_cta_coords(p, blockIdx.x, pbase, stack, row_begin, row_end);
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_addr(tmem_slot)), "r"(kBw2TmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  bw2_build_meta<T, KW>(p, meta, pbase, tid, kThreads);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  AccStore<T, KW> accs;
+  accs.taddr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)((warp >> 2) * 128);
+
+  bw2_init<T, KW>(p, accs, meta, stack, tid, kThreads);
+
+  for (int row0 = row_begin; row0 < row_end; row0 += kBw2Rows) {
+    tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
+    tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
+    tile_load_wait();
+    __syncthreads();
+    for (int j = 0; j + 1 < p.nsg; ++j) {
+      bw2_fw_step<T, KW, LOGC>(p, accs, meta, j, smX, smG, tid, kThreads);
+      __syncthreads();
+    }
+    for (int j = p.nsg - 1; j >= 0; --j) {
+      bw2_bw_step<T, KW, LOGC>(p, accs, meta, j, smX, smG, tid, kThreads);
+      __syncthreads();
+    }
+    tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
+    __syncthreads();
+  }
+  bw2_flush<T, KW>(p, accs, meta, stack, tid, kThreads);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBw2TmemCols) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ launch side
 
 static std::atomic<int64_t> g_launches{0};
@@ -184,6 +243,22 @@ struct CudaExec {
   DeviceInfo dev;
   int num_sms() const { return dev.sms; }
   int threads() const { return kThreads; }
+  bool has_bw2(size_t elem_size, int kw) const {
+    if (const char* e = std::getenv("BFLY_BW_V2")) return std::atoi(e) != 0 && elem_size == 4 && kw == 2;
+    return elem_size == 4 && kw == 2;
+  }
+
+  template <typename T, int KW, int LOGC> int launch_bw2(const BwParams<T>& p) {
+    const size_t smem = bw2_smem_bytes(p, kThreads) + 16;
+    int rc = set_smem(bfly_bw2_kernel<T, KW, LOGC>, smem);
+    if (rc) return rc;
+    {
+      ProfileScope prof(kKernBw, stream);
+      bfly_bw2_kernel<T, KW, LOGC><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+    }
+    g_launches.fetch_add(1);
+    return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+  }
 
   template <typename T, int KMAX, int LOGC, int ROWS> int launch_fw(const FwParams<T>& p) {
     const size_t smem = fw_smem_bytes(p, kThreads);
@@ -229,6 +304,7 @@ struct CudaExec {
   // Instances with the panel shape fixed at compile time cover full 1024-column float panels
   // (512-column complex panels) with the batch heights the planner picks; the rest is generic.
   int run_bw(const BwParams<float>& p, int KW) {
+    if (p.v2 && KW == 2) return p.panel.logC == 10 ? launch_bw2<float, 2, 10>(p) : launch_bw2<float, 2, 0>(p);
     if (KW == 2) {
       if (p.panel.logC == 10) {
         if (p.nsg >= 4 && p.Rb == 8) return launch_bw<float, 2, 5, 10, 8>(p);

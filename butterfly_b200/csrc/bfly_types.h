@@ -211,6 +211,7 @@ template <typename T> struct BwParams {
   const T* gin;  int64_t gin_sB, gin_sS;   int gin_cols;   // gradient leaving the phase (zero beyond)
   T* gout;       int64_t gout_sB, gout_sS; int gout_cols;  // gradient entering the phase
   int B, S, log_n;
+  int v2;            // run the two-CTAs-per-SM kernel (accumulators in tensor memory, 4-row batches)
   int Rb;            // rows per batch held in shared memory
   int rows_per_cta;  // rows of one row slice (multiple of Rb)
   int nslices;

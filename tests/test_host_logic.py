@@ -119,12 +119,13 @@ def test_stack_broadcast_and_ragged_slices(emul, oracle_mod):
 
 def test_backward_phase_plan_sizes(emul):
     ws = ctypes.c_int64(0)
-    # one phase (no scratch) while all stages fit one panel of 1024 columns
-    assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 10, 1, 1, ctypes.byref(ws)) == 1 and ws.value == 0
-    # n = 4096, two blocks: three phases -> two (B,S,n) float snapshots
+    # float: a phase holds at most 8 stages (4 sub-groups of 2) on a panel of 1024 columns
+    assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 8, 1, 1, ctypes.byref(ws)) == 1 and ws.value == 0
+    assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 10, 1, 1, ctypes.byref(ws)) == 2 and ws.value == 64 * 1024 * 4
+    # n = 4096, two blocks: 24 stages = three phases of 8 -> two (B,S,n) float snapshots
     assert emul.bfly_emul_bw_plan(0, 0, 16384, 1, 12, 2, 1, ctypes.byref(ws)) == 3
     assert ws.value == 2 * 16384 * 4096 * 4
-    # complex: panels of 512 columns
+    # complex: panels of 512 columns, up to 10 stages per phase
     nph = emul.bfly_emul_bw_plan(1, 0, 8192, 1, 11, 1, 1, ctypes.byref(ws))
     assert nph == 2 and ws.value == 8192 * 2048 * 8
 
