@@ -20,6 +20,7 @@ SYMBOLS = (
     "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
+    "bfly_device_error",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -198,6 +199,14 @@ def bw_base4(twiddle4, twiddle2, x, grad, increasing_stride=True, workspace=None
 
 def launch_count():
     return int(lib().bfly_launch_count())
+
+
+def device_error():
+    """1 if a kernel gave up on a bounded wait since the last call (its output is invalid), else 0."""
+    rc = int(lib().bfly_device_error())
+    if rc < 0:
+        raise BflyError(rc, "bfly_device_error")
+    return rc
 
 
 KERNEL_NAMES = ("bfly_fw_kernel", "bfly_bw_kernel")

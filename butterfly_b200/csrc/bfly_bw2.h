@@ -77,12 +77,21 @@ template <typename T, int KW> struct AccStore {
 #endif
 };
 
-// Per-thread, per-sub-group constants kept in shared memory: meta[(j * 3 + k) * nthr + tid],
-// k = 0: swizzled tile index of the unit, k = 1, 2: element offsets of the unit's twiddles.
-constexpr int kBw2Meta = 3;
+// Per-thread, per-sub-group constants kept in shared memory (kBw2Meta 32-bit words per thread
+// and sub-group):
+//   meta[(j * nthr + tid) * 4 + m], m = 0..3: byte offset, from the start of the first snapshot
+//     tile, of element m of the thread's unit in row 0 of snapshot tile j (swizzle applied); a
+//     step fetches the four with one 16-byte load;
+//   meta[nsg * nthr * 4 + (j * 2 + k) * nthr + tid], k = 0, 1: element offsets of the unit's
+//     twiddles (used when the twiddles are fetched and when the accumulators are flushed).
+constexpr int kBw2Meta = 6;
 
 template <typename T, int KW>
 BFLY_HD void bw2_build_meta(const BwParams<T>& p, uint32_t* meta, int pbase, int tid, int nthr) {
+  constexpr int E = 1 << KW;
+  constexpr int SZ = (int)sizeof(T);
+  const int C = 1 << p.panel.logC;
+  uint32_t* tws = meta + (size_t)p.nsg * nthr * 4;
   for (int j = 0; j < p.nsg; ++j) {
     const BwSg& sg = p.sg[j];
     const int lbase = deposit_unit(tid, sg.ubit, sg.nubits);
@@ -95,9 +104,11 @@ BFLY_HD void bw2_build_meta(const BwParams<T>& p, uint32_t* meta, int pbase, int
       t0 = sg.tw_off[0] + (uint32_t)delete_bit(col0, wg + sg.q[0]) * 4u;
       if (KW > 1 && sg.nst > 1) t1 = sg.tw_off[1] + (uint32_t)delete_bit(col0, wg + sg.q[1]) * 4u;
     }
-    meta[(j * kBw2Meta + 0) * nthr + tid] = (uint32_t)swzT<T>(lbase);
-    meta[(j * kBw2Meta + 1) * nthr + tid] = t0;
-    meta[(j * kBw2Meta + 2) * nthr + tid] = t1;
+    const int a0 = swzT<T>(lbase);
+    for (int m = 0; m < 4; ++m)
+      meta[(j * nthr + tid) * 4 + m] = m < E ? (uint32_t)(((a0 ^ sg.d[m]) + j * kBw2Rows * C) * SZ) : 0u;
+    tws[(j * 2 + 0) * nthr + tid] = t0;
+    tws[(j * 2 + 1) * nthr + tid] = t1;
   }
 }
 
@@ -105,8 +116,9 @@ BFLY_HD void bw2_build_meta(const BwParams<T>& p, uint32_t* meta, int pbase, int
 template <typename T, int KW>
 BFLY_HD void bw2_fetch_tw(const BwParams<T>& p, const uint32_t* meta, int j, int stack, int tid, int nthr, T* dst) {
   const BwSg& sg = p.sg[j];
+  const uint32_t* tws = meta + (size_t)p.nsg * nthr * 4;
   const T* twp = p.tw[sg.which] + (int64_t)stack * p.tw_stack[sg.which];
-  const uint32_t t0 = meta[(j * kBw2Meta + 1) * nthr + tid];
+  const uint32_t t0 = tws[(j * 2 + 0) * nthr + tid];
   if (sg.radix == 4) {
     if constexpr (KW == 2) load_tw<T, 16>(dst, twp + t0);
   } else {
@@ -115,7 +127,7 @@ BFLY_HD void bw2_fetch_tw(const BwParams<T>& p, const uint32_t* meta, int j, int
     for (int pp = 0; pp < (1 << (KW - 1)); ++pp) load_tw<T, 4>(dst + pp * 4, twp + t0 + (uint32_t)((pp << wg) * 4));
     if constexpr (KW > 1) {
       if (sg.nst > 1) {
-        const uint32_t t1 = meta[(j * kBw2Meta + 2) * nthr + tid];
+        const uint32_t t1 = tws[(j * 2 + 1) * nthr + tid];
 #pragma unroll
         for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
           load_tw<T, 4>(dst + (1 << (KW - 1)) * 4 + pp * 4, twp + t1 + (uint32_t)((pp << wg) * 4));
@@ -124,34 +136,68 @@ BFLY_HD void bw2_fetch_tw(const BwParams<T>& p, const uint32_t* meta, int j, int
   }
 }
 
+// Load / store the thread's unit of one tile row: a[m] are the addresses of its elements in
+// row 0 of the tile (only a[0] is used on the 16-byte path), IMM the row's byte offset.
+template <typename T, int KW, bool VEC, int IMM>
+BFLY_HD void bw2_unit_ld(const smaddr_t* a, smaddr_t ro, T* v) {
+  constexpr int E = 1 << KW;
+  constexpr int V = Vec16<T>::N;
+  if constexpr (VEC && E >= V) {
+#pragma unroll
+    for (int h = 0; h < E / V; ++h) sm_ld16<IMM>(a[h * V] + ro, v + h * V);
+  } else {
+#pragma unroll
+    for (int m = 0; m < E; ++m) sm_ld<IMM>(a[m] + ro, v[m]);
+  }
+}
+template <typename T, int KW, bool VEC, int IMM>
+BFLY_HD void bw2_unit_st(const smaddr_t* a, smaddr_t ro, const T* v) {
+  constexpr int E = 1 << KW;
+  constexpr int V = Vec16<T>::N;
+  if constexpr (VEC && E >= V) {
+#pragma unroll
+    for (int h = 0; h < E / V; ++h) sm_st16<IMM>(a[h * V] + ro, v + h * V);
+  } else {
+#pragma unroll
+    for (int m = 0; m < E; ++m) sm_st<IMM>(a[m] + ro, v[m]);
+  }
+}
+
 // One sub-group step over the four rows of a batch.
 //   FORWARD: snapshot j -> stages -> snapshot j+1.   else: accumulate and propagate the gradient.
+// o[m]: byte offsets of the unit's elements from the start of the first snapshot tile.
 template <typename T, int KW, int LOGC, int PATID, bool VEC, bool FORWARD>
-BFLY_HD void bw2_rows(const BwParams<T>& p, int j, const T* tw, T* acc, int a0, T* __restrict__ smX, T* __restrict__ smG) {
+BFLY_HD void bw2_rows(const BwParams<T>& p, int j, const T* tw, T* acc, const uint32_t* o, T* __restrict__ smX,
+                      T* __restrict__ smG) {
   constexpr int E = 1 << KW;
   constexpr int SZ = (int)sizeof(T);
   constexpr int R = kBw2Rows;
-  constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;
-  const BwSg& sg = p.sg[j];
+  constexpr int ROWB = LOGC > 0 ? (SZ << LOGC) : 0;   // compile-time row pitch
+  constexpr int TILEB = LOGC > 0 ? R * ROWB : 0;      // compile-time tile pitch
   const int C = LOGC > 0 ? (1 << LOGC) : (1 << p.panel.logC);
-  int off[E];
+  const smaddr_t xb = sm_addr(smX);
+  smaddr_t ax[E];
 #pragma unroll
-  for (int m = 0; m < E; ++m) off[m] = (a0 ^ sg.d[m]) * SZ;
-  const smaddr_t src = sm_addr(smX) + (smaddr_t)(j * R * C * SZ);
+  for (int m = 0; m < E; ++m) ax[m] = xb + (smaddr_t)o[m];
+  auto rowoff = [&](int r) -> smaddr_t { return LOGC > 0 ? (smaddr_t)0 : (smaddr_t)((size_t)r * C * SZ); };
   if constexpr (FORWARD) {
-    const smaddr_t dst = src + (smaddr_t)(R * C * SZ);
+    const smaddr_t tileoff = LOGC > 0 ? (smaddr_t)0 : (smaddr_t)((size_t)R * C * SZ);
     T v[R][E];
     static_for<0, R>([&](auto rc) {
       constexpr int r = decltype(rc)::value;
-      bw_unit_ld<T, KW, VEC, r * ROWB>(src + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, v[r]);
+      bw2_unit_ld<T, KW, VEC, r * ROWB>(ax, rowoff(r), v[r]);
     });
     static_for<0, R>([&](auto rc) {
       constexpr int r = decltype(rc)::value;
       bw_apply_fw<T, KW, PATID>(v[r], tw);
-      bw_unit_st<T, KW, VEC, r * ROWB>(dst + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, v[r]);
+      bw2_unit_st<T, KW, VEC, TILEB + r * ROWB>(ax, tileoff + rowoff(r), v[r]);
     });
   } else {
-    const smaddr_t gb = sm_addr(smG);
+    // the gradient tile follows the nsg snapshot tiles
+    const smaddr_t gdelta = (smaddr_t)((size_t)(p.nsg - j) * R * C * SZ);
+    smaddr_t ag[E];
+#pragma unroll
+    for (int m = 0; m < E; ++m) ag[m] = ax[m] + gdelta;
     // two rows at a time: x, g and the recomputed intermediate of four rows would not fit the
     // register budget of two CTAs per SM
     static_for<0, R / 2>([&](auto hc) {
@@ -159,43 +205,50 @@ BFLY_HD void bw2_rows(const BwParams<T>& p, int j, const T* tw, T* acc, int a0, 
       T x[2][E], g[2][E];
       static_for<0, 2>([&](auto rc) {
         constexpr int r = h + decltype(rc)::value;
-        bw_unit_ld<T, KW, VEC, r * ROWB>(src + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, x[r - h]);
-        bw_unit_ld<T, KW, VEC, r * ROWB>(gb + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, g[r - h]);
+        bw2_unit_ld<T, KW, VEC, r * ROWB>(ax, rowoff(r), x[r - h]);
+        bw2_unit_ld<T, KW, VEC, r * ROWB>(ag, rowoff(r), g[r - h]);
       });
       static_for<0, 2>([&](auto rc) {
         constexpr int r = h + decltype(rc)::value;
         bw_apply_bw<T, KW, PATID>(g[r - h], x[r - h], tw, acc);
-        bw_unit_st<T, KW, VEC, r * ROWB>(gb + (LOGC > 0 ? 0 : (smaddr_t)(r * C * SZ)), off, g[r - h]);
+        bw2_unit_st<T, KW, VEC, r * ROWB>(ag, rowoff(r), g[r - h]);
       });
     });
   }
+  (void)smG;
 }
 
+// sg.kase: stage pattern and access width of a sub-group, resolved on the host:
+//   2 * pattern + vec, pattern as in bw_pattern().
 template <typename T, int KW, int LOGC, bool FORWARD>
-BFLY_HD void bw2_step(const BwParams<T>& p, int j, const T* tw, T* acc, int a0, T* smX, T* smG) {
+BFLY_HD void bw2_step(const BwParams<T>& p, int j, const T* tw, T* acc, const uint32_t* o, T* smX, T* smG) {
   const BwSg& sg = p.sg[j];
-  const int pat = bw_pattern(sg, KW);
-  const bool vec = sg.vec != 0;
-  auto run = [&](auto pc, auto vc) {
-    bw2_rows<T, KW, LOGC, decltype(pc)::value, decltype(vc)::value, FORWARD>(p, j, tw, acc, a0, smX, smG);
-  };
-  auto with_vec = [&](auto pc) {
-    if (vec) run(pc, std::true_type{});
-    else run(pc, std::false_type{});
-  };
+  const int kase = bw_pattern(sg, KW) * 2 + (sg.vec != 0 ? 1 : 0);
+#define BFLY_BW2_CASE(PAT)                                                                        \
+  case 2 * PAT: bw2_rows<T, KW, LOGC, PAT, false, FORWARD>(p, j, tw, acc, o, smX, smG); break;     \
+  case 2 * PAT + 1: bw2_rows<T, KW, LOGC, PAT, true, FORWARD>(p, j, tw, acc, o, smX, smG); break;
   if constexpr (KW == 1) {
-    with_vec(std::integral_constant<int, 0>{});
+    switch (kase) {
+      BFLY_BW2_CASE(0)
+      default: break;
+    }
   } else {
-    switch (pat) {
-      case 0: with_vec(std::integral_constant<int, 0>{}); break;
-      case 1: with_vec(std::integral_constant<int, 1>{}); break;
-      case 2: with_vec(std::integral_constant<int, 2>{}); break;
-      case 3: with_vec(std::integral_constant<int, 3>{}); break;
-      case 4: with_vec(std::integral_constant<int, 4>{}); break;
-      case 5: with_vec(std::integral_constant<int, 5>{}); break;
-      default: with_vec(std::integral_constant<int, 6>{}); break;
+    switch (kase) {
+      BFLY_BW2_CASE(0) BFLY_BW2_CASE(1) BFLY_BW2_CASE(2) BFLY_BW2_CASE(3) BFLY_BW2_CASE(4) BFLY_BW2_CASE(5)
+      BFLY_BW2_CASE(6)
+      default: break;
     }
   }
+#undef BFLY_BW2_CASE
+}
+
+BFLY_HD void bw2_load_offsets(const uint32_t* meta, int j, int tid, int nthr, uint32_t* o) {
+#if defined(__CUDA_ARCH__)
+  const uint4 q = reinterpret_cast<const uint4*>(meta)[j * nthr + tid];
+  o[0] = q.x; o[1] = q.y; o[2] = q.z; o[3] = q.w;
+#else
+  for (int m = 0; m < 4; ++m) o[m] = meta[(j * nthr + tid) * 4 + m];
+#endif
 }
 
 // One forward-recompute step (sub-group j, 0 <= j <= nsg-2) of a batch for one thread.  A
@@ -206,8 +259,9 @@ BFLY_HD void bw2_fw_step(const BwParams<T>& p, const AccStore<T, KW>& accs, cons
   constexpr int N = BwTwn<KW>::value;
   T tw[N];
   accs.ld_tw(j, tw);
-  const int a0 = (int)meta[(j * kBw2Meta + 0) * nthr + tid];
-  bw2_step<T, KW, LOGC, true>(p, j, tw, (T*)nullptr, a0, smX, smG);
+  uint32_t o[4];
+  bw2_load_offsets(meta, j, tid, nthr, o);
+  bw2_step<T, KW, LOGC, true>(p, j, tw, (T*)nullptr, o, smX, smG);
 }
 
 // One reverse step (sub-group j, nsg-1 >= j >= 0).  A block-wide barrier must follow.
@@ -218,8 +272,9 @@ BFLY_HD void bw2_bw_step(const BwParams<T>& p, const AccStore<T, KW>& accs, cons
   T tw[N], acc[N];
   accs.ld_tw(j, tw);
   accs.ld(j, acc);
-  const int a0 = (int)meta[(j * kBw2Meta + 0) * nthr + tid];
-  bw2_step<T, KW, LOGC, false>(p, j, tw, acc, a0, smX, smG);
+  uint32_t o[4];
+  bw2_load_offsets(meta, j, tid, nthr, o);
+  bw2_step<T, KW, LOGC, false>(p, j, tw, acc, o, smX, smG);
   accs.st(j, acc);
 }
 
@@ -252,7 +307,8 @@ BFLY_HD void bw2_flush(const BwParams<T>& p, const AccStore<T, KW>& accs, const 
     T acc[N];
     accs.ld(j, acc);
     T* dtw = p.dtw[sg.which] + (int64_t)stack * p.tw_stack[sg.which];
-    const uint32_t t0 = meta[(j * kBw2Meta + 1) * nthr + tid];
+    const uint32_t* tws = meta + (size_t)p.nsg * nthr * 4;
+    const uint32_t t0 = tws[(j * 2 + 0) * nthr + tid];
     if (sg.radix == 4) {
       if constexpr (KW == 2) {
 #pragma unroll
@@ -260,7 +316,7 @@ BFLY_HD void bw2_flush(const BwParams<T>& p, const AccStore<T, KW>& accs, const 
       }
     } else {
       const int wg = p.panel.global_bit(sg.lbit);
-      const uint32_t t1 = meta[(j * kBw2Meta + 2) * nthr + tid];
+      const uint32_t t1 = tws[(j * 2 + 1) * nthr + tid];
 #pragma unroll
       for (int s = 0; s < KW; ++s) {
         if (s < sg.nst) {

@@ -201,21 +201,103 @@ BFLY_HD void tile_store_chunks(T* __restrict__ dst, int64_t sB, int64_t sS, int 
   }
 }
 
+// Chunk copies of a tile whose R rows all exist (row0 + R <= B): the common case, written so
+// that one 16-byte move costs a handful of instructions (running pointers, no per-row range
+// checks; what lies right of the tensor's last column is zero-filled on load, skipped on store).
+template <typename T>
+BFLY_HD void tile_load_rows(const T* __restrict__ src, int64_t sB, int64_t sS, int ncols, int stack, int row0,
+                            int R, const Panel& pn, int pbase, T* __restrict__ sm, int tid, int nthr) {
+  constexpr int V = Vec16<T>::N;
+  constexpr int VL = Vec16<T>::LOG;
+  constexpr int SZ = (int)sizeof(T);
+  const int C = 1 << pn.logC;
+  const ChunkSplit cs = chunk_split(pn.logC - VL, tid, nthr);
+  const T* rowbase = src + (int64_t)stack * sS + (int64_t)(row0 + cs.r0) * sB;
+  const int64_t qstep = (int64_t)cs.rstep * sB;
+  const int dstep = cs.rstep * C;
+  for (int s = 0; s < cs.nslot; ++s) {
+    const int l = (cs.c0 + s * nthr) << VL;
+    const int col = pn.col(pbase, l);
+    int vcol = ncols - col;
+    vcol = vcol < 0 ? 0 : (vcol > V ? V : vcol);
+    const T* q = vcol ? rowbase + col : rowbase;
+    T* d = sm + swzT<T>(l) + cs.r0 * C;
+#if defined(__CUDA_ARCH__)
+    smaddr_t da = sm_addr(d);
+    const int bytes = vcol * SZ;
+#pragma unroll 2
+    for (int r = cs.r0; r < R; r += cs.rstep) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(da), "l"(q), "r"(bytes) : "memory");
+      q += qstep;
+      da += (smaddr_t)(dstep * SZ);
+    }
+#else
+    for (int r = cs.r0; r < R; r += cs.rstep) {
+      for (int i = 0; i < V; ++i) d[i] = i < vcol ? q[i] : Ops<T>::zero();
+      q += qstep;
+      d += dstep;
+    }
+#endif
+  }
+}
+
+template <typename T>
+BFLY_HD void tile_store_rows(T* __restrict__ dst, int64_t sB, int64_t sS, int ncols, int stack, int row0, int R,
+                             const Panel& pn, int pbase, const T* __restrict__ sm, int tid, int nthr) {
+  constexpr int V = Vec16<T>::N;
+  constexpr int VL = Vec16<T>::LOG;
+  const int C = 1 << pn.logC;
+  const ChunkSplit cs = chunk_split(pn.logC - VL, tid, nthr);
+  T* rowbase = dst + (int64_t)stack * sS + (int64_t)(row0 + cs.r0) * sB;
+  const int64_t qstep = (int64_t)cs.rstep * sB;
+  const int dstep = cs.rstep * C;
+  for (int s = 0; s < cs.nslot; ++s) {
+    const int l = (cs.c0 + s * nthr) << VL;
+    const int col = pn.col(pbase, l);
+    if (col >= ncols) continue;
+    T* q = rowbase + col;
+    const T* sp = sm + swzT<T>(l) + cs.r0 * C;
+    if (col + V <= ncols) {
+#pragma unroll 2
+      for (int r = cs.r0; r < R; r += cs.rstep) {
+#if defined(__CUDA_ARCH__)
+        *reinterpret_cast<float4*>(q) = *reinterpret_cast<const float4*>(sp);
+#else
+        for (int i = 0; i < V; ++i) q[i] = sp[i];
+#endif
+        q += qstep;
+        sp += dstep;
+      }
+    } else {
+      for (int r = cs.r0; r < R; r += cs.rstep) {
+        for (int i = 0; i < V; ++i)
+          if (col + i < ncols) q[i] = sp[i];
+        q += qstep;
+        sp += dstep;
+      }
+    }
+  }
+}
+
 template <typename T>
 BFLY_HD void tile_load_auto(const T* src, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0, int R,
                             const Panel& pn, int pbase, bool vec, T* sm, int tid, int nthr) {
-  if (vec && pn.lseg >= Vec16<T>::LOG)
-    tile_load_chunks<T>(src, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
-  else
+  if (vec && pn.lseg >= Vec16<T>::LOG) {
+    if (row0 + R <= B) tile_load_rows<T>(src, sB, sS, ncols, stack, row0, R, pn, pbase, sm, tid, nthr);
+    else tile_load_chunks<T>(src, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+  } else {
     tile_load<T>(src, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+  }
 }
 template <typename T>
 BFLY_HD void tile_store_auto(T* dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0, int R,
                              const Panel& pn, int pbase, bool vec, const T* sm, int tid, int nthr) {
-  if (vec && pn.lseg >= Vec16<T>::LOG)
-    tile_store_chunks<T>(dst, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
-  else
+  if (vec && pn.lseg >= Vec16<T>::LOG) {
+    if (row0 + R <= B) tile_store_rows<T>(dst, sB, sS, ncols, stack, row0, R, pn, pbase, sm, tid, nthr);
+    else tile_store_chunks<T>(dst, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+  } else {
     tile_store<T>(dst, sB, sS, ncols, B, stack, row0, R, pn, pbase, sm, tid, nthr);
+  }
 }
 
 // ------------------------------------------------------------------ butterfly stages on a register window

@@ -23,6 +23,7 @@
 #include "bfly_core.h"
 #include "bfly_bw2.h"
 #include "bfly_driver.h"
+#include "bfly_tma.h"
 
 namespace bfly {
 
@@ -115,14 +116,26 @@ __global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks)) bfl
 // picked by warp / 4: 64 columns of accumulators and 64 of twiddles (4 sub-groups x 16).
 constexpr int kBw2TmemCols = 256;
 
+// Set when a bounded wait inside a kernel ran out (the kernel then stops early and its output
+// is invalid); read and cleared by bfly_device_error().
+__device__ int g_device_error = 0;
+
+// Tile traffic goes through the TMA unit when the three tensors can be described to it
+// (p.tma; bfly_tma.h): thread 0 issues one bulk tensor load per tile and one bulk tensor store
+// per batch, everybody waits on an mbarrier.  Otherwise every thread copies 16-byte chunks.
 template <typename T, int KW, int LOGC>
-__global__ void __launch_bounds__(kThreads, 2) bfly_bw2_kernel(const __grid_constant__ BwParams<T> p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(kThreads, 2)
+bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ CUtensorMap map_x,
+                const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_o) {
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  // the swizzle of the TMA unit works on address bits: tiles start on a 1024-byte boundary
+  unsigned char* smem_raw = smem_dyn + ((1024u - (tma_smem(smem_dyn) & 1023u)) & 1023u);
   T* smX = reinterpret_cast<T*>(smem_raw);
   const int C = 1 << p.panel.logC;
   T* smG = smX + (size_t)p.nsg * kBw2Rows * C;
   uint32_t* meta = reinterpret_cast<uint32_t*>(smem_raw + bw2_tile_bytes(p));
   uint32_t* tmem_slot = meta + (size_t)p.nsg * kBw2Meta * kThreads;
+  const uint32_t bar = tma_smem(tmem_slot + 2);  // 8-byte aligned: the tables before it are multiples of 16
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   int pbase, stack, row_begin, row_end;
@@ -131,6 +144,10 @@ __global__ void __launch_bounds__(kThreads, 2) bfly_bw2_kernel(const __grid_cons
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_addr(tmem_slot)), "r"(kBw2TmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (p.tma && tid == 0) {
+    mbar_init(bar, 1);
+    fence_async_smem();
   }
   bw2_build_meta<T, KW>(p, meta, pbase, tid, kThreads);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -142,22 +159,57 @@ __global__ void __launch_bounds__(kThreads, 2) bfly_bw2_kernel(const __grid_cons
 
   bw2_init<T, KW>(p, accs, meta, stack, tid, kThreads);
 
+  const uint32_t tile_bytes = (uint32_t)(kBw2Rows * C * sizeof(T));
+  const int sx = p.tma_sx ? stack : 0, sg_ = p.tma_sg ? stack : 0, so = p.tma_so ? stack : 0;
+  // the panel's first column block in the rank-5 view of a row (bfly_tma.h)
+  const int pbf = pbase * p.tma_f;
+  const int c1 = (pbf & ((1 << p.tma_pbe) - 1)) >> 5, c2 = pbf >> p.tma_pbe;
+  auto issue_loads = [&](int row0) {
+    mbar_expect_tx(bar, 2 * tile_bytes);
+    tma_load_tile(tma_smem(smX), &map_x, bar, c1, c2, sx, row0);
+    tma_load_tile(tma_smem(smG), &map_g, bar, c1, c2, sg_, row0);
+  };
+  uint32_t parity = 0;
+  if (p.tma && tid == 0 && row_begin < row_end) issue_loads(row_begin);
+
   for (int row0 = row_begin; row0 < row_end; row0 += kBw2Rows) {
-    tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
-    tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
-    tile_load_wait();
-    __syncthreads();
+    if (p.tma) {
+      const bool ok = mbar_wait(bar, parity);
+      parity ^= 1;
+      if (__syncthreads_or(!ok)) {  // uniform decision: give up on this CTA's rows
+        if (tid == 0) atomicExch(&g_device_error, 1);
+        break;
+      }
+    } else {
+      tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
+      tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
+      tile_load_wait();
+      __syncthreads();
+    }
     for (int j = 0; j + 1 < p.nsg; ++j) {
       bw2_fw_step<T, KW, LOGC>(p, accs, meta, j, smX, smG, tid, kThreads);
       __syncthreads();
     }
     for (int j = p.nsg - 1; j >= 0; --j) {
       bw2_bw_step<T, KW, LOGC>(p, accs, meta, j, smX, smG, tid, kThreads);
+      if (p.tma && j == 0) fence_async_smem();  // the gradient tile is read by the TMA unit next
       __syncthreads();
     }
-    tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
-    __syncthreads();
+    if (p.tma) {
+      if (tid == 0) {
+        tma_store_tile(&map_o, tma_smem(smG), c1, c2, so, row0);
+        tma_store_commit();
+        if (row0 + kBw2Rows < row_end) {
+          tma_store_wait_read();  // the gradient tile is free again
+          issue_loads(row0 + kBw2Rows);
+        }
+      }
+    } else {
+      tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, kBw2Rows, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
+      __syncthreads();
+    }
   }
+  if (p.tma && tid == 0) tma_store_wait_all();
   bw2_flush<T, KW>(p, accs, meta, stack, tid, kThreads);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -243,18 +295,37 @@ struct CudaExec {
   DeviceInfo dev;
   int num_sms() const { return dev.sms; }
   int threads() const { return kThreads; }
+  static bool use_tma() {
+    if (const char* e = std::getenv("BFLY_TMA")) return std::atoi(e) != 0;
+    return true;
+  }
   bool has_bw2(size_t elem_size, int kw) const {
     if (const char* e = std::getenv("BFLY_BW_V2")) return std::atoi(e) != 0 && elem_size == 4 && kw == 2;
     return elem_size == 4 && kw == 2;
   }
 
-  template <typename T, int KW, int LOGC> int launch_bw2(const BwParams<T>& p) {
-    const size_t smem = bw2_smem_bytes(p, kThreads) + 16;
+  template <typename T, int KW, int LOGC> int launch_bw2(const BwParams<T>& p_in) {
+    BwParams<T> p = p_in;
+    const size_t smem = bw2_smem_bytes(p, kThreads) + 16 + 1024;  // TMEM slot, mbarrier, alignment slack
     int rc = set_smem(bfly_bw2_kernel<T, KW, LOGC>, smem);
     if (rc) return rc;
+    // describe the three tensors to the TMA unit when they qualify; else per-thread copies
+    CUtensorMap mx, mg, mo;
+    std::memset(&mx, 0, sizeof(mx)); std::memset(&mg, 0, sizeof(mg)); std::memset(&mo, 0, sizeof(mo));
+    constexpr int F = (int)(sizeof(T) / 4);
+    const TmaGeom geo = tma_geometry(p.panel, p.log_n, kBw2Rows, F);
+    p.tma = 0;
+    if (use_tma() && geo.ok && p.vec_x && p.vec_g && p.vec_o &&
+        tma_describe(&mx, geo, p.xin, p.xin_sB, p.xin_sS, p.xin_cols, p.B, p.S, F) &&
+        tma_describe(&mg, geo, p.gin, p.gin_sB, p.gin_sS, p.gin_cols, p.B, p.S, F) &&
+        tma_describe(&mo, geo, p.gout, p.gout_sB, p.gout_sS, p.gout_cols, p.B, p.S, F)) {
+      p.tma = 1;
+      p.tma_sx = (p.S > 1 && p.xin_sS != 0); p.tma_sg = (p.S > 1 && p.gin_sS != 0); p.tma_so = (p.S > 1 && p.gout_sS != 0);
+      p.tma_pbe = geo.pbe; p.tma_f = F;
+    }
     {
       ProfileScope prof(kKernBw, stream);
-      bfly_bw2_kernel<T, KW, LOGC><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+      bfly_bw2_kernel<T, KW, LOGC><<<bw_num_ctas(p), kThreads, smem, stream>>>(p, mx, mg, mo);
     }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
@@ -437,6 +508,15 @@ const char* bfly_strerror(int status) {
 int bfly_version(void) { return 100; }
 int bfly_cuda_version(void) { return CUDA_VERSION; }
 int64_t bfly_launch_count(void) { return g_launches.load(); }
+
+int bfly_device_error(void) {
+  int flag = 0;
+  const int zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return BFLY_E_CUDA;
+  if (cudaMemcpyFromSymbol(&flag, bfly::g_device_error, sizeof(int)) != cudaSuccess) return BFLY_E_CUDA;
+  if (flag && cudaMemcpyToSymbol(bfly::g_device_error, &zero, sizeof(int)) != cudaSuccess) return BFLY_E_CUDA;
+  return flag != 0;
+}
 
 void bfly_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_prof_mu);

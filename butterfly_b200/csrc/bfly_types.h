@@ -216,6 +216,9 @@ template <typename T> struct BwParams {
   int rows_per_cta;  // rows of one row slice (multiple of Rb)
   int nslices;
   int vec_x, vec_g, vec_o;
+  // tile traffic through the TMA unit (set by the launcher when all three tensors qualify):
+  // tma_s*: the tensor's descriptor has a stack dimension; tma_pbe, tma_f: see bfly_tma.h
+  int tma, tma_sx, tma_sg, tma_so, tma_pbe, tma_f;
   Panel panel;
   int nsg;
   BwSg sg[kMaxSg];

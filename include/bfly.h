@@ -133,6 +133,13 @@ int bfly4_bw_f32(const float* twiddle4, const float* twiddle2, const float* x, i
 /* Number of kernels the library has launched in this process so far (all entry points). */
 int64_t bfly_launch_count(void);
 
+/* Every wait inside the kernels (on a bulk tensor copy) is bounded; a kernel whose wait ran out
+ * stops early, leaves invalid output and raises a flag in device memory.  This call waits for
+ * the current device to go idle, returns the flag (0 = no kernel has given up since the last
+ * call, 1 = one has) and clears it; a negative status on a CUDA error.  No counterpart in the
+ * reference; meant for tests and for hosts that want to double-check a run. */
+int bfly_device_error(void);
+
 /* Per-kernel timing for benchmarks.  While enabled, every launch is bracketed by a pair of
  * CUDA events on its stream.  bfly_profile_collect waits for the recorded launches, adds
  * their count and device time into launches[id] / total_ms[id] (id 0 = forward kernel,

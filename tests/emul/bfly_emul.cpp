@@ -55,7 +55,10 @@ struct EmulExec {
     constexpr int N = BwTwn<KW>::value;
     const int C = 1 << p.panel.logC;
     const int nthr = C >> KW;
-    std::vector<T> smX((size_t)p.nsg * kBw2Rows * C), smG((size_t)kBw2Rows * C);
+    // one buffer, as on the device: nsg snapshot tiles followed by the gradient tile
+    std::vector<T> smem((size_t)(p.nsg + 1) * kBw2Rows * C);
+    struct View { T* ptr; T* data() const { return ptr; } };
+    const View smX{smem.data()}, smG{smem.data() + (size_t)p.nsg * kBw2Rows * C};
     std::vector<uint32_t> meta((size_t)p.nsg * kBw2Meta * nthr);
     std::vector<T> accmem((size_t)nthr * 2 * kMaxSg * N);
     const int nctas = bw_num_ctas(p);
