@@ -136,7 +136,7 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
     }
     // the unit table follows the tile in shared memory when it is small; give it room
     {
-      const size_t budget = tune.ctas_per_sm <= 1 ? (size_t)kSmemMax : (size_t)(228 * 1024) / tune.ctas_per_sm - 1024;
+      const size_t budget = tune.ctas_per_sm <= 1 ? (size_t)kSmemMax : (size_t)(228 * 1024) / tune.ctas_per_sm - 1024 - 2048;
       const size_t tab = (size_t)p.ngroups * p.tab_slots * ex.threads() * sizeof(uint16_t);
       const size_t row_bytes = sizeof(T) << pn.logC;
       p.use_table = tab <= 16 * 1024 && row_bytes + tab <= budget;

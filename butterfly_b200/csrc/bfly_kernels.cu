@@ -36,35 +36,111 @@ template <typename T, int KMAX> struct FwOcc {
   static constexpr int kMinBlocks = (sizeof(T) == 4 ? (KMAX <= 3 ? 2 : 1) : (KMAX <= 2 ? 2 : 1));
 };
 
-template <typename T, int KMAX, int LOGC, int ROWS>
+// Set when a bounded wait inside a kernel ran out (the kernel then stops early and its output
+// is invalid); read and cleared by bfly_device_error().
+__device__ int g_device_error = 0;
+
+// TMA descriptors of a forward launch (bfly_tma.h): input, output, snapshots.
+struct FwMaps {
+  CUtensorMap in, out, snap[8];
+};
+
+// Tile traffic goes through the TMA unit when every tensor of the launch can be described to
+// it (p.tma): thread 0 issues one bulk tensor load per tile and one bulk tensor store per
+// output, everybody waits on an mbarrier.  Otherwise every thread copies 16-byte chunks.
+template <typename T, int KMAX, int LOGC, int ROWS, bool TMA>
 __global__ void __launch_bounds__(kThreads, (FwOcc<T, KMAX>::kMinBlocks))
-bfly_fw_kernel(const __grid_constant__ FwParams<T> p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ FwMaps maps) {
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  // the swizzle of the TMA unit works on address bits: the tile starts on a 1024-byte boundary
+  unsigned char* smem_raw = smem_dyn + ((1024u - (tma_smem(smem_dyn) & 1023u)) & 1023u);
   T* sm = reinterpret_cast<T*>(smem_raw);
   uint16_t* tab = reinterpret_cast<uint16_t*>(smem_raw + fw_tile_bytes(p));
+  const uint32_t bar = tma_smem(smem_raw + fw_smem_bytes(p, kThreads));  // tile and table sizes are multiples of 16
   const int tid = threadIdx.x;
   const int64_t ntiles = fw_num_tiles(p);
   const int64_t n = (int64_t)1 << p.log_n;
   fw_build_table<T>(p, tab, tid, kThreads);  // read only by the thread that wrote it
+  if constexpr (TMA) {
+    if (tid == 0) {
+      mbar_init(bar, 1);
+      fence_async_smem();
+    }
+    __syncthreads();
+  }
+  const uint32_t tile_bytes = (uint32_t)fw_tile_bytes(p);
+  auto coords = [&](int64_t tile, int& row0, int& stack, int& c1, int& c2) {
+    int pbase;
+    fw_tile_coords(p, tile, row0, stack, pbase);
+    const int pbf = pbase * p.tma_f;
+    c1 = (pbf & ((1 << p.tma_pbe) - 1)) >> 5;
+    c2 = pbf >> p.tma_pbe;
+  };
+  auto issue_load = [&](int64_t tile) {
+    int row0, stack, c1, c2;
+    coords(tile, row0, stack, c1, c2);
+    mbar_expect_tx(bar, tile_bytes);
+    tma_load_tile(tma_smem(sm), &maps.in, bar, c1, c2, p.tma_sx ? stack : 0, row0);
+  };
+  uint32_t parity = 0;
+  if (TMA && tid == 0 && blockIdx.x < ntiles) issue_load(blockIdx.x);
+
   for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     int row0, stack, pbase;
     fw_tile_coords(p, tile, row0, stack, pbase);
-    tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
-    tile_load_wait();
-    __syncthreads();
+    if constexpr (TMA) {
+      const bool ok = mbar_wait(bar, parity);
+      parity ^= 1;
+      if (__syncthreads_or(!ok)) {  // uniform decision: give up on this CTA's tiles
+        if (tid == 0) atomicExch(&g_device_error, 1);
+        break;
+      }
+    } else {
+      tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
+      tile_load_wait();
+      __syncthreads();
+    }
     for (int g = 0; g < p.ngroups; ++g) {
       fw_group_dispatch<T, KMAX, LOGC, ROWS>(p, g, sm, tab, p.R, stack, pbase, tid, kThreads);
+      const bool last = (g + 1 == p.ngroups);
+      const int emit = p.g[g].emit;
+      if (TMA && (emit || (last && p.out))) fence_async_smem();  // the tile is read by the TMA unit next
       __syncthreads();
-      if (p.g[g].emit) {
-        tile_store_auto<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm, tid, kThreads);
-        __syncthreads();
+      if (emit) {
+        if constexpr (TMA) {
+          if (tid == 0) {
+            int r0_, st_, c1, c2;
+            coords(tile, r0_, st_, c1, c2);
+            tma_store_tile(&maps.snap[emit - 1], tma_smem(sm), c1, c2, stack, row0);
+            tma_store_commit();
+            if (!last) tma_store_wait_read();  // the next group rewrites the tile
+          }
+          if (!last) __syncthreads();
+        } else {
+          tile_store_auto<T>(p.snap[emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm, tid, kThreads);
+          __syncthreads();
+        }
       }
     }
-    if (p.out) {
+    if constexpr (TMA) {
+      if (tid == 0) {
+        if (p.out) {
+          int r0_, st_, c1, c2;
+          coords(tile, r0_, st_, c1, c2);
+          tma_store_tile(&maps.out, tma_smem(sm), c1, c2, p.tma_so ? stack : 0, row0);
+          tma_store_commit();
+        }
+        if (tile + gridDim.x < ntiles) {
+          tma_store_wait_read();  // the tile is free again
+          issue_load(tile + gridDim.x);
+        }
+      }
+    } else if (p.out) {
       tile_store_auto<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm, tid, kThreads);
       __syncthreads();
     }
   }
+  if (TMA && tid == 0) tma_store_wait_all();
 }
 
 // LOGC / RB: compile-time panel width (log2) and rows per batch, 0 = read from the parameters.
@@ -115,10 +191,6 @@ __global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks)) bfl
 // a thread owns the lane (32 * (warp % 4) + lane-in-warp) and, within it, the 128-column range
 // picked by warp / 4: 64 columns of accumulators and 64 of twiddles (4 sub-groups x 16).
 constexpr int kBw2TmemCols = 256;
-
-// Set when a bounded wait inside a kernel ran out (the kernel then stops early and its output
-// is invalid); read and cleared by bfly_device_error().
-__device__ int g_device_error = 0;
 
 // Tile traffic goes through the TMA unit when the three tensors can be described to it
 // (p.tma; bfly_tma.h): thread 0 issues one bulk tensor load per tile and one bulk tensor store
@@ -331,15 +403,43 @@ struct CudaExec {
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
   }
 
-  template <typename T, int KMAX, int LOGC, int ROWS> int launch_fw(const FwParams<T>& p) {
-    const size_t smem = fw_smem_bytes(p, kThreads);
-    int rc = set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS>, smem);
+  template <typename T, int KMAX, int LOGC, int ROWS> int launch_fw(const FwParams<T>& p_in) {
+    FwParams<T> p = p_in;
+    const size_t smem = fw_smem_bytes(p, kThreads) + 16 + 1024;  // mbarrier, alignment slack
+    // the TMA variant exists for the instances with a compile-time tile shape (the generic
+    // instances have no registers to spare for it)
+    constexpr bool kTmaInstance = LOGC > 0;
+    int rc = set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, false>, smem);
+    if constexpr (kTmaInstance) {
+      if (rc == BFLY_OK) rc = set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, true>, smem);
+    }
     if (rc) return rc;
     const int64_t ntiles = fw_num_tiles(p);
     const int grid = (int)std::min<int64_t>(ntiles, (int64_t)dev.sms * FwOcc<T, KMAX>::kMinBlocks);
+    // describe the tensors to the TMA unit when all of them qualify; else per-thread copies
+    FwMaps maps;
+    std::memset(&maps, 0, sizeof(maps));
+    constexpr int F = (int)(sizeof(T) / 4);
+    const int64_t n = (int64_t)1 << p.log_n;
+    const TmaGeom geo = tma_geometry(p.panel, p.log_n, p.R, F);
+    bool tma = kTmaInstance && use_tma() && geo.ok && p.vec_in && (!p.out || p.vec_out) &&
+               tma_describe(&maps.in, geo, p.x, p.x_sB, p.x_sS, p.x_cols, p.B, p.S, F) &&
+               (!p.out || tma_describe(&maps.out, geo, p.out, p.out_sB, p.out_sS, p.out_cols, p.B, p.S, F));
+    for (int i = 0; tma && i < 8; ++i)
+      if (p.snap[i]) tma = tma_describe(&maps.snap[i], geo, p.snap[i], (int64_t)p.S * n, n, (int)n, p.B, p.S, F);
+    p.tma = tma ? 1 : 0;
+    p.tma_sx = (p.S > 1 && p.x_sS != 0); p.tma_so = (p.S > 1 && p.out_sS != 0);
+    p.tma_pbe = geo.pbe; p.tma_f = F;
     {
       ProfileScope prof(kKernFw, stream);
-      bfly_fw_kernel<T, KMAX, LOGC, ROWS><<<grid, kThreads, smem, stream>>>(p);
+      bool launched = false;
+      if constexpr (kTmaInstance) {
+        if (tma) {
+          bfly_fw_kernel<T, KMAX, LOGC, ROWS, true><<<grid, kThreads, smem, stream>>>(p, maps);
+          launched = true;
+        }
+      }
+      if (!launched) bfly_fw_kernel<T, KMAX, LOGC, ROWS, false><<<grid, kThreads, smem, stream>>>(p, maps);
     }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;

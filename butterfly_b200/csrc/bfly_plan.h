@@ -74,7 +74,9 @@ inline int choose_unit_bits(int logC, int lbit, int K, int vb, bool vec, uint8_t
   return (int)order.size();
 }
 
-constexpr int kSmemMax = 227 * 1024;  // opt-in shared memory per CTA on sm_100
+// Shared memory the planners may fill per CTA: the 227 KB a CTA can opt into on sm_100, less 2 KB
+// that the kernels keep for alignment slack (tiles start on a 1024-byte boundary), barriers and slots.
+constexpr int kSmemMax = 227 * 1024 - 2048;
 constexpr int kMaxSnap = 8;
 
 inline Panel full_row_panel(int log_n) { return Panel{log_n, log_n, log_n, 0}; }
@@ -135,7 +137,7 @@ inline bool plan_fw_groups(const std::vector<Stage>& st, int t0, int t1, const s
 template <typename T>
 inline int fw_rows_per_tile(int logC, int B, int ctas, int max_rows) {
   const int row_bytes = (int)sizeof(T) << logC;
-  const int budget = ctas <= 1 ? kSmemMax : (228 * 1024) / ctas - 1024;
+  const int budget = ctas <= 1 ? kSmemMax : (228 * 1024) / ctas - 1024 - 2048;
   int R = budget / row_bytes;
   if (R < 1) R = kSmemMax / row_bytes;  // a row that only fits alone: one CTA per SM after all
   if (R > max_rows) R = max_rows;

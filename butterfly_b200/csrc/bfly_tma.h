@@ -72,8 +72,11 @@ inline TmaGeom tma_geometry(const Panel& pn, int log_n, int R, int floats_per_el
   g.pw = pn.logC - pn.lseg;
   g.pbe = (g.pw == 0 ? log_n : pn.pb) + fl;
   g.R = R;
-  // segments of at least one column block; box extents of at most 256 per dimension
-  g.ok = g.lseg >= 5 && g.lseg - 5 <= 8 && g.pw <= 8 && R >= 1 && R <= 256 && g.pbe >= g.lseg;
+  // segments of at least one column block; box extents of at most 256 per dimension; tile rows
+  // of whole 1024-byte swizzle periods (the hardware swizzles on address bits, the tile layout
+  // on the position inside the row: they agree when every row starts a new period)
+  g.ok = g.lseg >= 5 && g.lseg - 5 <= 8 && g.pw <= 8 && R >= 1 && R <= 256 && g.pbe >= g.lseg &&
+         pn.logC + fl >= 8;
   return g;
 }
 

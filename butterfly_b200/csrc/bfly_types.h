@@ -186,6 +186,9 @@ template <typename T> struct FwParams {
   int tab_slots;             // units per thread and group (max over groups)
   int use_table;             // unit positions come from a per-CTA table in shared memory
   int vec_in, vec_out;       // 16-byte global accesses allowed
+  // tile traffic through the TMA unit (set by the launcher when every tensor qualifies):
+  // tma_s*: the tensor's descriptor has a stack dimension; tma_pbe, tma_f: see bfly_tma.h
+  int tma, tma_sx, tma_so, tma_pbe, tma_f;
   Panel panel;
   int ngroups;
   FwGroup g[kMaxFwGroups];
