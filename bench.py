@@ -61,7 +61,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -248,7 +248,6 @@ def run_gpu_arm(args):
     barrier()
     ms = e0.elapsed_time(e1)
     launches = abi.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -323,6 +322,9 @@ def run_gpu_arm(args):
         e2e = {"value": step_bytes * world / (ems / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ems / e2e_steps,
                "steps": e2e_steps, "api": "butterfly_b200.host.HostPipeline.fw_bw (%d row chunks, 3 streams)" % args.e2e_chunks}
+
+    # the sampler ran through the kernel-timed loop, the per-kernel pass and the end-to-end loop
+    clocks = sampler.stop() if rank == 0 else None
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:

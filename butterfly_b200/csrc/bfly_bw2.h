@@ -105,8 +105,10 @@ BFLY_HD void bw2_build_meta(const BwParams<T>& p, uint32_t* meta, int pbase, int
       if (KW > 1 && sg.nst > 1) t1 = sg.tw_off[1] + (uint32_t)delete_bit(col0, wg + sg.q[1]) * 4u;
     }
     const int a0 = swzT<T>(lbase);
-    for (int m = 0; m < 4; ++m)
-      meta[(j * nthr + tid) * 4 + m] = m < E ? (uint32_t)(((a0 ^ sg.d[m]) + j * kBw2Rows * C) * SZ) : 0u;
+    for (int m = 0; m < 4; ++m) {
+      const int ms = (sg.swap12 && (m == 1 || m == 2)) ? 3 - m : m;  // register m holds element ms
+      meta[(j * nthr + tid) * 4 + m] = m < E ? (uint32_t)(((a0 ^ sg.d[ms]) + j * kBw2Rows * C) * SZ) : 0u;
+    }
     tws[(j * 2 + 0) * nthr + tid] = t0;
     tws[(j * 2 + 1) * nthr + tid] = t1;
   }
@@ -218,28 +220,35 @@ BFLY_HD void bw2_rows(const BwParams<T>& p, int j, const T* tw, T* acc, const ui
   (void)smG;
 }
 
-// sg.kase: stage pattern and access width of a sub-group, resolved on the host:
-//   2 * pattern + vec, pattern as in bw_pattern().
+// Code variant of a sub-group (BwSg::kase), resolved on the host by bw2_assign_kase (bfly_plan.h): 2 * pattern +
+// vec, pattern as in bw_pattern().  Without 16-byte accesses, the patterns that differ only in
+// which window bit comes first share code: the later-bit-first ones (2, 3, 5) run as (1, 0, 4)
+// on a unit whose elements 1 and 2 trade places (BwSg::swap12; the element offsets come from a
+// table, so the exchange is free), pair and twiddle numbering being the same under the swap.
 template <typename T, int KW, int LOGC, bool FORWARD>
 BFLY_HD void bw2_step(const BwParams<T>& p, int j, const T* tw, T* acc, const uint32_t* o, T* smX, T* smG) {
-  const BwSg& sg = p.sg[j];
-  const int kase = bw_pattern(sg, KW) * 2 + (sg.vec != 0 ? 1 : 0);
-#define BFLY_BW2_CASE(PAT)                                                                        \
-  case 2 * PAT: bw2_rows<T, KW, LOGC, PAT, false, FORWARD>(p, j, tw, acc, o, smX, smG); break;     \
-  case 2 * PAT + 1: bw2_rows<T, KW, LOGC, PAT, true, FORWARD>(p, j, tw, acc, o, smX, smG); break;
+  const int kase = p.sg[j].kase;
+#define BFLY_BW2_RUN(PAT, VEC) bw2_rows<T, KW, LOGC, PAT, VEC, FORWARD>(p, j, tw, acc, o, smX, smG)
   if constexpr (KW == 1) {
-    switch (kase) {
-      BFLY_BW2_CASE(0)
-      default: break;
-    }
+    if (kase & 1) BFLY_BW2_RUN(0, true);
+    else BFLY_BW2_RUN(0, false);
   } else {
+    if (kase == 2) { BFLY_BW2_RUN(1, false); return; }  // the common case first
     switch (kase) {
-      BFLY_BW2_CASE(0) BFLY_BW2_CASE(1) BFLY_BW2_CASE(2) BFLY_BW2_CASE(3) BFLY_BW2_CASE(4) BFLY_BW2_CASE(5)
-      BFLY_BW2_CASE(6)
+      case 0: BFLY_BW2_RUN(0, false); break;
+      case 8: BFLY_BW2_RUN(4, false); break;
+      case 12: BFLY_BW2_RUN(6, false); break;
+      case 1: BFLY_BW2_RUN(0, true); break;
+      case 3: BFLY_BW2_RUN(1, true); break;
+      case 5: BFLY_BW2_RUN(2, true); break;
+      case 7: BFLY_BW2_RUN(3, true); break;
+      case 9: BFLY_BW2_RUN(4, true); break;
+      case 11: BFLY_BW2_RUN(5, true); break;
+      case 13: BFLY_BW2_RUN(6, true); break;
       default: break;
     }
   }
-#undef BFLY_BW2_CASE
+#undef BFLY_BW2_RUN
 }
 
 BFLY_HD void bw2_load_offsets(const uint32_t* meta, int j, int tid, int nthr, uint32_t* o) {

@@ -238,7 +238,10 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     p.B = q.B; p.S = q.S; p.log_n = q.log_n;
     p.panel = P.panel;
     p.nsg = P.nsg;
-    for (int j = 0; j < P.nsg; ++j) p.sg[j] = P.sg[j];
+    for (int j = 0; j < P.nsg; ++j) {
+      p.sg[j] = P.sg[j];
+      bw2_assign_kase(p.sg[j], lay.kw);
+    }
     const size_t row_bytes = (size_t)(P.nsg + 1) * sizeof(T) << P.panel.logC;
     const int U = (1 << P.panel.logC) >> lay.kw;
     // second-generation kernel: full panels (one unit per thread), four-row batches, two CTAs per SM

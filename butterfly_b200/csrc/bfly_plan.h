@@ -147,6 +147,19 @@ inline int fw_rows_per_tile(int logC, int B, int ctas, int max_rows) {
 
 // ------------------------------------------------------------------ backward phases
 
+// Code variant that the second-generation backward kernel runs for a sub-group (bfly_bw2.h).
+inline void bw2_assign_kase(BwSg& sg, int KW) {
+  // pattern numbering of bw_pattern() in bfly_core.h
+  int pat = KW == 1 ? 0 : (sg.radix == 4 ? 6 : (sg.nst == 2 ? sg.q[0] * 2 + sg.q[1] : 4 + sg.q[0]));
+  sg.swap12 = 0;
+  if (!sg.vec && KW == 2 && (pat == 2 || pat == 3 || pat == 5)) {
+    pat = pat == 2 ? 1 : (pat == 3 ? 0 : 4);
+    sg.swap12 = 1;
+  }
+  sg.kase = (uint8_t)(2 * pat + (sg.vec ? 1 : 0));
+}
+
+
 struct BwPhase {
   int t0, t1;   // stages [t0, t1)
   Panel panel;

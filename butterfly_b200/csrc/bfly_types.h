@@ -204,6 +204,9 @@ struct BwSg {
   uint32_t tw_off[2];
   uint8_t ubit[kMaxUnitBits];
   uint16_t d[4];               // swz(m << lbit)
+  // second-generation backward kernel: the code variant that runs this sub-group (bw2_kase) and
+  // whether the unit's elements 1 and 2 trade places in the registers for it
+  uint8_t kase, swap12, pad_[2];
 };
 
 template <typename T> struct BwParams {
