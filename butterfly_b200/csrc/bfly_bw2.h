@@ -19,6 +19,10 @@
 namespace bfly {
 
 constexpr int kBw2Rows = 4;  // rows per batch
+#ifndef BFLY_BW2_UNR
+#define BFLY_BW2_UNR 2
+#endif
+constexpr int kBw2Unr = BFLY_BW2_UNR;  // rows a thread keeps in flight in a reverse step
 
 // ---------------------------------------------------------------- accumulator store
 template <typename T, int KW> struct AccStore {
@@ -200,17 +204,16 @@ BFLY_HD void bw2_rows(const BwParams<T>& p, int j, const T* tw, T* acc, const ui
     smaddr_t ag[E];
 #pragma unroll
     for (int m = 0; m < E; ++m) ag[m] = ax[m] + gdelta;
-    // two rows at a time: x, g and the recomputed intermediate of four rows would not fit the
-    // register budget of two CTAs per SM
-    static_for<0, R / 2>([&](auto hc) {
-      constexpr int h = decltype(hc)::value * 2;
-      T x[2][E], g[2][E];
-      static_for<0, 2>([&](auto rc) {
+    // kBw2Unr rows in flight (x, g and the recomputed intermediate of each are live together)
+    static_for<0, R / kBw2Unr>([&](auto hc) {
+      constexpr int h = decltype(hc)::value * kBw2Unr;
+      T x[kBw2Unr][E], g[kBw2Unr][E];
+      static_for<0, kBw2Unr>([&](auto rc) {
         constexpr int r = h + decltype(rc)::value;
         bw2_unit_ld<T, KW, VEC, r * ROWB>(ax, rowoff(r), x[r - h]);
         bw2_unit_ld<T, KW, VEC, r * ROWB>(ag, rowoff(r), g[r - h]);
       });
-      static_for<0, 2>([&](auto rc) {
+      static_for<0, kBw2Unr>([&](auto rc) {
         constexpr int r = h + decltype(rc)::value;
         bw_apply_bw<T, KW, PATID>(g[r - h], x[r - h], tw, acc);
         bw2_unit_st<T, KW, VEC, r * ROWB>(ag, rowoff(r), g[r - h]);
