@@ -245,7 +245,7 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     const size_t row_bytes = (size_t)(P.nsg + 1) * sizeof(T) << P.panel.logC;
     const int U = (1 << P.panel.logC) >> lay.kw;
     // second-generation kernel: full panels (one unit per thread), four-row batches, two CTAs per SM
-    const size_t v2_bytes = 4 * row_bytes + (size_t)P.nsg * 6 * KernelCfg<T>::kThreads * sizeof(uint32_t) + 16 + 1024;
+    const size_t v2_bytes = 4 * row_bytes + (size_t)P.nsg * 6 * KernelCfg<T>::kThreads * sizeof(uint32_t) + 32 + 1024;
     p.v2 = ex.has_bw2(sizeof(T), lay.kw) && P.nsg <= 4 && U == KernelCfg<T>::kThreads && v2_bytes <= (size_t)(228 * 1024) / 2 - 1024 &&
            q.B >= 4;
     int Rb = (int)(kSmemMax / row_bytes);

@@ -207,7 +207,9 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
   T* smG = smX + (size_t)p.nsg * kBw2Rows * C;
   uint32_t* meta = reinterpret_cast<uint32_t*>(smem_raw + bw2_tile_bytes(p));
   uint32_t* tmem_slot = meta + (size_t)p.nsg * kBw2Meta * kThreads;
-  const uint32_t bar = tma_smem(tmem_slot + 2);  // 8-byte aligned: the tables before it are multiples of 16
+  // two mbarriers (8-byte aligned: the tables before them are multiples of 16 bytes): one for the
+  // activation tile, one for the gradient tile, which is needed only after the forward steps
+  const uint32_t bar = tma_smem(tmem_slot + 2), bar_g = bar + 8;
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   int pbase, stack, row_begin, row_end;
@@ -219,6 +221,7 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
   }
   if (p.tma && tid == 0) {
     mbar_init(bar, 1);
+    mbar_init(bar_g, 1);
     fence_async_smem();
   }
   bw2_build_meta<T, KW>(p, meta, pbase, tid, kThreads);
@@ -236,13 +239,19 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
   // the panel's first column block in the rank-5 view of a row (bfly_tma.h)
   const int pbf = pbase * p.tma_f;
   const int c1 = (pbf & ((1 << p.tma_pbe) - 1)) >> 5, c2 = pbf >> p.tma_pbe;
-  auto issue_loads = [&](int row0) {
-    mbar_expect_tx(bar, 2 * tile_bytes);
+  auto issue_load_x = [&](int row0) {
+    mbar_expect_tx(bar, tile_bytes);
     tma_load_tile(tma_smem(smX), &map_x, bar, c1, c2, sx, row0);
-    tma_load_tile(tma_smem(smG), &map_g, bar, c1, c2, sg_, row0);
+  };
+  auto issue_load_g = [&](int row0) {
+    mbar_expect_tx(bar_g, tile_bytes);
+    tma_load_tile(tma_smem(smG), &map_g, bar_g, c1, c2, sg_, row0);
   };
   uint32_t parity = 0;
-  if (p.tma && tid == 0 && row_begin < row_end) issue_loads(row_begin);
+  if (p.tma && tid == 0 && row_begin < row_end) {
+    issue_load_x(row_begin);
+    issue_load_g(row_begin);
+  }
 
   for (int row0 = row_begin; row0 < row_end; row0 += kBw2Rows) {
     if (p.tma) {
@@ -262,6 +271,13 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
       bw2_fw_step<T, KW, LOGC>(p, accs, meta, j, smX, smG, tid, kThreads);
       __syncthreads();
     }
+    if (p.tma) {  // the gradient tile has had the forward steps to arrive
+      const bool ok = mbar_wait(bar_g, parity ^ 1);
+      if (__syncthreads_or(!ok)) {
+        if (tid == 0) atomicExch(&g_device_error, 1);
+        break;
+      }
+    }
     for (int j = p.nsg - 1; j >= 0; --j) {
       bw2_bw_step<T, KW, LOGC>(p, accs, meta, j, smX, smG, tid, kThreads);
       if (p.tma && j == 0) fence_async_smem();  // the gradient tile is read by the TMA unit next
@@ -269,11 +285,13 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
     }
     if (p.tma) {
       if (tid == 0) {
+        const bool more = row0 + kBw2Rows < row_end;
+        if (more) issue_load_x(row0 + kBw2Rows);  // the snapshot tiles are free already
         tma_store_tile(&map_o, tma_smem(smG), c1, c2, so, row0);
         tma_store_commit();
-        if (row0 + kBw2Rows < row_end) {
+        if (more) {
           tma_store_wait_read();  // the gradient tile is free again
-          issue_loads(row0 + kBw2Rows);
+          issue_load_g(row0 + kBw2Rows);
         }
       }
     } else {
@@ -378,7 +396,7 @@ struct CudaExec {
 
   template <typename T, int KW, int LOGC> int launch_bw2(const BwParams<T>& p_in) {
     BwParams<T> p = p_in;
-    const size_t smem = bw2_smem_bytes(p, kThreads) + 16 + 1024;  // TMEM slot, mbarrier, alignment slack
+    const size_t smem = bw2_smem_bytes(p, kThreads) + 32 + 1024;  // TMEM slot, two mbarriers, alignment slack
     int rc = set_smem(bfly_bw2_kernel<T, KW, LOGC>, smem);
     if (rc) return rc;
     // describe the three tensors to the TMA unit when they qualify; else per-thread copies
