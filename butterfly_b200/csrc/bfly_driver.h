@@ -40,11 +40,13 @@ template <> struct KernelCfg<cf> {
 };
 
 // Launch shape of the forward kernel.  The defaults (two CTAs per SM, windows of up to 3 bits
-// for float / 2 for complex) can be overridden for experiments with the environment variables
+// for float / 2 for complex; for float radix-4 products 4-bit windows, which hold two radix-4
+// stages, at one CTA per SM) can be overridden for experiments with the environment variables
 // BFLY_FW_KMAX (window bits) and BFLY_FW_ROWS (rows per tile).
 struct FwTuning { int kmax, ctas_per_sm, max_rows; };
-template <typename T> inline FwTuning fw_tuning() {
+template <typename T> inline FwTuning fw_tuning(bool base4) {
   FwTuning t{KernelCfg<T>::kFwKmaxTwoCtas, 2, 16};
+  if (base4 && sizeof(T) == 4) t.kmax = KernelCfg<T>::kFwKmaxOneCta;
   if (const char* e = std::getenv("BFLY_FW_KMAX")) {
     const int k = std::atoi(e);
     if (k >= 1 && k <= KernelCfg<T>::kFwKmaxOneCta) t.kmax = k;
@@ -99,7 +101,7 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
   if (((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;
   const Panel pn = full_row_panel(q.log_n);
   std::vector<FwGroup> groups;
-  const FwTuning tune = fw_tuning<T>();
+  const FwTuning tune = fw_tuning<T>(q.base4);
   if (!plan_fw_groups(st, t0, t1, cuts, pn, Vec16<T>::LOG, tune.kmax, groups))
     return BFLY_E_UNSUPPORTED;
   int64_t stk[2];
