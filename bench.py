@@ -192,6 +192,27 @@ def run_reference_arm(args):
 
 # ------------------------------------------------------------------------------ GPU arm
 
+# (config, kernel) -> (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch of the capture);
+# mean of the three phase launches in profiles/bfly_bw2_kernel_cfg2_batch4096.md
+NCU_DRAM_BYTES = {("cfg2", "bfly_bw_kernel"): (165.1e6, 4096)}
+
+
+def fp32_ceiling_gbs(cfg, B, step_bytes, sms=148, sm_mhz=1965.0):
+    """Algorithmic GB/s of fw+bw if only the FP32 pipes limited it (real radix-2 products).
+
+    Per element and stage: forward 2 multiply-add instructions; backward 4 (twiddle gradient and
+    input gradient) + 2 for each recomputed stage (the snapshot pass covers all but the last phase,
+    the phases recompute all but their last sub-group; 3/4 and 2/3 of the stages for 24 stages)."""
+    import torch
+    if cfg["base4"] or cfg["dtype"] != torch.float32:
+        return None
+    stages = cfg["nblocks"] * cfg["log_n"]
+    elem_stages = float(B) * cfg["nstacks"] * (1 << cfg["log_n"]) * stages
+    lane_ops = elem_stages * (2 + 4 + 2 * 0.75 + 2 * (2.0 / 3.0))
+    seconds = lane_ops / (sms * 128 * sm_mhz * 1e6)
+    return step_bytes / seconds / 1e9
+
+
 def run_gpu_arm(args):
     import torch.distributed as dist
     import butterfly_b200 as bb
@@ -278,8 +299,19 @@ def run_gpu_arm(args):
         alg = 2 * plane + tw_bytes
     avg_ms = dom_ms / max(dom_launches, 1)
     achieved = alg / (avg_ms * 1e-3) / 1e9
+    # DRAM bytes per launch of the dominant kernel from an ncu capture of a smaller batch of the
+    # same configuration, scaled by the rows (the summaries under profiles/ give the captures)
+    traffic = None
+    cap = NCU_DRAM_BYTES.get((args.config, dom))
+    if cap is not None:
+        traffic = cap[0] * B / cap[1]
+    # what the FP32 pipes alone allow for this step: multiply-add instructions of forward, snapshot
+    # pass, recompute and reverse sweep at 128 lanes per SM and the sampled clock
+    fp32_ceiling = fp32_ceiling_gbs(cfg, B, step_bytes)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_src,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": None, "launches_per_step": per_step,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                "traffic_source": ("ncu dram__bytes_read+write of a batch-%d capture, scaled by rows" % cap[1]) if cap else None,
+                "fp32_ceiling_gbs": fp32_ceiling, "launches_per_step": per_step,
                 "avg_launch_ms": avg_ms, "algorithmic_bytes_per_launch": alg,
                 "kernel_ms_per_step": {k: v[1] / 3 for k, v in prof.items()},
                 "op_frac_of_hbm_peak": (step_bytes / (ms_per_step * 1e-3) / 1e9) / peak}
