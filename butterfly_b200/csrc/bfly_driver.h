@@ -90,65 +90,95 @@ inline void twiddle_stack_sizes(const Problem& q, int64_t out[2]) {
   }
 }
 
+// Widest panel (log2 columns) of a forward pass when a row does not fit one SM: 32 KB rows.
+// BFLY_FW_LOGCMAX forces passes of narrower panels (tests run the multi-pass path at small n).
+template <typename T> inline int fw_pass_logc(int log_n) {
+  int lc = sizeof(T) == 4 ? 13 : 12;
+  if (((int64_t)sizeof(T) << log_n) <= kSmemMax) lc = log_n;
+  if (const char* e = std::getenv("BFLY_FW_LOGCMAX")) {
+    const int v = std::atoi(e);
+    if (v >= 3 && v < lc) lc = v;
+  }
+  return lc;
+}
+
 // Run stages [t0, t1) of the product with the row-owner forward kernel.  `cuts` lists the
-// stage indices after which a snapshot is written (slot i -> snaps[i]); `out` may be null.
+// stage indices after which a snapshot is written (slot i -> snaps[i]); `out` may be null when
+// only snapshots are wanted.  Rows that fit one SM's shared memory run in one pass; wider rows
+// in several passes over panels, in place on `out` (or on `scratch`, a (B, S, n) buffer with
+// the given strides, when `out` is null).
 template <typename T, typename E>
 int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int t1,
                    const std::vector<int>& cuts, T* const* snaps, const T* tw2, const T* tw4, const T* x,
                    int64_t x_sB, int64_t x_sS, int x_cols, T* out, int64_t out_sB, int64_t out_sS,
-                   int out_cols) {
+                   int out_cols, T* scratch = nullptr, int64_t scratch_sB = 0, int64_t scratch_sS = 0) {
   if (q.B == 0 || t1 <= t0) return BFLY_OK;
-  if (((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;
-  const Panel pn = full_row_panel(q.log_n);
-  std::vector<FwGroup> groups;
+  const int lc = fw_pass_logc<T>(q.log_n);
+  if (((int64_t)sizeof(T) << lc) > kSmemMax) return BFLY_E_UNSUPPORTED;
+  std::vector<FwPass> passes;
+  if (lc >= q.log_n) passes.push_back(FwPass{t0, t1, full_row_panel(q.log_n)});
+  else passes = plan_fw_passes(st, t0, t1, q.log_n, lc);
+  if (passes.empty()) return BFLY_E_UNSUPPORTED;
   const FwTuning tune = fw_tuning<T>(q.base4);
-  if (!plan_fw_groups(st, t0, t1, cuts, pn, Vec16<T>::LOG, tune.kmax, groups))
-    return BFLY_E_UNSUPPORTED;
   int64_t stk[2];
   twiddle_stack_sizes(q, stk);
   const int64_t n = (int64_t)1 << q.log_n;
-  size_t g0 = 0;
+  // the buffer the passes work on between the first read of x and the last write
+  T* work = out; int64_t work_sB = out_sB, work_sS = out_sS;
+  if (!work) { work = scratch; work_sB = scratch_sB; work_sS = scratch_sS; }
   bool first = true;
-  while (g0 < groups.size()) {
-    const size_t g1 = std::min(groups.size(), g0 + (size_t)kMaxFwGroups);
-    const bool last = (g1 == groups.size());
-    FwParams<T> p;
-    std::memset(&p, 0, sizeof(p));
-    p.tw[0] = tw2; p.tw[1] = tw4; p.tw_stack[0] = stk[0]; p.tw_stack[1] = stk[1];
-    if (first) {
-      p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
-    } else {  // continue in place from the full-width rows written by the previous launch
-      if (!out) return BFLY_E_UNSUPPORTED;
-      p.x = out; p.x_sB = out_sB; p.x_sS = out_sS; p.x_cols = (int)n;
+  for (size_t pi = 0; pi < passes.size(); ++pi) {
+    const FwPass& ps = passes[pi];
+    const Panel pn = ps.panel;
+    std::vector<FwGroup> groups;
+    if (!plan_fw_groups(st, ps.t0, ps.t1, cuts, pn, Vec16<T>::LOG, tune.kmax, groups))
+      return BFLY_E_UNSUPPORTED;
+    size_t g0 = 0;
+    while (g0 < groups.size()) {
+      const size_t g1 = std::min(groups.size(), g0 + (size_t)kMaxFwGroups);
+      const bool last = (g1 == groups.size()) && (pi + 1 == passes.size());
+      FwParams<T> p;
+      std::memset(&p, 0, sizeof(p));
+      p.tw[0] = tw2; p.tw[1] = tw4; p.tw_stack[0] = stk[0]; p.tw_stack[1] = stk[1];
+      if (first) {
+        p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
+      } else {  // continue in place from the full-width rows written by the previous launch
+        if (!work) return BFLY_E_UNSUPPORTED;
+        p.x = work; p.x_sB = work_sB; p.x_sS = work_sS; p.x_cols = (int)n;
+      }
+      if (last) {
+        p.out = out; p.out_sB = out_sB; p.out_sS = out_sS; p.out_cols = out_cols;
+      } else {
+        if (!work) return BFLY_E_UNSUPPORTED;
+        p.out = work; p.out_sB = work_sB; p.out_sS = work_sS; p.out_cols = (int)n;
+      }
+      for (int i = 0; i < kMaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
+      p.B = q.B; p.S = q.S; p.log_n = q.log_n;
+      p.R = fw_rows_per_tile<T>(pn.logC, q.B, tune.ctas_per_sm, tune.max_rows);
+      p.vec_in = vec_ok<T>(p.x, p.x_sB, p.x_sS);
+      p.vec_out = p.out ? vec_ok<T>(p.out, p.out_sB, p.out_sS) : 1;
+      p.panel = pn;
+      p.ngroups = (int)(g1 - g0);
+      p.tab_slots = 1;
+      for (size_t g = g0; g < g1; ++g) {
+        p.g[g - g0] = groups[g];
+        const int U = (1 << pn.logC) >> groups[g].K;
+        p.tab_slots = std::max(p.tab_slots, U / ex.threads());
+      }
+      // the unit table follows the tile in shared memory when it is small; give it room
+      {
+        const size_t budget = tune.ctas_per_sm <= 1 ? (size_t)kSmemMax : (size_t)(228 * 1024) / tune.ctas_per_sm - 1024 - 2048;
+        const size_t tab = (size_t)p.ngroups * p.tab_slots * ex.threads() * sizeof(uint16_t);
+        const size_t row_bytes = sizeof(T) << pn.logC;
+        p.use_table = tab <= 16 * 1024 && row_bytes + tab <= budget;
+        if (p.use_table)
+          while (p.R > 1 && (size_t)p.R * row_bytes + tab > budget) --p.R;
+      }
+      const int rc = ex.run_fw(p);
+      if (rc != BFLY_OK) return rc;
+      g0 = g1;
+      first = false;
     }
-    p.out = out; p.out_sB = out_sB; p.out_sS = out_sS;
-    p.out_cols = last ? out_cols : (int)n;
-    for (int i = 0; i < kMaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
-    p.B = q.B; p.S = q.S; p.log_n = q.log_n;
-    p.R = fw_rows_per_tile<T>(q.log_n, q.B, tune.ctas_per_sm, tune.max_rows);
-    p.vec_in = vec_ok<T>(p.x, p.x_sB, p.x_sS);
-    p.vec_out = out ? vec_ok<T>(out, out_sB, out_sS) : 1;
-    p.panel = pn;
-    p.ngroups = (int)(g1 - g0);
-    p.tab_slots = 1;
-    for (size_t g = g0; g < g1; ++g) {
-      p.g[g - g0] = groups[g];
-      const int U = (1 << pn.logC) >> groups[g].K;
-      p.tab_slots = std::max(p.tab_slots, U / ex.threads());
-    }
-    // the unit table follows the tile in shared memory when it is small; give it room
-    {
-      const size_t budget = tune.ctas_per_sm <= 1 ? (size_t)kSmemMax : (size_t)(228 * 1024) / tune.ctas_per_sm - 1024 - 2048;
-      const size_t tab = (size_t)p.ngroups * p.tab_slots * ex.threads() * sizeof(uint16_t);
-      const size_t row_bytes = sizeof(T) << pn.logC;
-      p.use_table = tab <= 16 * 1024 && row_bytes + tab <= budget;
-      if (p.use_table)
-        while (p.R > 1 && (size_t)p.R * row_bytes + tab > budget) --p.R;
-    }
-    const int rc = ex.run_fw(p);
-    if (rc != BFLY_OK) return rc;
-    g0 = g1;
-    first = false;
   }
   return BFLY_OK;
 }
@@ -182,7 +212,6 @@ int plan_bw(const Problem& q, BwLayout<T>& lay) {
   lay.phases = plan_bw_phases(st, q.log_n, logCmax, lay.kw, KernelCfg<T>::bw_max_sg(lay.kw), Vec16<T>::LOG);
   if (lay.phases.empty()) return BFLY_E_UNSUPPORTED;
   if ((int)lay.phases.size() - 1 > kMaxSnap) return BFLY_E_UNSUPPORTED;
-  if (lay.phases.size() > 1 && ((int64_t)sizeof(T) << q.log_n) > kSmemMax) return BFLY_E_UNSUPPORTED;
   const size_t plane = (size_t)q.B * q.S * sizeof(T) << q.log_n;
   lay.ws_bytes = (lay.phases.size() - 1) * ((plane + 255) / 256 * 256);
   return BFLY_OK;
@@ -220,8 +249,11 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     cuts.push_back(lay.phases[ph].t0);
   }
   if (nph > 1) {
+    // the snapshot pass of a product with wide rows (several forward passes) works in place on
+    // d_x, which no phase has written yet
+    const int64_t DXs = std::max<int64_t>(q.in_size, n);
     rc = drive_fw_range<T>(ex, q, st, 0, lay.phases[nph - 1].t0, cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size,
-                           (T*)nullptr, 0, 0, 0);
+                           (T*)nullptr, 0, 0, 0, d_x, (int64_t)q.S * DXs, DXs);
     if (rc != BFLY_OK) return rc;
   }
   const int64_t DX = std::max<int64_t>(q.in_size, n);

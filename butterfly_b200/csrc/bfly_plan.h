@@ -145,6 +145,52 @@ inline int fw_rows_per_tile(int logC, int B, int ctas, int max_rows) {
   return R;
 }
 
+// ------------------------------------------------------------------ forward passes
+//
+// A product whose rows do not fit one SM's shared memory runs as several launches ("passes")
+// of the forward kernel, each on panels of at most 2^logCmax columns: a pass is a run of
+// consecutive stages whose bits all lie below logCmax (contiguous panels) or inside a bit range
+// [lo, hi] narrow enough to leave segments of consecutive columns (strided panels: global bits
+// [0, w) and [lo, hi]).  The passes work in place on a full-width buffer.
+struct FwPass {
+  int t0, t1;
+  Panel panel;
+};
+
+inline std::vector<FwPass> plan_fw_passes(const std::vector<Stage>& st, int t0, int t1, int log_n, int logCmax) {
+  std::vector<FwPass> passes;
+  const int lc = std::min(logCmax, log_n);
+  auto stage_hi = [&](const Stage& s) { return s.bit + (s.radix == 4 ? 1 : 0); };
+  auto feasible = [&](int lo, int hi) {
+    if (hi + 1 <= lc) return true;
+    return (hi - lo + 1) + std::min(5, lo) <= lc;  // keep 32 consecutive columns per segment when the bits allow
+  };
+  int t = t0;
+  while (t < t1) {
+    int lo = st[t].bit, hi = stage_hi(st[t]);
+    if (!feasible(lo, hi)) return {};
+    int e = t + 1;
+    while (e < t1) {
+      const int nlo = std::min(lo, st[e].bit), nhi = std::max(hi, stage_hi(st[e]));
+      if (!feasible(nlo, nhi)) break;
+      lo = nlo; hi = nhi;
+      ++e;
+    }
+    FwPass ps;
+    ps.t0 = t; ps.t1 = e;
+    if (hi + 1 <= lc) {
+      ps.panel = Panel{lc, lc, lc, log_n - lc};
+    } else {
+      const int pw = hi - lo + 1;
+      const int w = std::min(lc - pw, lo);
+      ps.panel = Panel{pw + w, w, lo, log_n - pw - w};
+    }
+    passes.push_back(ps);
+    t = e;
+  }
+  return passes;
+}
+
 // ------------------------------------------------------------------ backward phases
 
 // Code variant that the second-generation backward kernel runs for a sub-group (bfly_bw2.h).

@@ -33,15 +33,17 @@ def P(t):
 I64 = ctypes.c_int64
 
 
-def emul_fw(lib, tw2, tw4, x, inc, out_size, log_n, nblocks, base4, threads=64):
+def emul_fw(lib, tw2, tw4, x, inc, out_size, log_n, nblocks, base4, threads=64, tail_untouched=True):
     B, S, insz = x.shape
     n = 1 << log_n
     out = torch.full((B, S, n), float("nan"), dtype=x.dtype)
     rc = lib.bfly_emul_fw(int(x.is_complex()), int(base4), P(tw2), P(tw4), P(x), I64(x.stride(0)), I64(x.stride(1)),
                           P(out), B, S, log_n, nblocks, insz, out_size, int(inc), threads)
     assert rc == 0, rc
-    # columns >= out_size must stay untouched
-    assert torch.isnan(out[:, :, out_size:]).all()
+    # columns >= out_size must stay untouched (a product that runs in several passes uses them as
+    # working space)
+    if tail_untouched:
+        assert torch.isnan(out[:, :, out_size:]).all()
     return out[:, :, :out_size]
 
 
@@ -115,6 +117,36 @@ def test_stack_broadcast_and_ragged_slices(emul, oracle_mod):
         d2, _, dx = emul_bw(emul, tw, None, x, g, True, 6, 2, False, sms=sms)
         dtr, dxr = oracle_mod.multiply_bw(tw, x, g, True)
         assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
+
+
+@pytest.mark.parametrize("logc", [6, 7, 8])
+def test_forward_passes_over_panels(emul, oracle_mod, monkeypatch, logc):
+    """Rows wider than a tile run as several forward launches over panels, in place; the
+    environment switch forces that path at sizes the emulator handles (the product path takes
+    it for rows beyond one SM's shared memory)."""
+    monkeypatch.setenv("BFLY_FW_LOGCMAX", str(logc))
+    torch.manual_seed(40 + logc)
+    for dtype in (torch.float32, torch.complex64):
+        for log_n, nb, inc in [(9, 1, True), (9, 2, False), (10, 2, True), (11, 1, False)]:
+            n = 1 << log_n
+            for insz, outsz in [(n, n), (n // 2 + 32, n - 64)]:
+                S, B = 2, 3
+                tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+                x = torch.randn(B, S, insz, dtype=dtype)
+                g = torch.randn(B, S, outsz, dtype=dtype)
+                y = emul_fw(emul, tw, None, x, inc, outsz, log_n, nb, False, 64, tail_untouched=False)
+                assert rel_err(y, oracle_mod.multiply_fw(tw, x, inc, outsz)) < 2e-5
+                d2, _, dx = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, 64)
+                dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+                assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
+    # base-4, odd and even log_n (a radix-4 stage needs two panel bits plus 32-column segments)
+    for log_n, nb, inc in ([(9, 2, True), (10, 1, False)] if logc >= 7 else []):
+        n = 1 << log_n
+        tw4 = torch.randn(1, nb, log_n // 2, n // 4, 4, 4) / 2
+        tw2 = torch.randn(1, nb, log_n % 2, n // 2, 2, 2) / 2 ** 0.5
+        x = torch.randn(3, 1, n)
+        y = emul_fw(emul, tw2, tw4, x, inc, n, log_n, nb, True, tail_untouched=False)
+        assert rel_err(y, oracle_mod.base4_fw(tw4, tw2, x, inc, n)) < 2e-5
 
 
 def test_backward_phase_plan_sizes(emul):

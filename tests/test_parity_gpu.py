@@ -107,6 +107,62 @@ def test_sweep_against_oracle(abi, dev, oracle_mod, dtype, log_n):
             assert rel_err(d_x[:, :, :insz], dxr) < TOL, (nb, inc, insz, outsz)
 
 
+@pytest.mark.parametrize("dtype,log_n", [(torch.float32, 16), (torch.complex64, 15), (torch.float32, 17)],
+                         ids=["f32-65536", "c64-32768", "f32-131072"])
+def test_rows_wider_than_one_sm(abi, dev, oracle_mod, dtype, log_n):
+    """Rows beyond one SM's shared memory (n > 32768 float, > 16384 complex): the forward runs as
+    several passes over column panels, the backward's snapshot pass likewise."""
+    torch.manual_seed(log_n)
+    n = 1 << log_n
+    B, S = 5, 1
+    for nb, inc in [(1, True), (2, False)]:
+        if log_n >= 17 and nb == 2:
+            continue
+        for insz, outsz in [(n, n), (n // 2 + 96, n - 160)]:
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+            x = torch.randn(B, S, insz, dtype=dtype)
+            g = torch.randn(B, S, outsz, dtype=dtype)
+            yr = oracle_mod.multiply_fw(tw, x, inc, outsz)
+            dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+            out, _ = abi.fw(tw.to(dev), x.to(dev), inc, outsz)
+            d_tw, d_x, _ = abi.bw(tw.to(dev), x.to(dev), g.to(dev), inc)
+            assert rel_err(out[:, :, :outsz], yr) < TOL, (nb, inc, insz, outsz)
+            assert rel_err(d_tw, dtr) < TOL, (nb, inc, insz, outsz)
+            assert rel_err(d_x[:, :, :insz], dxr) < TOL, (nb, inc, insz, outsz)
+
+
+@pytest.mark.parametrize("logc", [7, 9, 10])
+def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, logc):
+    """The multi-pass forward (environment switch BFLY_FW_LOGCMAX) must give what the one-pass
+    forward gives, for radix-2 and base-4 products, float and complex."""
+    torch.manual_seed(logc)
+    log_n, B, S = 12, 33, 2
+    n = 1 << log_n
+    for dtype in (torch.float32, torch.complex64):
+        for nb, inc in [(2, True), (1, False)]:
+            tw = (torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5).to(dev)
+            x = torch.randn(B, S, n - 64, dtype=dtype).to(dev)
+            g = torch.randn(B, S, n - 32, dtype=dtype).to(dev)
+            monkeypatch.delenv("BFLY_FW_LOGCMAX", raising=False)
+            y1, _ = abi.fw(tw, x, inc, n - 32)
+            dt1, dx1, _ = abi.bw(tw, x, g, inc)
+            monkeypatch.setenv("BFLY_FW_LOGCMAX", str(logc))
+            y2, _ = abi.fw(tw, x, inc, n - 32)
+            dt2, dx2, _ = abi.bw(tw, x, g, inc)
+            torch.cuda.synchronize()
+            assert torch.equal(y1[:, :, :n - 32], y2[:, :, :n - 32])  # same arithmetic, different tiling
+            assert rel_err(dt2, dt1) < 1e-5 and torch.equal(dx1, dx2)
+    tw4 = (torch.randn(S, 2, log_n // 2, n // 4, 4, 4) / 2).to(dev)
+    tw2 = torch.zeros(S, 2, 0, n // 2, 2, 2, device=dev)
+    x = torch.randn(B, S, n).to(dev)
+    monkeypatch.delenv("BFLY_FW_LOGCMAX", raising=False)
+    y1, _ = abi.fw_base4(tw4, tw2, x, True, n)
+    monkeypatch.setenv("BFLY_FW_LOGCMAX", str(logc))
+    y2, _ = abi.fw_base4(tw4, tw2, x, True, n)
+    torch.cuda.synchronize()
+    assert rel_err(y2, y1) < 1e-6  # window widths (and so the FMA grouping) may differ between tilings
+
+
 @pytest.mark.parametrize("log_n", [1, 2, 3, 6, 7, 10, 11, 14])
 def test_base4_sweep_against_oracle(abi, dev, oracle_mod, log_n):
     torch.manual_seed(50 + log_n)
