@@ -19,7 +19,7 @@ CSRC = os.path.join(ROOT, "butterfly_b200", "csrc")
 
 @pytest.fixture(scope="module")
 def emul():
-    deps = [EMUL_SRC] + [os.path.join(CSRC, f) for f in ("bfly_core.h", "bfly_types.h", "bfly_plan.h", "bfly_driver.h")]
+    deps = [EMUL_SRC] + [os.path.join(CSRC, f) for f in ("bfly_core.h", "bfly_bw2.h", "bfly_types.h", "bfly_plan.h", "bfly_driver.h")]
     if not os.path.exists(EMUL_LIB) or os.path.getmtime(EMUL_LIB) < max(os.path.getmtime(f) for f in deps):
         subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-unknown-pragmas", "-I", CSRC,
                                EMUL_SRC, "-o", EMUL_LIB])
