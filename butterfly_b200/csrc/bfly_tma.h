@@ -53,12 +53,9 @@ inline EncodeTiledFn tma_encoder() {
   return fn;
 }
 
-// Where a panel's first column block sits in the rank-5 view.
-struct TmaCoord {
-  int c1, c2;
-};
-
 // Geometry shared by all tensors of a launch: panel, rows per tile, floats per element.
+// A panel whose first column is pbase (in floats) starts at column block
+// (pbase mod 2^pbe) / 32 of group pbase >> pbe (the kernels compute these two coordinates).
 struct TmaGeom {
   int lseg, pw, pbe;  // in floats: log2 segment length, log2 segments per panel, log2 group length
   int R;              // rows per box
@@ -78,14 +75,6 @@ inline TmaGeom tma_geometry(const Panel& pn, int log_n, int R, int floats_per_el
   g.ok = g.lseg >= 5 && g.lseg - 5 <= 8 && g.pw <= 8 && R >= 1 && R <= 256 && g.pbe >= g.lseg &&
          pn.logC + fl >= 8;
   return g;
-}
-
-inline TmaCoord tma_coord(const TmaGeom& g, int pbase_elems, int floats_per_elem) {
-  const int pbase = pbase_elems * floats_per_elem;
-  TmaCoord c;
-  c.c1 = (pbase & ((1 << g.pbe) - 1)) >> 5;
-  c.c2 = pbase >> g.pbe;
-  return c;
 }
 
 // Describe tensor `ptr` ((B, S, cols) elements of floats_per_elem floats, element strides sB, sS)
