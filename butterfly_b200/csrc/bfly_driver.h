@@ -90,11 +90,14 @@ inline void twiddle_stack_sizes(const Problem& q, int64_t out[2]) {
   }
 }
 
-// Widest panel (log2 columns) of a forward pass when a row does not fit one SM: 32 KB rows.
-// BFLY_FW_LOGCMAX forces passes of narrower panels (tests run the multi-pass path at small n).
+// Widest panel (log2 columns) of a forward pass: 16 KB rows (4096 floats, 2048 complex).  Rows up
+// to that width run in one pass; wider rows would leave too few rows per tile to amortise the
+// twiddle fetches (and beyond 227 KB would not fit at all), so they run as several passes over
+// panels, which measures 1.3x (n = 8192) to 2.7x (n = 16384) faster than one pass with 3 or 1
+// rows per tile.  BFLY_FW_LOGCMAX forces narrower panels (tests run the multi-pass path at small n).
 template <typename T> inline int fw_pass_logc(int log_n) {
-  int lc = sizeof(T) == 4 ? 13 : 12;
-  if (((int64_t)sizeof(T) << log_n) <= kSmemMax) lc = log_n;
+  int lc = sizeof(T) == 4 ? 12 : 11;
+  if (log_n < lc) lc = log_n;
   if (const char* e = std::getenv("BFLY_FW_LOGCMAX")) {
     const int v = std::atoi(e);
     if (v >= 3 && v < lc) lc = v;
