@@ -43,8 +43,7 @@ def build(force=False, verbose=False):
     if not os.path.exists(nvcc):
         nvcc = "nvcc"
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-    core_src = [os.path.join(CSRC, f) for f in
-                ("bfly_kernels.cu", "bfly_core.h", "bfly_types.h", "bfly_plan.h", "bfly_driver.h")]
+    core_src = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".h"))]
     core_src.append(os.path.join(HERE, "..", "include", "bfly.h"))
     if force or _newer(LIB_CORE, core_src):
         _run([nvcc] + NVCC_FLAGS + [os.path.join(CSRC, "bfly_kernels.cu"), "-o", LIB_CORE], verbose)
