@@ -131,6 +131,47 @@ def test_rows_wider_than_one_sm(abi, dev, oracle_mod, dtype, log_n):
             assert rel_err(d_x[:, :, :insz], dxr) < TOL, (nb, inc, insz, outsz)
 
 
+@pytest.mark.parametrize("log_n,S", [(12, 3), (10, 2)], ids=["n4096", "n1024"])
+def test_tma_tile_path_edges(abi, dev, oracle_mod, monkeypatch, log_n, S):
+    """Shapes whose tiles travel through the TMA unit (4096- and 1024-column float rows), at the
+    edges the descriptors have to get right: stack-broadcast input, rows with a padded pitch,
+    zero-padded input, sliced output, batches that end inside a tile.  The per-thread copy path
+    (BFLY_TMA=0) must give the same bits, and both must match the oracle."""
+    torch.manual_seed(900 + log_n)
+    n = 1 << log_n
+    nb = 2
+    tw = (torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5)
+    cases = []
+    B = 53  # not a multiple of any tile height
+    xb = torch.randn(B, 1, n).expand(B, S, n)                       # stack stride 0
+    cases.append(("broadcast", xb, n))
+    wide = torch.randn(B, S, n + 64)
+    cases.append(("pitched rows", wide[:, :, :n], n - 96))           # row pitch n + 64, sliced output
+    cases.append(("padded input", torch.randn(B, S, n // 2 + 32), n))  # zero fill beyond the input
+    cases.append(("two rows", torch.randn(2, S, n), n))               # fewer rows than a batch of the backward
+    for name, x, outsz in cases:
+        g = torch.randn(x.shape[0], S, outsz)
+        yr = oracle_mod.multiply_fw(tw, x, True, outsz)
+        dtr, dxr = oracle_mod.multiply_bw(tw, x, g, True)
+        xd = x.to(dev) if name != "pitched rows" else wide.to(dev)[:, :, :n]
+        if name == "broadcast":
+            xd = xb[:, :1].to(dev).expand(B, S, n)
+        res = {}
+        for tma in ("1", "0"):
+            monkeypatch.setenv("BFLY_TMA", tma)
+            out, _ = abi.fw(tw.to(dev), xd, True, outsz)
+            d_tw, d_x, _ = abi.bw(tw.to(dev), xd, g.to(dev), True)
+            torch.cuda.synchronize()
+            res[tma] = (out[:, :, :outsz].clone(), d_tw.clone(), d_x.clone())
+        assert abi.device_error() == 0
+        assert torch.equal(res["1"][0], res["0"][0]), name
+        assert torch.equal(res["1"][2], res["0"][2]), name
+        assert rel_err(res["1"][1], res["0"][1]) < 1e-5, name
+        assert rel_err(res["1"][0], yr) < TOL, name
+        assert rel_err(res["1"][1], dtr) < TOL, name
+        assert rel_err(res["1"][2][:, :, :x.shape[2]], dxr) < TOL, name
+
+
 @pytest.mark.parametrize("logc", [7, 9, 10])
 def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, logc):
     """The multi-pass forward (environment switch BFLY_FW_LOGCMAX) must give what the one-pass
