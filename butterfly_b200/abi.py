@@ -20,7 +20,7 @@ SYMBOLS = (
     "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
-    "bfly_device_error",
+    "bfly_device_error", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -119,6 +119,54 @@ def bw(twiddle, x, grad, increasing_stride=True, workspace=None, d_twiddle=None,
             int(out_size), int(bool(increasing_stride)), _p(workspace), ctypes.c_size_t(ws_bytes), _stream())
     if check and rc != 0:
         raise BflyError(rc, "bfly_bw")
+    return d_twiddle, d_x, rc
+
+
+def fw_saving(twiddle, x, increasing_stride=True, output_size=None, out=None, snapshots=None, check=True):
+    """``bfly_fw_f32_saving`` / ``bfly_fw_c64_saving``: the forward that also writes the activations
+    the backward starts its phases from.  Returns (output buffer, snapshots, status)."""
+    _check_rows(x)
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    output_size = n if output_size is None else output_size
+    if out is None:
+        out = torch.empty(B, S, n, dtype=x.dtype, device=x.device)
+    need = bw_workspace_bytes(x.dtype, B, S, log_n, nblocks)
+    if need < 0:
+        if check:
+            raise BflyError(need, "bfly_bw_workspace_bytes")
+        return out, snapshots, need
+    if snapshots is None:
+        snapshots = torch.empty(need, dtype=torch.uint8, device=x.device)
+    fn = lib().bfly_fw_f32_saving if x.dtype == torch.float32 else lib().bfly_fw_c64_saving
+    rc = fn(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(B), int(S), int(log_n),
+            int(nblocks), int(in_size), int(output_size), int(bool(increasing_stride)), _p(snapshots),
+            ctypes.c_size_t(snapshots.numel()), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_fw_saving")
+    return out, snapshots, rc
+
+
+def bw_saved(twiddle, x, grad, snapshots, increasing_stride=True, d_twiddle=None, d_x=None, check=True):
+    """``bfly_bw_f32_saved`` / ``bfly_bw_c64_saved``: the backward that starts from the snapshots the
+    matching ``fw_saving`` call wrote.  Returns (d_twiddle, d_x buffer, status)."""
+    _check_rows(x)
+    _check_rows(grad)
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    out_size = grad.shape[2]
+    if d_twiddle is None:
+        d_twiddle = torch.empty_like(twiddle)
+    if d_x is None:
+        d_x = torch.empty(B, S, max(in_size, n), dtype=x.dtype, device=x.device)
+    fn = lib().bfly_bw_f32_saved if x.dtype == torch.float32 else lib().bfly_bw_c64_saved
+    rc = fn(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(grad), _i64(grad.stride(0)),
+            _i64(grad.stride(1)), _p(d_twiddle), _p(d_x), int(B), int(S), int(log_n), int(nblocks), int(in_size),
+            int(out_size), int(bool(increasing_stride)), _p(snapshots), ctypes.c_size_t(snapshots.numel()), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_bw_saved")
     return d_twiddle, d_x, rc
 
 

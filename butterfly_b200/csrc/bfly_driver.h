@@ -200,6 +200,9 @@ int drive_fw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
                            out, (int64_t)q.S * n, n, q.out_size);
 }
 
+template <typename T> struct BwLayout;
+template <typename T> int plan_bw(const Problem& q, BwLayout<T>& lay);
+
 template <typename T> struct BwLayout {
   std::vector<BwPhase> phases;
   int kw;
@@ -220,12 +223,41 @@ int plan_bw(const Problem& q, BwLayout<T>& lay) {
   return BFLY_OK;
 }
 
+// Forward that also writes, into ws, the phase-boundary activations the backward of the same
+// problem starts from (the layout drive_bw expects when it is told the snapshots are ready).
+template <typename T, typename E>
+int drive_fw_saving(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, int64_t x_sB, int64_t x_sS,
+                    T* out, void* ws, size_t ws_bytes) {
+  int rc = check_problem(q);
+  if (rc != BFLY_OK) return rc;
+  if (q.B == 0) return BFLY_OK;
+  if (!x || !out || (!tw2 && !tw4)) return BFLY_E_ARG;
+  if ((tw2 && !aligned16(tw2)) || (tw4 && !aligned16(tw4))) return BFLY_E_ALIGN;
+  BwLayout<T> lay;
+  rc = plan_bw<T>(q, lay);
+  if (rc != BFLY_OK) return rc;
+  if (lay.ws_bytes > 0 && (!ws || ws_bytes < lay.ws_bytes || !aligned16(ws))) return BFLY_E_WORKSPACE;
+  const std::vector<Stage> st = problem_stages(q);
+  const int64_t n = (int64_t)1 << q.log_n;
+  const int nph = (int)lay.phases.size();
+  const size_t plane = ((size_t)q.B * q.S * sizeof(T) << q.log_n);
+  const size_t plane_pad = (plane + 255) / 256 * 256;
+  T* snaps[kMaxSnap] = {nullptr};
+  std::vector<int> cuts;
+  for (int ph = 1; ph < nph; ++ph) {
+    snaps[ph - 1] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
+    cuts.push_back(lay.phases[ph].t0);
+  }
+  return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size, out,
+                           (int64_t)q.S * n, n, q.out_size);
+}
+
 // Backward of the whole product.  d_x is (B, S, max(in_size, n)) contiguous and doubles as
 // the gradient buffer between phases; d_tw2 / d_tw4 are overwritten.
 template <typename T, typename E>
 int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, int64_t x_sB, int64_t x_sS,
              const T* grad, int64_t g_sB, int64_t g_sS, T* d_tw2, T* d_tw4, T* d_x, void* ws,
-             size_t ws_bytes) {
+             size_t ws_bytes, bool snapshots_ready = false) {
   int rc = check_problem(q);
   if (rc != BFLY_OK) return rc;
   int64_t stk[2];
@@ -251,7 +283,7 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     snaps[ph - 1] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
     cuts.push_back(lay.phases[ph].t0);
   }
-  if (nph > 1) {
+  if (nph > 1 && !snapshots_ready) {
     // the snapshot pass of a product with wide rows (several forward passes) works in place on
     // d_x, which no phase has written yet
     const int64_t DXs = std::max<int64_t>(q.in_size, n);

@@ -541,17 +541,29 @@ static int fw_entry(bool base4, const void* tw2, const void* tw4, const void* x,
 }
 
 template <typename T>
+static int fw_saving_entry(const void* tw2, const void* x, int64_t x_sB, int64_t x_sS, void* out, int B, int S,
+                           int log_n, int nblocks, int in_size, int out_size, int inc, void* ws, size_t ws_bytes,
+                           void* stream) {
+  CudaExec ex;
+  int rc = make_exec(stream, ex);
+  if (rc) return rc;
+  Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, false};
+  return drive_fw_saving<T>(ex, q, static_cast<const T*>(tw2), static_cast<const T*>(nullptr),
+                            static_cast<const T*>(x), x_sB, x_sS, static_cast<T*>(out), ws, ws_bytes);
+}
+
+template <typename T>
 static int bw_entry(bool base4, const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS,
                     const void* grad, int64_t g_sB, int64_t g_sS, void* d2, void* d4, void* dx, int B, int S,
                     int log_n, int nblocks, int in_size, int out_size, int inc, void* ws, size_t ws_bytes,
-                    void* stream) {
+                    void* stream, bool snapshots_ready = false) {
   CudaExec ex;
   int rc = make_exec(stream, ex);
   if (rc) return rc;
   Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, base4};
   return drive_bw<T>(ex, q, static_cast<const T*>(tw2), static_cast<const T*>(tw4), static_cast<const T*>(x),
                      x_sB, x_sS, static_cast<const T*>(grad), g_sB, g_sS, static_cast<T*>(d2),
-                     static_cast<T*>(d4), static_cast<T*>(dx), ws, ws_bytes);
+                     static_cast<T*>(d4), static_cast<T*>(dx), ws, ws_bytes, snapshots_ready);
 }
 
 template <typename T>
@@ -693,6 +705,34 @@ int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, 
   return bw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x, batch,
                       nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
                       workspace_bytes, stream);
+}
+int bfly_fw_f32_saving(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, int batch,
+                       int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                       void* snapshots, size_t snapshot_bytes, void* stream) {
+  return fw_saving_entry<float>(twiddle, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks, input_size, output_size,
+                                increasing_stride, snapshots, snapshot_bytes, stream);
+}
+int bfly_fw_c64_saving(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, void* out, int batch,
+                       int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                       void* snapshots, size_t snapshot_bytes, void* stream) {
+  return fw_saving_entry<cf>(twiddle, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks, input_size, output_size,
+                             increasing_stride, snapshots, snapshot_bytes, stream);
+}
+int bfly_bw_f32_saved(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, const float* grad,
+                      int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x, int batch, int nstacks, int log_n,
+                      int nblocks, int input_size, int output_size, int increasing_stride, void* snapshots,
+                      size_t snapshot_bytes, void* stream) {
+  return bw_entry<float>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x, batch,
+                         nstacks, log_n, nblocks, input_size, output_size, increasing_stride, snapshots,
+                         snapshot_bytes, stream, true);
+}
+int bfly_bw_c64_saved(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, const void* grad, int64_t g_sB,
+                      int64_t g_sS, void* d_twiddle, void* d_x, int batch, int nstacks, int log_n, int nblocks,
+                      int input_size, int output_size, int increasing_stride, void* snapshots, size_t snapshot_bytes,
+                      void* stream) {
+  return bw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x, batch,
+                      nstacks, log_n, nblocks, input_size, output_size, increasing_stride, snapshots, snapshot_bytes,
+                      stream, true);
 }
 int bfly_bw_f32_noalloc(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, const float* grad,
                         int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x, int batch, int nstacks, int log_n,

@@ -13,6 +13,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/script.h>
 
+#include <cstdlib>
 #include <tuple>
 
 #include "../../include/bfly.h"
@@ -47,8 +48,10 @@ Tensor rows_view(const Tensor& t) {
   return r;
 }
 
-Tensor butterfly_multiply_fw(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
-                             c10::optional<int64_t> output_size) {
+// Shared by the plain operator and the autograd node: with `snapshots` the forward also writes
+// the activations the backward starts its phases from (bfly_fw_*_saving).
+Tensor fw_impl(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
+               c10::optional<int64_t> output_size, Tensor* snapshots) {
   BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_SAME_DEVICE(twiddle, input);
   BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 3);
   const int64_t batch = input.size(0), nstacks = input.size(1), input_size = input.size(2);
@@ -68,7 +71,21 @@ Tensor butterfly_multiply_fw(const Tensor& twiddle, const Tensor& input, bool in
   Tensor output = torch::empty({batch, nstacks, n}, input.options());
   auto stream = at::cuda::getCurrentCUDAStream();
   int rc;
-  if (dt == BFLY_F32) {
+  if (snapshots) {
+    const int64_t ws_bytes = bfly_bw_workspace_bytes(dt, (int)batch, (int)nstacks, (int)log_n, (int)nblocks);
+    TORCH_CHECK(ws_bytes >= 0, "butterfly_multiply failed: ", bfly_strerror((int)ws_bytes));
+    *snapshots = torch::empty({ws_bytes}, input.options().dtype(at::kByte));
+    void* sp = ws_bytes ? snapshots->data_ptr() : nullptr;
+    if (dt == BFLY_F32) {
+      rc = bfly_fw_f32_saving(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1),
+                              output.data_ptr<float>(), (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
+                              (int)input_size, (int)out_size, increasing_stride, sp, (size_t)ws_bytes, stream.stream());
+    } else {
+      rc = bfly_fw_c64_saving(tw.data_ptr(), x.data_ptr(), x.stride(0), x.stride(1), output.data_ptr(), (int)batch,
+                              (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
+                              increasing_stride, sp, (size_t)ws_bytes, stream.stream());
+    }
+  } else if (dt == BFLY_F32) {
     rc = bfly_fw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1),
                      output.data_ptr<float>(), (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
                      (int)input_size, (int)out_size, increasing_stride, stream.stream());
@@ -81,8 +98,15 @@ Tensor butterfly_multiply_fw(const Tensor& twiddle, const Tensor& input, bool in
   return out_size < n ? output.slice(2, 0, out_size) : output;
 }
 
-std::tuple<Tensor, Tensor> butterfly_multiply_bw(const Tensor& twiddle, const Tensor& input, const Tensor& grad,
-                                                 bool increasing_stride) {
+Tensor butterfly_multiply_fw(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
+                             c10::optional<int64_t> output_size) {
+  return fw_impl(twiddle, input, increasing_stride, output_size, nullptr);
+}
+
+// `snapshots`: what the matching fw_impl call saved (then the backward skips its own forward
+// pass over the first phases), or null.
+std::tuple<Tensor, Tensor> bw_impl(const Tensor& twiddle, const Tensor& input, const Tensor& grad,
+                                   bool increasing_stride, const Tensor* snapshots) {
   BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_CUDA(grad);
   BFLY_CHECK_SAME_DEVICE(twiddle, input); BFLY_CHECK_SAME_DEVICE(input, grad);
   BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 3); BFLY_CHECK_DIM(grad, 3);
@@ -107,10 +131,21 @@ std::tuple<Tensor, Tensor> butterfly_multiply_bw(const Tensor& twiddle, const Te
   Tensor d_input = torch::empty({batch, nstacks, std::max(input_size, n)}, input.options());
   const int64_t ws_bytes = bfly_bw_workspace_bytes(dt, (int)batch, (int)nstacks, (int)log_n, (int)nblocks);
   TORCH_CHECK(ws_bytes >= 0, "butterfly_multiply_bw failed: ", bfly_strerror((int)ws_bytes));
-  Tensor ws = torch::empty({ws_bytes}, input.options().dtype(at::kByte));
+  const bool saved = snapshots && snapshots->defined() && snapshots->numel() >= ws_bytes;
+  Tensor ws = saved ? *snapshots : torch::empty({ws_bytes}, input.options().dtype(at::kByte));
   auto stream = at::cuda::getCurrentCUDAStream();
   int rc;
-  if (dt == BFLY_F32) {
+  if (saved && dt == BFLY_F32) {
+    rc = bfly_bw_f32_saved(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1), g.data_ptr<float>(),
+                           g.stride(0), g.stride(1), d_twiddle.data_ptr<float>(), d_input.data_ptr<float>(),
+                           (int)batch, (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
+                           increasing_stride, ws_bytes ? ws.data_ptr() : nullptr, (size_t)ws_bytes, stream.stream());
+  } else if (saved) {
+    rc = bfly_bw_c64_saved(tw.data_ptr(), x.data_ptr(), x.stride(0), x.stride(1), g.data_ptr(), g.stride(0),
+                           g.stride(1), d_twiddle.data_ptr(), d_input.data_ptr(), (int)batch, (int)nstacks,
+                           (int)log_n, (int)nblocks, (int)input_size, (int)out_size, increasing_stride,
+                           ws_bytes ? ws.data_ptr() : nullptr, (size_t)ws_bytes, stream.stream());
+  } else if (dt == BFLY_F32) {
     rc = bfly_bw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1), g.data_ptr<float>(),
                      g.stride(0), g.stride(1), d_twiddle.data_ptr<float>(), d_input.data_ptr<float>(), (int)batch,
                      (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size, increasing_stride,
@@ -126,6 +161,21 @@ std::tuple<Tensor, Tensor> butterfly_multiply_bw(const Tensor& twiddle, const Te
   return std::make_tuple(d_twiddle, d_input);
 }
 
+std::tuple<Tensor, Tensor> butterfly_multiply_bw(const Tensor& twiddle, const Tensor& input, const Tensor& grad,
+                                                 bool increasing_stride) {
+  return bw_impl(twiddle, input, grad, increasing_stride, nullptr);
+}
+
+// The autograd node may keep the forward's phase-boundary activations for its backward (the
+// reference recomputes them, csrc/butterfly.cpp:99-118): that removes one forward-sized pass from
+// every training step at the price of holding (phases - 1) activation-sized buffers per call
+// between forward and backward.  On by default while those buffers stay under 1 GiB per call;
+// BFLY_AUTOGRAD_SAVE=0 always recomputes, =1 always saves.
+bool autograd_saves(int64_t snapshot_bytes) {
+  if (const char* e = std::getenv("BFLY_AUTOGRAD_SAVE")) return std::atoi(e) != 0;
+  return snapshot_bytes > 0 && snapshot_bytes <= ((int64_t)1 << 30);
+}
+
 using torch::autograd::AutogradContext;
 using torch::autograd::variable_list;
 
@@ -136,13 +186,28 @@ class ButterflyMultiply : public torch::autograd::Function<ButterflyMultiply> {
   static Tensor forward(AutogradContext* ctx, Tensor twiddle, Tensor input, bool increasing_stride,
                         c10::optional<int64_t> output_size) {
     ctx->saved_data["increasing_stride"] = increasing_stride;
-    ctx->save_for_backward({twiddle, input});
-    return butterfly_multiply_fw(twiddle, input, increasing_stride, output_size);
+    bool save = false;
+    if (twiddle.is_cuda() && input.is_cuda() && twiddle.dim() == 6 && input.dim() == 3 &&
+        (twiddle.requires_grad() || input.requires_grad()) &&
+        (input.scalar_type() == at::kFloat || input.scalar_type() == at::kComplexFloat)) {
+      const int64_t ws = bfly_bw_workspace_bytes(input.scalar_type() == at::kFloat ? BFLY_F32 : BFLY_C64,
+                                                 (int)input.size(0), (int)input.size(1), (int)twiddle.size(2),
+                                                 (int)twiddle.size(1));
+      save = ws > 0 && autograd_saves(ws);
+    }
+    if (!save) {
+      ctx->save_for_backward({twiddle, input});
+      return butterfly_multiply_fw(twiddle, input, increasing_stride, output_size);
+    }
+    Tensor snapshots;
+    Tensor out = fw_impl(twiddle, input, increasing_stride, output_size, &snapshots);
+    ctx->save_for_backward({twiddle, input, snapshots});
+    return out;
   }
   static variable_list backward(AutogradContext* ctx, variable_list grad_output) {
     auto saved = ctx->get_saved_variables();
-    auto result = butterfly_multiply_bw(saved[0], saved[1], grad_output[0],
-                                        ctx->saved_data["increasing_stride"].toBool());
+    auto result = bw_impl(saved[0], saved[1], grad_output[0], ctx->saved_data["increasing_stride"].toBool(),
+                          saved.size() > 2 ? &saved[2] : nullptr);
     return {std::get<0>(result), std::get<1>(result), Tensor(), Tensor()};
   }
 };

@@ -132,6 +132,34 @@ int bfly4_bw_f32(const float* twiddle4, const float* twiddle2, const float* x, i
                  int input_size, int output_size, int increasing_stride, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/* Forward / backward pair that trades memory for time.  No counterpart in the reference, whose
+ * autograd node saves only {twiddle, input} and recomputes everything in the backward
+ * (csrc/butterfly.cpp:99-118).
+ *
+ * bfly_fw_*_saving is the forward that also leaves in `snapshots` the activations at the
+ * backward's phase boundaries (bfly_bw_workspace_bytes bytes for the same problem; 0 bytes when
+ * the backward has a single phase).  bfly_bw_*_saved is the backward that starts from them
+ * instead of recomputing them: same arguments and results as bfly_bw_*, with `snapshots` as
+ * written by the matching forward (same twiddle, x, sizes and direction) and left untouched. */
+int bfly_fw_f32_saving(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out,
+                       int batch, int nstacks, int log_n, int nblocks, int input_size,
+                       int output_size, int increasing_stride, void* snapshots,
+                       size_t snapshot_bytes, void* stream);
+int bfly_fw_c64_saving(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, void* out,
+                       int batch, int nstacks, int log_n, int nblocks, int input_size,
+                       int output_size, int increasing_stride, void* snapshots,
+                       size_t snapshot_bytes, void* stream);
+int bfly_bw_f32_saved(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS,
+                      const float* grad, int64_t g_sB, int64_t g_sS, float* d_twiddle, float* d_x,
+                      int batch, int nstacks, int log_n, int nblocks, int input_size,
+                      int output_size, int increasing_stride, void* snapshots,
+                      size_t snapshot_bytes, void* stream);
+int bfly_bw_c64_saved(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS,
+                      const void* grad, int64_t g_sB, int64_t g_sS, void* d_twiddle, void* d_x,
+                      int batch, int nstacks, int log_n, int nblocks, int input_size,
+                      int output_size, int increasing_stride, void* snapshots,
+                      size_t snapshot_bytes, void* stream);
+
 /* Number of kernels the library has launched in this process so far (all entry points). */
 int64_t bfly_launch_count(void);
 

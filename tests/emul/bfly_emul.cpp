@@ -151,6 +151,24 @@ int emul_bw(const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64
   return drive_bw<T>(ex, q, (const T*)tw2, (const T*)tw4, (const T*)x, x_sB, x_sS, (const T*)g, g_sB, g_sS, (T*)d2, (T*)d4, (T*)dx, wsp, lay.ws_bytes);
 }
 
+// forward that saves the phase-boundary activations, then the backward that starts from them
+template <typename T>
+int emul_fw_bw_saved(const void* tw2, const void* x, int64_t x_sB, int64_t x_sS, void* out, const void* g, int64_t g_sB,
+                     int64_t g_sS, void* d2, void* dx, Problem q, int threads, int sms) {
+  EmulExec ex; ex.threads_ = threads; ex.sms = sms;
+  BwLayout<T> lay;
+  int rc = check_problem(q);
+  if (rc) return rc;
+  rc = plan_bw<T>(q, lay);
+  if (rc) return rc;
+  std::vector<char> ws(lay.ws_bytes + 256);
+  void* wsp = (void*)(((uintptr_t)ws.data() + 255) / 256 * 256);
+  rc = drive_fw_saving<T>(ex, q, (const T*)tw2, (const T*)nullptr, (const T*)x, x_sB, x_sS, (T*)out, wsp, lay.ws_bytes);
+  if (rc) return rc;
+  return drive_bw<T>(ex, q, (const T*)tw2, (const T*)nullptr, (const T*)x, x_sB, x_sS, (const T*)g, g_sB, g_sS, (T*)d2,
+                     (T*)nullptr, (T*)dx, wsp, lay.ws_bytes, true);
+}
+
 }  // namespace
 
 // Worst shared-memory bank-conflict degree (1 = conflict-free) of the accesses a 256-thread CTA
@@ -228,6 +246,13 @@ int bfly_emul_bw(int dtype, int base4, const void* tw2, const void* tw4, const v
   Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, base4 != 0};
   return dtype == 0 ? emul_bw<float>(tw2, tw4, x, x_sB, x_sS, g, g_sB, g_sS, d2, d4, dx, q, threads, sms)
                     : emul_bw<cf>(tw2, tw4, x, x_sB, x_sS, g, g_sB, g_sS, d2, d4, dx, q, threads, sms);
+}
+int bfly_emul_fw_bw_saved(int dtype, const void* tw, const void* x, int64_t x_sB, int64_t x_sS, void* out, const void* g,
+                          int64_t g_sB, int64_t g_sS, void* d_tw, void* dx, int B, int S, int log_n, int nblocks, int in_size,
+                          int out_size, int inc, int threads, int sms) {
+  Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, false};
+  return dtype == 0 ? emul_fw_bw_saved<float>(tw, x, x_sB, x_sS, out, g, g_sB, g_sS, d_tw, dx, q, threads, sms)
+                    : emul_fw_bw_saved<cf>(tw, x, x_sB, x_sS, out, g, g_sB, g_sS, d_tw, dx, q, threads, sms);
 }
 // number of backward phases and workspace bytes the planner chooses (for tests of the planner)
 int bfly_emul_bw_plan(int dtype, int base4, int B, int S, int log_n, int nblocks, int inc, int64_t* ws_bytes) {

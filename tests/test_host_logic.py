@@ -149,6 +149,30 @@ def test_forward_passes_over_panels(emul, oracle_mod, monkeypatch, logc):
         assert rel_err(y, oracle_mod.base4_fw(tw4, tw2, x, inc, n)) < 2e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
+def test_forward_that_saves_snapshots_feeds_the_backward(emul, oracle_mod, dtype):
+    """bfly_fw_*_saving + bfly_bw_*_saved: the forward leaves the phase-boundary activations, the
+    backward starts from them; results as from the recomputing pair."""
+    torch.manual_seed(77)
+    for log_n, nb, inc, thr in [(6, 3, True, 64), (10, 2, False, 256), (11, 2, True, 256), (4, 1, True, 64)]:
+        n = 1 << log_n
+        for insz, outsz in [(n, n), (max(1, n // 2 - 1), max(1, n - 5))]:
+            S, B = 2, 5
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+            x = torch.randn(B, S, insz, dtype=dtype)
+            g = torch.randn(B, S, outsz, dtype=dtype)
+            out = torch.full((B, S, n), float("nan"), dtype=dtype)
+            d_tw = torch.full_like(tw, float("nan"))
+            dx = torch.full((B, S, max(insz, n)), float("nan"), dtype=dtype)
+            rc = emul.bfly_emul_fw_bw_saved(int(dtype.is_complex), P(tw), P(x), I64(x.stride(0)), I64(x.stride(1)), P(out),
+                                            P(g), I64(g.stride(0)), I64(g.stride(1)), P(d_tw), P(dx), B, S, log_n, nb,
+                                            insz, outsz, int(inc), thr, 7)
+            assert rc == 0, rc
+            assert rel_err(out[:, :, :outsz], oracle_mod.multiply_fw(tw, x, inc, outsz)) < 2e-5
+            dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+            assert rel_err(d_tw, dtr) < 2e-5 and rel_err(dx[:, :, :insz], dxr) < 2e-5
+
+
 def test_backward_phase_plan_sizes(emul):
     ws = ctypes.c_int64(0)
     # float: a phase holds at most 8 stages (4 sub-groups of 2) on a panel of 1024 columns

@@ -172,6 +172,42 @@ def test_tma_tile_path_edges(abi, dev, oracle_mod, monkeypatch, log_n, S):
         assert rel_err(res["1"][2][:, :, :x.shape[2]], dxr) < TOL, name
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
+def test_saving_forward_and_saved_backward(abi, dev, oracle_mod, monkeypatch, dtype):
+    """bfly_fw_*_saving / bfly_bw_*_saved through the C ABI, and the autograd operator that uses
+    them: same bits as the recomputing pair for output and d_input (same arithmetic, the activations
+    are stored instead of recomputed), d_twiddle up to the order of the final adds."""
+    import butterfly_b200 as bb
+    torch.manual_seed(5)
+    for log_n, nb, inc, B in [(12, 2, True, 37), (10, 3, False, 64), (13, 1, True, 9), (5, 1, True, 3)]:
+        n = 1 << log_n
+        S = 2
+        for insz, outsz in [(n, n), (n // 2 + 32 if n >= 64 else n, n - 32 if n >= 64 else n)]:
+            tw = (torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5).to(dev)
+            x = torch.randn(B, S, insz, dtype=dtype).to(dev)
+            g = torch.randn(B, S, outsz, dtype=dtype).to(dev)
+            y0, _ = abi.fw(tw, x, inc, outsz)
+            dt0, dx0, _ = abi.bw(tw, x, g, inc)
+            y1, snaps, _ = abi.fw_saving(tw, x, inc, outsz)
+            dt1, dx1, _ = abi.bw_saved(tw, x, g, snaps, inc)
+            torch.cuda.synchronize()
+            assert torch.equal(y0[:, :, :outsz], y1[:, :, :outsz])
+            assert torch.equal(dx0[:, :, :insz], dx1[:, :, :insz])
+            assert rel_err(dt1, dt0) < 1e-5
+            # autograd operator, saving on and off
+            res = {}
+            for mode in ("1", "0"):
+                monkeypatch.setenv("BFLY_AUTOGRAD_SAVE", mode)
+                twp = tw.clone().requires_grad_(True)
+                xp = x.clone().requires_grad_(True)
+                y = bb.butterfly_multiply(twp, xp, inc, outsz)
+                y.backward(g)
+                res[mode] = (y.detach(), twp.grad, xp.grad)
+            assert torch.equal(res["1"][0], res["0"][0]) and torch.equal(res["1"][2], res["0"][2])
+            assert rel_err(res["1"][1], res["0"][1]) < 1e-5
+            assert torch.equal(res["1"][0], y0[:, :, :outsz]) and torch.equal(res["1"][2], dx0[:, :, :insz])
+
+
 @pytest.mark.parametrize("logc", [7, 9, 10])
 def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, logc):
     """The multi-pass forward (environment switch BFLY_FW_LOGCMAX) must give what the one-pass
