@@ -149,23 +149,62 @@ template <typename T, int KW, int NSG> struct BwOcc {
   static constexpr int kMinBlocks = (sizeof(T) == 4 && KW == 2 && NSG <= 3) ? 2 : 1;
 };
 
+// Tile traffic goes through the TMA unit when the three tensors can be described to it (p.tma),
+// as in the second-generation kernel below; otherwise every thread copies 16-byte chunks.
 template <typename T, int KW, int NSG, int LOGC, int RB>
-__global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks)) bfly_bw_kernel(const __grid_constant__ BwParams<T> p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks))
+bfly_bw_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ CUtensorMap map_x,
+               const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_o) {
+  extern __shared__ __align__(16) unsigned char smem_dyn[];
+  unsigned char* smem_raw = smem_dyn + ((1024u - (tma_smem(smem_dyn) & 1023u)) & 1023u);
   T* smX = reinterpret_cast<T*>(smem_raw);
   const int C = 1 << p.panel.logC;
   T* smG = smX + (size_t)p.nsg * p.Rb * C;
+  const uint32_t bar = tma_smem(smG + (size_t)p.Rb * C), bar_g = bar + 8;  // after the tiles (16-byte multiples)
   const int tid = threadIdx.x;
   int pbase, stack, row_begin, row_end;
   bw_cta_coords(p, blockIdx.x, pbase, stack, row_begin, row_end);
+  if (p.tma) {
+    if (tid == 0) {
+      mbar_init(bar, 1);
+      mbar_init(bar_g, 1);
+      fence_async_smem();
+    }
+    __syncthreads();
+  }
   BwState<T, KW, NSG> st;
   bw_load_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
+  const uint32_t tile_bytes = (uint32_t)((size_t)p.Rb * C * sizeof(T));
+  const int pbf = pbase * p.tma_f;
+  const int c1 = (pbf & ((1 << p.tma_pbe) - 1)) >> 5, c2 = pbf >> p.tma_pbe;
+  auto issue_load_x = [&](int row0) {
+    mbar_expect_tx(bar, tile_bytes);
+    tma_load_tile(tma_smem(smX), &map_x, bar, c1, c2, p.tma_sx ? stack : 0, row0);
+  };
+  auto issue_load_g = [&](int row0) {
+    mbar_expect_tx(bar_g, tile_bytes);
+    tma_load_tile(tma_smem(smG), &map_g, bar_g, c1, c2, p.tma_sg ? stack : 0, row0);
+  };
+  uint32_t parity = 0;
+  if (p.tma && tid == 0 && row_begin < row_end) {
+    issue_load_x(row_begin);
+    issue_load_g(row_begin);
+  }
   for (int row0 = row_begin; row0 < row_end; row0 += p.Rb) {
     const int R = p.Rb;
-    tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
-    tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
-    tile_load_wait();
-    __syncthreads();
+    if (p.tma) {
+      const bool ok = mbar_wait(bar, parity) && mbar_wait(bar_g, parity);
+      parity ^= 1;
+      if (__syncthreads_or(!ok)) {  // uniform decision: give up on this CTA's rows
+        if (tid == 0) atomicExch(&g_device_error, 1);
+        break;
+      }
+    } else {
+      tile_load_auto<T>(p.xin, p.xin_sB, p.xin_sS, p.xin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_x != 0, smX, tid, kThreads);
+      tile_load_auto<T>(p.gin, p.gin_sB, p.gin_sS, p.gin_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_g != 0, smG, tid, kThreads);
+      tile_load_wait();
+      __syncthreads();
+    }
 #pragma unroll
     for (int j = 0; j < NSG - 1; ++j) {
       if (j + 1 < p.nsg) {
@@ -177,12 +216,27 @@ __global__ void __launch_bounds__(kThreads, (BwOcc<T, KW, NSG>::kMinBlocks)) bfl
     for (int j = NSG - 1; j >= 0; --j) {
       if (j < p.nsg) {
         bw_sg_step<T, KW, NSG, LOGC, RB, false>(p, st, j, stack, smX, smG, R, tid, kThreads);
+        if (p.tma && j == 0) fence_async_smem();  // the gradient tile is read by the TMA unit next
         __syncthreads();
       }
     }
-    tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
-    __syncthreads();
+    if (p.tma) {
+      if (tid == 0) {
+        const bool more = row0 + p.Rb < row_end;
+        if (more) issue_load_x(row0 + p.Rb);  // the snapshot tiles are free already
+        tma_store_tile(&map_o, tma_smem(smG), c1, c2, p.tma_so ? stack : 0, row0);
+        tma_store_commit();
+        if (more) {
+          tma_store_wait_read();  // the gradient tile is free again
+          issue_load_g(row0 + p.Rb);
+        }
+      }
+    } else {
+      tile_store_auto<T>(p.gout, p.gout_sB, p.gout_sS, p.gout_cols, row_end, stack, row0, R, p.panel, pbase, p.vec_o != 0, smG, tid, kThreads);
+      __syncthreads();
+    }
   }
+  if (p.tma && tid == 0) tma_store_wait_all();
   bw_flush_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
 }
 
@@ -401,18 +455,7 @@ struct CudaExec {
     if (rc) return rc;
     // describe the three tensors to the TMA unit when they qualify; else per-thread copies
     CUtensorMap mx, mg, mo;
-    std::memset(&mx, 0, sizeof(mx)); std::memset(&mg, 0, sizeof(mg)); std::memset(&mo, 0, sizeof(mo));
-    constexpr int F = (int)(sizeof(T) / 4);
-    const TmaGeom geo = tma_geometry(p.panel, p.log_n, kBw2Rows, F);
-    p.tma = 0;
-    if (use_tma() && geo.ok && p.vec_x && p.vec_g && p.vec_o &&
-        tma_describe(&mx, geo, p.xin, p.xin_sB, p.xin_sS, p.xin_cols, p.B, p.S, F) &&
-        tma_describe(&mg, geo, p.gin, p.gin_sB, p.gin_sS, p.gin_cols, p.B, p.S, F) &&
-        tma_describe(&mo, geo, p.gout, p.gout_sB, p.gout_sS, p.gout_cols, p.B, p.S, F)) {
-      p.tma = 1;
-      p.tma_sx = (p.S > 1 && p.xin_sS != 0); p.tma_sg = (p.S > 1 && p.gin_sS != 0); p.tma_so = (p.S > 1 && p.gout_sS != 0);
-      p.tma_pbe = geo.pbe; p.tma_f = F;
-    }
+    describe_bw(p, kBw2Rows, mx, mg, mo);
     {
       ProfileScope prof(kKernBw, stream);
       bfly_bw2_kernel<T, KW, LOGC><<<bw_num_ctas(p), kThreads, smem, stream>>>(p, mx, mg, mo);
@@ -463,12 +506,15 @@ struct CudaExec {
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
   }
   // Instances with the tile shape fixed at compile time exist for the shapes the row planner
-  // picks for n = 4096 and n = 1024 float rows at two CTAs per SM; everything else runs the
-  // generic instance.
+  // picks for n = 4096 and n = 1024 float rows and n = 2048 complex rows at two CTAs per SM;
+  // everything else runs the generic instance.
   template <typename T, int KMAX> int launch_fw_shape(const FwParams<T>& p) {
     if constexpr (sizeof(T) == 4 && KMAX == KernelCfg<T>::kFwKmaxTwoCtas) {
       if (p.panel.logC == 12 && p.R == 6) return launch_fw<T, KMAX, 12, 6>(p);
       if (p.panel.logC == 10 && p.R == 16) return launch_fw<T, KMAX, 10, 16>(p);
+    }
+    if constexpr (sizeof(T) == 8 && KMAX == KernelCfg<T>::kFwKmaxTwoCtas) {
+      if (p.panel.logC == 11 && p.R == 6) return launch_fw<T, KMAX, 11, 6>(p);  // 2048 complex columns
     }
     return launch_fw<T, KMAX, 0, 0>(p);
   }
@@ -479,13 +525,32 @@ struct CudaExec {
     return launch_fw_shape<T, KernelCfg<T>::kFwKmaxOneCta>(p);
   }
 
-  template <typename T, int KW, int NSG, int LOGC, int RB> int launch_bw(const BwParams<T>& p) {
-    const size_t smem = (size_t)(p.nsg + 1) * p.Rb * sizeof(T) << p.panel.logC;
+  // Describe the three tensors of a backward phase to the TMA unit; p.tma says whether all qualify.
+  template <typename T> void describe_bw(BwParams<T>& p, int rows, CUtensorMap& mx, CUtensorMap& mg, CUtensorMap& mo) {
+    std::memset(&mx, 0, sizeof(mx)); std::memset(&mg, 0, sizeof(mg)); std::memset(&mo, 0, sizeof(mo));
+    constexpr int F = (int)(sizeof(T) / 4);
+    const TmaGeom geo = tma_geometry(p.panel, p.log_n, rows, F);
+    p.tma = 0;
+    if (use_tma() && geo.ok && p.vec_x && p.vec_g && p.vec_o && p.B >= rows &&
+        tma_describe(&mx, geo, p.xin, p.xin_sB, p.xin_sS, p.xin_cols, p.B, p.S, F) &&
+        tma_describe(&mg, geo, p.gin, p.gin_sB, p.gin_sS, p.gin_cols, p.B, p.S, F) &&
+        tma_describe(&mo, geo, p.gout, p.gout_sB, p.gout_sS, p.gout_cols, p.B, p.S, F)) {
+      p.tma = 1;
+      p.tma_sx = (p.S > 1 && p.xin_sS != 0); p.tma_sg = (p.S > 1 && p.gin_sS != 0); p.tma_so = (p.S > 1 && p.gout_sS != 0);
+      p.tma_pbe = geo.pbe; p.tma_f = F;
+    }
+  }
+
+  template <typename T, int KW, int NSG, int LOGC, int RB> int launch_bw(const BwParams<T>& p_in) {
+    BwParams<T> p = p_in;
+    const size_t smem = ((size_t)(p.nsg + 1) * p.Rb * sizeof(T) << p.panel.logC) + 16 + 1024;  // two mbarriers, alignment slack
     int rc = set_smem(bfly_bw_kernel<T, KW, NSG, LOGC, RB>, smem);
     if (rc) return rc;
+    CUtensorMap mx, mg, mo;
+    describe_bw(p, p.Rb, mx, mg, mo);
     {
       ProfileScope prof(kKernBw, stream);
-      bfly_bw_kernel<T, KW, NSG, LOGC, RB><<<bw_num_ctas(p), kThreads, smem, stream>>>(p);
+      bfly_bw_kernel<T, KW, NSG, LOGC, RB><<<bw_num_ctas(p), kThreads, smem, stream>>>(p, mx, mg, mo);
     }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
