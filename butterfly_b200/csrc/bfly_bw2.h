@@ -324,7 +324,7 @@ BFLY_HD void bw2_flush(const BwParams<T>& p, const AccStore<T, KW>& accs, const 
     if (sg.radix == 4) {
       if constexpr (KW == 2) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) atomic_add_el(dtw + t0 + e, acc[e]);
+        for (int b = 0; b < 4; ++b) atomic_add_block(dtw + t0 + b * 4, acc + b * 4);
       }
     } else {
       const int wg = p.panel.global_bit(sg.lbit);
@@ -334,10 +334,7 @@ BFLY_HD void bw2_flush(const BwParams<T>& p, const AccStore<T, KW>& accs, const 
         if (s < sg.nst) {
 #pragma unroll
           for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              atomic_add_el(dtw + (s == 0 ? t0 : t1) + (uint32_t)((pp << wg) * 4) + e,
-                            acc[s * (1 << (KW - 1)) * 4 + pp * 4 + e]);
+            atomic_add_block(dtw + (s == 0 ? t0 : t1) + (uint32_t)((pp << wg) * 4), acc + s * (1 << (KW - 1)) * 4 + pp * 4);
         }
       }
     }

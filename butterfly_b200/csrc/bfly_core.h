@@ -722,16 +722,22 @@ BFLY_HD void bw_load_state(const BwParams<T>& p, BwState<T, KW, NSG>& st, int st
   bw_fetch_tw<T, KW, NSG>(p, st, 0, stack);
 }
 
-BFLY_HD void atomic_add_el(float* dst, float v) {
+// Add one 2x2 block (four elements, 16-byte aligned) of accumulators to d_twiddle: one vector
+// reduction per 16 bytes instead of one per scalar.
+BFLY_HD void atomic_add_block(float* dst, const float* v) {
 #if defined(__CUDA_ARCH__)
-  atomicAdd(dst, v);
+  asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
 #else
-  *dst += v;
+  for (int e = 0; e < 4; ++e) dst[e] += v[e];
 #endif
 }
-BFLY_HD void atomic_add_el(cf* dst, cf v) {
-  atomic_add_el(&dst->re, v.re);
-  atomic_add_el(&dst->im, v.im);
+BFLY_HD void atomic_add_block(cf* dst, const cf* v) {
+#if defined(__CUDA_ARCH__)
+  asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0].re), "f"(v[0].im), "f"(v[1].re), "f"(v[1].im) : "memory");
+  asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(dst + 2), "f"(v[2].re), "f"(v[2].im), "f"(v[3].re), "f"(v[3].im) : "memory");
+#else
+  for (int e = 0; e < 4; ++e) { dst[e].re += v[e].re; dst[e].im += v[e].im; }
+#endif
 }
 
 template <typename T, int KW, int NSG>
@@ -745,7 +751,7 @@ BFLY_HD void bw_flush_state(const BwParams<T>& p, const BwState<T, KW, NSG>& st,
       if (sg.radix == 4) {
         if constexpr (KW == 2) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) atomic_add_el(dtw + st.twi[j][0] + e, st.acc[j][e]);
+          for (int b = 0; b < 4; ++b) atomic_add_block(dtw + st.twi[j][0] + b * 4, st.acc[j] + b * 4);
         }
       } else {
         const int wg = p.panel.global_bit(sg.lbit);
@@ -754,10 +760,7 @@ BFLY_HD void bw_flush_state(const BwParams<T>& p, const BwState<T, KW, NSG>& st,
           if (s < sg.nst) {
 #pragma unroll
             for (int pp = 0; pp < (1 << (KW - 1)); ++pp)
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                atomic_add_el(dtw + st.twi[j][s] + (uint32_t)((pp << wg) * 4) + e,
-                              st.acc[j][s * (1 << (KW - 1)) * 4 + pp * 4 + e]);
+              atomic_add_block(dtw + st.twi[j][s] + (uint32_t)((pp << wg) * 4), st.acc[j] + s * (1 << (KW - 1)) * 4 + pp * 4);
           }
         }
       }

@@ -264,6 +264,7 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
   twiddle_stack_sizes(q, stk);
   if ((stk[0] && (!tw2 || !d_tw2)) || (stk[1] && (!tw4 || !d_tw4))) return BFLY_E_ARG;
   if ((tw2 && !aligned16(tw2)) || (tw4 && !aligned16(tw4))) return BFLY_E_ALIGN;
+  if ((d_tw2 && !aligned16(d_tw2)) || (d_tw4 && !aligned16(d_tw4))) return BFLY_E_ALIGN;  // 16-byte vector reductions
   if (stk[0]) { rc = ex.zero(d_tw2, (size_t)q.S * stk[0] * sizeof(T)); if (rc) return rc; }
   if (stk[1]) { rc = ex.zero(d_tw4, (size_t)q.S * stk[1] * sizeof(T)); if (rc) return rc; }
   if (q.B == 0) return BFLY_OK;
