@@ -22,6 +22,7 @@
  *             with rows wider than 16 KB -- n > 4096 float32, > 2048 complex64 -- run in several
  *             passes and use the columns beyond output_size as working space)
  *   grad      (batch, nstacks, output_size), strides g_sB / g_sS, last dim contiguous
+ *   d_twiddle (d_twiddle4, d_twiddle2): like the twiddle they belong to, 16-byte aligned
  *   d_x       (batch, nstacks, max(input_size, n)) contiguous; columns < input_size
  *             hold the input gradient (columns >= n of them are zero)
  * Input columns >= n are ignored, missing ones (input_size < n) read as zero, exactly as
@@ -40,7 +41,7 @@ extern "C" {
 #define BFLY_OK 0
 #define BFLY_E_ARG (-1)          /* inconsistent sizes or a null pointer */
 #define BFLY_E_UNSUPPORTED (-2)  /* shape outside what the kernels cover */
-#define BFLY_E_ALIGN (-3)        /* twiddle pointer not 16-byte aligned */
+#define BFLY_E_ALIGN (-3)        /* twiddle or d_twiddle pointer not 16-byte aligned */
 #define BFLY_E_WORKSPACE (-4)    /* workspace missing, misaligned or too small */
 #define BFLY_E_CUDA (-5)         /* a CUDA runtime call or launch failed */
 #define BFLY_E_NODEVICE (-6)     /* no usable CUDA device */
