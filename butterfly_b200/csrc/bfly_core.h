@@ -416,21 +416,19 @@ BFLY_HD void fw_group(const FwParams<T>& p, int gi, T* __restrict__ sm, const ui
     const int col0 = pn.col(pbase, lbase);
     const int a0 = swzT<T>(lbase);
     T tw[NST * PER];
+    // Twiddle index of the unit: its column with one window bit (radix 2; two bits for radix 4)
+    // deleted.  The window bits of col0 are all zero, so the result does not depend on which of
+    // them goes -- it is the same for every stage of the group -- and the pairs (quads) of a
+    // stage lie 2^wg blocks apart.  Addresses are formed as (uniform pointer) + (32-bit index).
+    constexpr int DEL = R4 ? 2 : 1;          // window bits a stage removes from the column index
+    constexpr int BLK = R4 ? 16 : 4;         // twiddle scalars per pair (quad)
+    const uint32_t ib = (uint32_t)((((col0 >> (wg + K)) << (wg + K - DEL)) | (col0 & ((1 << wg) - 1))) * BLK);
 #pragma unroll
     for (int s = 0; s < NST; ++s) {
-      if constexpr (!R4) {
-        const int q = (PAT == kR2Inc) ? s : K - 1 - s;
-        const int ibase = delete_bit(col0, wg + q);
+      const uint32_t es = g.tw_off[s] + ib;
 #pragma unroll
-        for (int pp = 0; pp < E / 2; ++pp)
-          load_tw<T, 4>(tw + s * PER + pp * 4, twbase + g.tw_off[s] + (uint32_t)(ibase + (pp << wg)) * 4u);
-      } else {
-        const int q = (PAT == kR4Inc) ? 2 * s : K - 2 - 2 * s;
-        const int ibase = delete_2bits(col0, wg + q);
-#pragma unroll
-        for (int pp = 0; pp < E / 4; ++pp)
-          load_tw<T, 16>(tw + s * PER + pp * 16, twbase + g.tw_off[s] + (uint32_t)(ibase + (pp << wg)) * 16u);
-      }
+      for (int pp = 0; pp < (E >> DEL); ++pp)
+        load_tw<T, BLK>(tw + s * PER + pp * BLK, (twbase + (size_t)(pp << wg) * BLK) + es);
     }
     // byte offsets of the unit's elements (scalar path) or chunks (vector path) inside a tile row
     int off[NA];
