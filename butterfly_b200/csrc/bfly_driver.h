@@ -207,6 +207,9 @@ template <typename T> struct BwLayout {
   std::vector<BwPhase> phases;
   int kw;
   size_t ws_bytes;
+  // more phases than one forward launch can write snapshots for: the backward then runs in
+  // chunks of kMaxSnap phases, each with its own forward pass from the input
+  bool chunked;
 };
 
 template <typename T>
@@ -217,9 +220,11 @@ int plan_bw(const Problem& q, BwLayout<T>& lay) {
   while ((1 << logCmax) < (KernelCfg<T>::kThreads << lay.kw)) ++logCmax;
   lay.phases = plan_bw_phases(st, q.log_n, logCmax, lay.kw, KernelCfg<T>::bw_max_sg(lay.kw), Vec16<T>::LOG);
   if (lay.phases.empty()) return BFLY_E_UNSUPPORTED;
-  if ((int)lay.phases.size() - 1 > kMaxSnap) return BFLY_E_UNSUPPORTED;
+  lay.chunked = (int)lay.phases.size() - 1 > kMaxSnap;
   const size_t plane = (size_t)q.B * q.S * sizeof(T) << q.log_n;
-  lay.ws_bytes = (lay.phases.size() - 1) * ((plane + 255) / 256 * 256);
+  // chunked: kMaxSnap snapshots plus one plane the forward passes of the later chunks work on
+  const size_t planes = lay.chunked ? (size_t)kMaxSnap + 1 : lay.phases.size() - 1;
+  lay.ws_bytes = planes * ((plane + 255) / 256 * 256);
   return BFLY_OK;
 }
 
@@ -244,9 +249,11 @@ int drive_fw_saving(E& ex, const Problem& q, const T* tw2, const T* tw4, const T
   const size_t plane_pad = (plane + 255) / 256 * 256;
   T* snaps[kMaxSnap] = {nullptr};
   std::vector<int> cuts;
-  for (int ph = 1; ph < nph; ++ph) {
-    snaps[ph - 1] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
-    cuts.push_back(lay.phases[ph].t0);
+  if (!lay.chunked) {  // a chunked backward recomputes its snapshots chunk by chunk: nothing to save
+    for (int ph = 1; ph < nph; ++ph) {
+      snaps[ph - 1] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
+      cuts.push_back(lay.phases[ph].t0);
+    }
   }
   return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size, out,
                            (int64_t)q.S * n, n, q.out_size);
@@ -278,29 +285,41 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
   const int nph = (int)lay.phases.size();
   const size_t plane = ((size_t)q.B * q.S * sizeof(T) << q.log_n);
   const size_t plane_pad = (plane + 255) / 256 * 256;
+  const int64_t DX = std::max<int64_t>(q.in_size, n);
+  if (lay.chunked) snapshots_ready = false;
+  // Phases run last to first.  Normally one forward launch writes every phase-boundary activation
+  // and all phases follow; a product with more phases than snapshot slots runs in chunks of
+  // kMaxSnap phases, each preceded by its own forward pass from the input.
+  for (int pb = nph; pb > 0;) {
+  const int pa = lay.chunked ? std::max(0, pb - kMaxSnap) : 0;
+  const int first = std::max(pa, 1);  // phase 0 enters with x itself
   T* snaps[kMaxSnap] = {nullptr};
   std::vector<int> cuts;
-  for (int ph = 1; ph < nph; ++ph) {
-    snaps[ph - 1] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
+  for (int ph = first; ph < pb; ++ph) {
+    snaps[ph - first] = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)(ph - first) * plane_pad);
     cuts.push_back(lay.phases[ph].t0);
   }
-  if (nph > 1 && !snapshots_ready) {
-    // the snapshot pass of a product with wide rows (several forward passes) works in place on
-    // d_x, which no phase has written yet
-    const int64_t DXs = std::max<int64_t>(q.in_size, n);
-    rc = drive_fw_range<T>(ex, q, st, 0, lay.phases[nph - 1].t0, cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size,
-                           (T*)nullptr, 0, 0, 0, d_x, (int64_t)q.S * DXs, DXs);
+  if (!cuts.empty() && !snapshots_ready) {
+    // the forward pass of a product with wide rows (several launches over panels) works in place
+    // on d_x while no phase has written it yet, afterwards on the spare plane of the workspace
+    T* scratch = d_x;
+    int64_t scr_sB = (int64_t)q.S * DX, scr_sS = DX;
+    if (pb != nph) {
+      scratch = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)kMaxSnap * plane_pad);
+      scr_sB = (int64_t)q.S * n; scr_sS = n;
+    }
+    rc = drive_fw_range<T>(ex, q, st, 0, lay.phases[pb - 1].t0, cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size,
+                           (T*)nullptr, 0, 0, 0, scratch, scr_sB, scr_sS);
     if (rc != BFLY_OK) return rc;
   }
-  const int64_t DX = std::max<int64_t>(q.in_size, n);
-  for (int ph = nph - 1; ph >= 0; --ph) {
+  for (int ph = pb - 1; ph >= pa; --ph) {
     const BwPhase& P = lay.phases[ph];
     BwParams<T> p;
     std::memset(&p, 0, sizeof(p));
     p.tw[0] = tw2; p.tw[1] = tw4; p.dtw[0] = d_tw2; p.dtw[1] = d_tw4;
     p.tw_stack[0] = stk[0]; p.tw_stack[1] = stk[1];
     if (ph == 0) { p.xin = x; p.xin_sB = x_sB; p.xin_sS = x_sS; p.xin_cols = q.in_size; }
-    else { p.xin = snaps[ph - 1]; p.xin_sB = (int64_t)q.S * n; p.xin_sS = n; p.xin_cols = (int)n; }
+    else { p.xin = snaps[ph - first]; p.xin_sB = (int64_t)q.S * n; p.xin_sS = n; p.xin_cols = (int)n; }
     if (ph == nph - 1) { p.gin = grad; p.gin_sB = g_sB; p.gin_sS = g_sS; p.gin_cols = q.out_size; }
     else { p.gin = d_x; p.gin_sB = (int64_t)q.S * DX; p.gin_sS = DX; p.gin_cols = (int)n; }
     p.gout = d_x; p.gout_sB = (int64_t)q.S * DX; p.gout_sS = DX;
@@ -345,6 +364,8 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     p.vec_o = vec_ok<T>(p.gout, p.gout_sB, p.gout_sS);
     rc = ex.run_bw(p, lay.kw);
     if (rc != BFLY_OK) return rc;
+  }
+  pb = pa;
   }
   if (q.in_size > n) {
     rc = ex.zero2d(d_x + n, (size_t)DX * sizeof(T), (size_t)(q.in_size - n) * sizeof(T), (size_t)q.B * q.S);

@@ -19,8 +19,9 @@
  *             element strides of the batch and stack dims (x_sS may be 0: one row
  *             broadcast to every stack, as Butterfly.pre_process's expand() produces)
  *   out       (batch, nstacks, n) contiguous; only columns < output_size are written (products
- *             with rows wider than 16 KB -- n > 4096 float32, > 2048 complex64 -- run in several
- *             passes and use the columns beyond output_size as working space)
+ *             with rows wider than 16 KB -- n > 4096 float32, > 2048 complex64 -- or of more than
+ *             about 120 stages run as several launches and use the columns beyond output_size as
+ *             working space)
  *   grad      (batch, nstacks, output_size), strides g_sB / g_sS, last dim contiguous
  *   d_twiddle (d_twiddle4, d_twiddle2): like the twiddle they belong to, 16-byte aligned
  *   d_x       (batch, nstacks, max(input_size, n)) contiguous; columns < input_size

@@ -173,6 +173,27 @@ def test_forward_that_saves_snapshots_feeds_the_backward(emul, oracle_mod, dtype
             assert rel_err(d_tw, dtr) < 2e-5 and rel_err(dx[:, :, :insz], dxr) < 2e-5
 
 
+def test_backward_in_chunks_of_phases(emul, oracle_mod):
+    """More phases than one forward launch has snapshot slots for (here 9 and 11 blocks of 8 stages
+    at n = 256): the backward runs in chunks, each with its own forward pass from the input."""
+    torch.manual_seed(3)
+    log_n, S, B = 8, 2, 5
+    n = 1 << log_n
+    for nb, inc in [(11, True), (9, False), (19, True)]:
+        tw = torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
+        x = torch.randn(B, S, n - 3)
+        g = torch.randn(B, S, n - 7)
+        # products of more than 40 stage groups run as several forward launches, in place on `out`
+        y = emul_fw(emul, tw, None, x, inc, n - 7, log_n, nb, False, 64, tail_untouched=False)
+        assert rel_err(y, oracle_mod.multiply_fw(tw, x, inc, n - 7)) < 5e-5
+        d2, _, dx = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, 64)
+        dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+        assert rel_err(d2, dtr) < 5e-5 and rel_err(dx, dxr) < 5e-5
+    ws = ctypes.c_int64(0)
+    assert emul.bfly_emul_bw_plan(0, 0, 16, 1, 10, 9, 1, ctypes.byref(ws)) > 9  # 90 stages: chunked
+    assert ws.value == 9 * 16 * 1024 * 4
+
+
 def test_backward_phase_plan_sizes(emul):
     ws = ctypes.c_int64(0)
     # float: a phase holds at most 8 stages (4 sub-groups of 2) on a panel of 1024 columns

@@ -208,6 +208,27 @@ def test_saving_forward_and_saved_backward(abi, dev, oracle_mod, monkeypatch, dt
             assert torch.equal(res["1"][0], y0[:, :, :outsz]) and torch.equal(res["1"][2], dx0[:, :, :insz])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
+def test_many_blocks_backward_in_chunks(abi, dev, oracle_mod, dtype):
+    """More backward phases than one forward launch has snapshot slots for (10 blocks at n = 1024:
+    100 stages): the backward runs in chunks of phases, each with its own forward pass."""
+    torch.manual_seed(31)
+    log_n, nb, S, B = 10, 10, 1, 19
+    n = 1 << log_n
+    for inc in (True, False):
+        tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+        x = torch.randn(B, S, n, dtype=dtype)
+        g = torch.randn(B, S, n - 32, dtype=dtype)
+        yr = oracle_mod.multiply_fw(tw, x, inc, n - 32)
+        dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+        out, _ = abi.fw(tw.to(dev), x.to(dev), inc, n - 32)
+        d_tw, d_x, _ = abi.bw(tw.to(dev), x.to(dev), g.to(dev), inc)
+        y2, snaps, _ = abi.fw_saving(tw.to(dev), x.to(dev), inc, n - 32)
+        dt2, dx2, _ = abi.bw_saved(tw.to(dev), x.to(dev), g.to(dev), snaps, inc)
+        for a, b in ((out[:, :, :n - 32], yr), (d_tw, dtr), (d_x, dxr), (y2[:, :, :n - 32], yr), (dt2, dtr), (dx2, dxr)):
+            assert rel_err(a, b) < 1e-4  # 100 stages of float32 round-off
+
+
 @pytest.mark.parametrize("logc", [7, 9, 10])
 def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, logc):
     """The multi-pass forward (environment switch BFLY_FW_LOGCMAX) must give what the one-pass
