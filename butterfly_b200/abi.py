@@ -20,7 +20,7 @@ SYMBOLS = (
     "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
-    "bfly_device_error", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
+    "bfly_device_error", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -199,7 +199,7 @@ def bw_noalloc(twiddle, x, grad, increasing_stride=True, d_twiddle=None, d_x=Non
 
 
 def fw_base4(twiddle4, twiddle2, x, increasing_stride=True, output_size=None, out=None, check=True):
-    """``bfly4_fw_f32``."""
+    """``bfly4_fw_f32`` / ``bfly4_fw_c64``."""
     _check_rows(x)
     S, nblocks = twiddle4.shape[:2]
     log_n = twiddle4.shape[2] * 2 + twiddle2.shape[2]
@@ -208,7 +208,8 @@ def fw_base4(twiddle4, twiddle2, x, increasing_stride=True, output_size=None, ou
     output_size = n if output_size is None else output_size
     if out is None:
         out = torch.empty(B, S, n, dtype=x.dtype, device=x.device)
-    rc = lib().bfly4_fw_f32(_p(twiddle4), _p(twiddle2), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(B),
+    fn = lib().bfly4_fw_f32 if x.dtype == torch.float32 else lib().bfly4_fw_c64
+    rc = fn(_p(twiddle4), _p(twiddle2), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(B),
                             int(S), int(log_n), int(nblocks), int(in_size), int(output_size),
                             int(bool(increasing_stride)), _stream())
     if check and rc != 0:
@@ -217,7 +218,7 @@ def fw_base4(twiddle4, twiddle2, x, increasing_stride=True, output_size=None, ou
 
 
 def bw_base4(twiddle4, twiddle2, x, grad, increasing_stride=True, workspace=None, check=True):
-    """``bfly4_bw_f32``.  Returns (d_twiddle4, d_twiddle2, d_x buffer, status)."""
+    """``bfly4_bw_f32`` / ``bfly4_bw_c64``.  Returns (d_twiddle4, d_twiddle2, d_x buffer, status)."""
     _check_rows(x)
     _check_rows(grad)
     S, nblocks = twiddle4.shape[:2]
@@ -236,7 +237,8 @@ def bw_base4(twiddle4, twiddle2, x, grad, increasing_stride=True, workspace=None
     if workspace is None and need > 0:
         workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
     ws_bytes = 0 if workspace is None else workspace.numel()
-    rc = lib().bfly4_bw_f32(_p(twiddle4), _p(twiddle2), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(grad),
+    fn = lib().bfly4_bw_f32 if x.dtype == torch.float32 else lib().bfly4_bw_c64
+    rc = fn(_p(twiddle4), _p(twiddle2), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(grad),
                             _i64(grad.stride(0)), _i64(grad.stride(1)), _p(d4), _p(d2), _p(d_x), int(B), int(S),
                             int(log_n), int(nblocks), int(in_size), int(out_size), int(bool(increasing_stride)),
                             _p(workspace), ctypes.c_size_t(ws_bytes), _stream())

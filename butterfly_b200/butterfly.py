@@ -262,7 +262,7 @@ class ButterflyBmm(Butterfly):
 
 class ButterflyBase4(Butterfly):
     """Butterfly stored as radix-4 factors (twiddle4) plus one radix-2 factor per block when log_n is
-    odd (twiddle2); multiplies with the native base-4 operator (float32)."""
+    odd (twiddle2); multiplies with the native base-4 operator (float32 or complex64)."""
 
     def __init__(self, *args, init="randn", **kwargs):
         init_pair = None

@@ -21,7 +21,7 @@ template <> struct KernelCfg<float> {
   static constexpr int kFwKmaxTwoCtas = 3;  // widest window that still fits two CTAs per SM
   static constexpr int kFwKmaxOneCta = 4;   // widest window at one CTA per SM
   static constexpr int kThreads = 256;
-  static int bw_kw(int log_n) { return log_n >= 2 ? 2 : 1; }
+  static int bw_kw(int log_n, bool /*base4*/) { return log_n >= 2 ? 2 : 1; }
   static int bw_max_sg(int kw) {
     if (kw != 2) return 10;
     if (const char* e = std::getenv("BFLY_BW_MAXSG")) {  // experiments: other phase lengths
@@ -35,8 +35,10 @@ template <> struct KernelCfg<cf> {
   static constexpr int kFwKmaxTwoCtas = 2;
   static constexpr int kFwKmaxOneCta = 3;
   static constexpr int kThreads = 256;
-  static int bw_kw(int) { return 1; }
-  static int bw_max_sg(int) { return 10; }
+  // one-stage sub-groups for radix-2 products; a radix-4 factor needs the 2-bit window, and the
+  // 16 complex accumulators per sub-group leave room for two sub-groups per phase
+  static int bw_kw(int log_n, bool base4) { return (base4 && log_n >= 2) ? 2 : 1; }
+  static int bw_max_sg(int kw) { return kw == 2 ? 2 : 10; }
 };
 
 // Launch shape of the forward kernel.  The defaults (two CTAs per SM, windows of up to 3 bits
@@ -215,7 +217,7 @@ template <typename T> struct BwLayout {
 template <typename T>
 int plan_bw(const Problem& q, BwLayout<T>& lay) {
   const std::vector<Stage> st = problem_stages(q);
-  lay.kw = KernelCfg<T>::bw_kw(q.log_n);
+  lay.kw = KernelCfg<T>::bw_kw(q.log_n, q.base4);
   int logCmax = 0;
   while ((1 << logCmax) < (KernelCfg<T>::kThreads << lay.kw)) ++logCmax;
   lay.phases = plan_bw_phases(st, q.log_n, logCmax, lay.kw, KernelCfg<T>::bw_max_sg(lay.kw), Vec16<T>::LOG);

@@ -571,6 +571,7 @@ struct CudaExec {
     return launch_bw<float, 1, 10, 0, 0>(p);
   }
   int run_bw(const BwParams<cf>& p, int KW) {
+    if (KW == 2) return p.nsg <= 2 ? launch_bw<cf, 2, 2, 0, 0>(p) : BFLY_E_UNSUPPORTED;  // radix-4 factors
     if (KW != 1) return BFLY_E_UNSUPPORTED;
     if (p.panel.logC == 9) {
       if (p.nsg >= 9 && p.Rb == 4) return launch_bw<cf, 1, 10, 9, 4>(p);
@@ -651,7 +652,7 @@ static int64_t ws_entry(bool base4, int dtype, int B, int S, int log_n, int nblo
   int rc = check_problem(q);
   if (rc) return rc;
   if (dtype == BFLY_F32) return ws_for<float>(q);
-  if (dtype == BFLY_C64 && !base4) return ws_for<cf>(q);
+  if (dtype == BFLY_C64) return ws_for<cf>(q);
   return BFLY_E_UNSUPPORTED;
 }
 
@@ -824,6 +825,20 @@ int bfly4_fw_f32(const float* twiddle4, const float* twiddle2, const float* x, i
                  int increasing_stride, void* stream) {
   return fw_entry<float>(true, twiddle2, twiddle4, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks,
                          input_size, output_size, increasing_stride, stream);
+}
+int bfly4_fw_c64(const void* twiddle4, const void* twiddle2, const void* x, int64_t x_sB, int64_t x_sS, void* out,
+                 int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                 int increasing_stride, void* stream) {
+  return fw_entry<cf>(true, twiddle2, twiddle4, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks, input_size,
+                      output_size, increasing_stride, stream);
+}
+int bfly4_bw_c64(const void* twiddle4, const void* twiddle2, const void* x, int64_t x_sB, int64_t x_sS,
+                 const void* grad, int64_t g_sB, int64_t g_sS, void* d_twiddle4, void* d_twiddle2, void* d_x,
+                 int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                 int increasing_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  return bw_entry<cf>(true, twiddle2, twiddle4, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle2, d_twiddle4, d_x, batch,
+                      nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
+                      workspace_bytes, stream);
 }
 int64_t bfly4_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks) {
   return ws_entry(true, dtype, batch, nstacks, log_n, nblocks);

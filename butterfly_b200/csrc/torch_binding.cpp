@@ -239,9 +239,9 @@ Base4Shape base4_shape(const Tensor& twiddle4, const Tensor& twiddle2, const Ten
   if (s.log_n % 2 == 1)
     TORCH_CHECK(twiddle2.sizes() == torch::IntArrayRef({s.nstacks, s.nblocks, 1, s.n / 2, 2, 2}),
                 "twiddle2 must have shape (nstacks, nblocks, 1, n / 2, 2, 2)");
-  TORCH_CHECK(input.scalar_type() == at::kFloat && twiddle4.scalar_type() == at::kFloat &&
-                  twiddle2.scalar_type() == at::kFloat,
-              what, " not implemented for '", toString(input.scalar_type()), "' (float32 only)");
+  TORCH_CHECK((input.scalar_type() == at::kFloat || input.scalar_type() == at::kComplexFloat) &&
+                  twiddle4.scalar_type() == input.scalar_type() && twiddle2.scalar_type() == input.scalar_type(),
+              what, " not implemented for '", toString(input.scalar_type()), "' (float32 and complex64 only, one dtype)");
   return s;
 }
 
@@ -255,10 +255,17 @@ Tensor butterfly_multiply_base4_fw(const Tensor& twiddle4, const Tensor& twiddle
   const Tensor x = rows_view(input);
   Tensor output = torch::empty({s.batch, s.nstacks, s.n}, input.options());
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int rc = bfly4_fw_f32(t4.numel() ? t4.data_ptr<float>() : nullptr, t2.numel() ? t2.data_ptr<float>() : nullptr,
-                              x.data_ptr<float>(), x.stride(0), x.stride(1), output.data_ptr<float>(), (int)s.batch,
-                              (int)s.nstacks, (int)s.log_n, (int)s.nblocks, (int)s.input_size, (int)out_size,
-                              increasing_stride, stream.stream());
+  int rc;
+  if (input.scalar_type() == at::kFloat) {
+    rc = bfly4_fw_f32(t4.numel() ? t4.data_ptr<float>() : nullptr, t2.numel() ? t2.data_ptr<float>() : nullptr,
+                      x.data_ptr<float>(), x.stride(0), x.stride(1), output.data_ptr<float>(), (int)s.batch,
+                      (int)s.nstacks, (int)s.log_n, (int)s.nblocks, (int)s.input_size, (int)out_size,
+                      increasing_stride, stream.stream());
+  } else {
+    rc = bfly4_fw_c64(t4.numel() ? t4.data_ptr() : nullptr, t2.numel() ? t2.data_ptr() : nullptr, x.data_ptr(),
+                      x.stride(0), x.stride(1), output.data_ptr(), (int)s.batch, (int)s.nstacks, (int)s.log_n,
+                      (int)s.nblocks, (int)s.input_size, (int)out_size, increasing_stride, stream.stream());
+  }
   check_status(rc, "butterfly_multiply_base4_fw");
   return out_size < s.n ? output.slice(2, 0, out_size) : output;
 }
@@ -271,22 +278,33 @@ std::tuple<Tensor, Tensor, Tensor> butterfly_multiply_base4_bw(const Tensor& twi
   const int64_t out_size = grad.size(2);
   TORCH_CHECK(grad.sizes() == torch::IntArrayRef({s.batch, s.nstacks, out_size}) && out_size <= s.n,
               "grad must have shape (batch_size, nstacks, output_size) with output_size <= n");
-  TORCH_CHECK(grad.scalar_type() == at::kFloat, "grad must be float32");
+  TORCH_CHECK(grad.scalar_type() == input.scalar_type(), "grad must have the dtype of input");
   c10::cuda::CUDAGuard guard(input.device());
   const Tensor t4 = dense_twiddle(twiddle4), t2 = dense_twiddle(twiddle2);
   const Tensor x = rows_view(input), g = rows_view(grad);
   Tensor d4 = torch::empty_like(t4), d2 = torch::empty_like(t2);
   Tensor d_input = torch::empty({s.batch, s.nstacks, std::max(s.input_size, s.n)}, input.options());
-  const int64_t ws_bytes = bfly4_bw_workspace_bytes(BFLY_F32, (int)s.batch, (int)s.nstacks, (int)s.log_n, (int)s.nblocks);
+  const bool real = input.scalar_type() == at::kFloat;
+  const int64_t ws_bytes = bfly4_bw_workspace_bytes(real ? BFLY_F32 : BFLY_C64, (int)s.batch, (int)s.nstacks, (int)s.log_n,
+                                                    (int)s.nblocks);
   TORCH_CHECK(ws_bytes >= 0, "butterfly_multiply_base4_bw failed: ", bfly_strerror((int)ws_bytes));
   Tensor ws = torch::empty({ws_bytes}, input.options().dtype(at::kByte));
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int rc = bfly4_bw_f32(t4.numel() ? t4.data_ptr<float>() : nullptr, t2.numel() ? t2.data_ptr<float>() : nullptr,
-                              x.data_ptr<float>(), x.stride(0), x.stride(1), g.data_ptr<float>(), g.stride(0), g.stride(1),
-                              d4.numel() ? d4.data_ptr<float>() : nullptr, d2.numel() ? d2.data_ptr<float>() : nullptr,
-                              d_input.data_ptr<float>(), (int)s.batch, (int)s.nstacks, (int)s.log_n, (int)s.nblocks,
-                              (int)s.input_size, (int)out_size, increasing_stride, ws_bytes ? ws.data_ptr() : nullptr,
-                              (size_t)ws_bytes, stream.stream());
+  int rc;
+  if (real) {
+    rc = bfly4_bw_f32(t4.numel() ? t4.data_ptr<float>() : nullptr, t2.numel() ? t2.data_ptr<float>() : nullptr,
+                      x.data_ptr<float>(), x.stride(0), x.stride(1), g.data_ptr<float>(), g.stride(0), g.stride(1),
+                      d4.numel() ? d4.data_ptr<float>() : nullptr, d2.numel() ? d2.data_ptr<float>() : nullptr,
+                      d_input.data_ptr<float>(), (int)s.batch, (int)s.nstacks, (int)s.log_n, (int)s.nblocks,
+                      (int)s.input_size, (int)out_size, increasing_stride, ws_bytes ? ws.data_ptr() : nullptr,
+                      (size_t)ws_bytes, stream.stream());
+  } else {
+    rc = bfly4_bw_c64(t4.numel() ? t4.data_ptr() : nullptr, t2.numel() ? t2.data_ptr() : nullptr, x.data_ptr(),
+                      x.stride(0), x.stride(1), g.data_ptr(), g.stride(0), g.stride(1),
+                      d4.numel() ? d4.data_ptr() : nullptr, d2.numel() ? d2.data_ptr() : nullptr, d_input.data_ptr(),
+                      (int)s.batch, (int)s.nstacks, (int)s.log_n, (int)s.nblocks, (int)s.input_size, (int)out_size,
+                      increasing_stride, ws_bytes ? ws.data_ptr() : nullptr, (size_t)ws_bytes, stream.stream());
+  }
   check_status(rc, "butterfly_multiply_base4_bw");
   if (s.input_size < s.n) d_input = d_input.slice(2, 0, s.input_size);
   return std::make_tuple(d4, d2, d_input);

@@ -127,6 +127,14 @@ int bfly_bw_f32_noalloc(const float* twiddle, const float* x, int64_t x_sB, int6
 int bfly4_fw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB,
                  int64_t x_sS, float* out, int batch, int nstacks, int log_n, int nblocks,
                  int input_size, int output_size, int increasing_stride, void* stream);
+int bfly4_fw_c64(const void* twiddle4, const void* twiddle2, const void* x, int64_t x_sB, int64_t x_sS,
+                 void* out, int batch, int nstacks, int log_n, int nblocks, int input_size,
+                 int output_size, int increasing_stride, void* stream);
+int bfly4_bw_c64(const void* twiddle4, const void* twiddle2, const void* x, int64_t x_sB,
+                 int64_t x_sS, const void* grad, int64_t g_sB, int64_t g_sS, void* d_twiddle4,
+                 void* d_twiddle2, void* d_x, int batch, int nstacks, int log_n, int nblocks,
+                 int input_size, int output_size, int increasing_stride, void* workspace,
+                 size_t workspace_bytes, void* stream);
 int64_t bfly4_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks);
 int bfly4_bw_f32(const float* twiddle4, const float* twiddle2, const float* x, int64_t x_sB,
                  int64_t x_sS, const float* grad, int64_t g_sB, int64_t g_sS, float* d_twiddle4,

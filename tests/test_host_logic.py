@@ -84,17 +84,18 @@ def test_radix2_plan_and_indexing(emul, oracle_mod, dtype, log_n):
             assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
 @pytest.mark.parametrize("log_n", [1, 2, 3, 4, 5, 6, 7, 10, 11])
-def test_base4_plan_and_indexing(emul, oracle_mod, log_n):
+def test_base4_plan_and_indexing(emul, oracle_mod, log_n, dtype):
     torch.manual_seed(100 + log_n)
     n = 1 << log_n
     for nb, inc in [(1, True), (1, False), (2, True), (3, False)]:
         S, B = 2, 4
         for insz, outsz in [(n, n), (max(1, n // 2 - 1), max(1, n - 5)), (2 * n + 7, max(1, n // 2 - 2))]:
-            tw4 = torch.randn(S, nb, log_n // 2, n // 4, 4, 4) / 2
-            tw2 = torch.randn(S, nb, log_n % 2, n // 2, 2, 2) / 2 ** 0.5
-            x = torch.randn(B, S, insz)
-            g = torch.randn(B, S, outsz)
+            tw4 = torch.randn(S, nb, log_n // 2, n // 4, 4, 4, dtype=dtype) / 2
+            tw2 = torch.randn(S, nb, log_n % 2, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+            x = torch.randn(B, S, insz, dtype=dtype)
+            g = torch.randn(B, S, outsz, dtype=dtype)
             y = emul_fw(emul, tw2, tw4, x, inc, outsz, log_n, nb, True)
             assert rel_err(y, oracle_mod.base4_fw(tw4, tw2, x, inc, outsz)) < 2e-5
             d2, d4, dx = emul_bw(emul, tw2, tw4, x, g, inc, log_n, nb, True)

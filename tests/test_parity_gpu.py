@@ -65,7 +65,8 @@ def test_golden_radix2_through_c_abi(abi, dev, path):
         assert (d_x[:, :, n:d["input_size"]] == 0).all()
 
 
-@pytest.mark.parametrize("path", [p for p in golden_files("base4") if "_f32_" in p], ids=lambda p: p.split("/")[-1])
+@pytest.mark.parametrize("path", [p for p in golden_files("base4") if "_f32_" in p or "_c64_" in p],
+                         ids=lambda p: p.split("/")[-1])
 def test_golden_base4_through_c_abi(abi, dev, path):
     d = load_golden(path)
     t4, t2, x, g = d["twiddle4"].to(dev), d["twiddle2"].to(dev), d["input"].to(dev), d["grad"].to(dev)
@@ -261,8 +262,9 @@ def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, log
     assert rel_err(y2, y1) < 1e-6  # window widths (and so the FMA grouping) may differ between tilings
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
 @pytest.mark.parametrize("log_n", [1, 2, 3, 6, 7, 10, 11, 14])
-def test_base4_sweep_against_oracle(abi, dev, oracle_mod, log_n):
+def test_base4_sweep_against_oracle(abi, dev, oracle_mod, log_n, dtype):
     torch.manual_seed(50 + log_n)
     n = 1 << log_n
     for nb, inc in [(1, True), (2, False), (3, True)]:
@@ -270,10 +272,10 @@ def test_base4_sweep_against_oracle(abi, dev, oracle_mod, log_n):
             continue
         S, B = (2, 19) if log_n < 14 else (1, 5)
         for insz, outsz in [(n, n), (max(1, n // 2 - 1), max(1, n - 5))]:
-            tw4 = torch.randn(S, nb, log_n // 2, n // 4, 4, 4) / 2
-            tw2 = torch.randn(S, nb, log_n % 2, n // 2, 2, 2) / 2 ** 0.5
-            x = torch.randn(B, S, insz)
-            g = torch.randn(B, S, outsz)
+            tw4 = torch.randn(S, nb, log_n // 2, n // 4, 4, 4, dtype=dtype) / 2
+            tw2 = torch.randn(S, nb, log_n % 2, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+            x = torch.randn(B, S, insz, dtype=dtype)
+            g = torch.randn(B, S, outsz, dtype=dtype)
             yr = oracle_mod.base4_fw(tw4, tw2, x, inc, outsz)
             d4r, d2r, dxr = oracle_mod.base4_bw(tw4, tw2, x, g, inc)
             out, _ = abi.fw_base4(tw4.to(dev), tw2.to(dev), x.to(dev), inc, outsz)
