@@ -110,6 +110,20 @@ def test_to_base4_and_unitary_and_scaling(dev):
         y = b(x)
         b *= 3.0
         assert torch.allclose((b(x) - b.bias) , 3.0 * (y - b.bias), rtol=1e-4, atol=1e-4)
+    # complex layers: the base-4 form runs the complex64 base-4 operator, forward and backward
+    for n, nblocks in [(32, 1), (64, 2)]:
+        b = bb.Butterfly(n, n, bias=False, complex=True, nblocks=nblocks).to(dev)
+        b4 = b.to_base4()
+        x = torch.randn(9, n, dtype=torch.complex64, device=dev)
+        xa = x.clone().requires_grad_(True)
+        xb = x.clone().requires_grad_(True)
+        ya, yb = b(xa), b4(xb)
+        assert torch.allclose(ya, yb, rtol=1e-4, atol=1e-4)
+        w = torch.randn_like(ya)
+        (ya * w).real.sum().backward()
+        (yb * w).real.sum().backward()
+        assert torch.allclose(xa.grad, xb.grad, rtol=1e-4, atol=1e-4)
+        assert b4.twiddle4.grad is not None and torch.isfinite(torch.view_as_real(b4.twiddle4.grad)).all()
     u = bb.ButterflyUnitary(32, 32, bias=False, nblocks=2).to(dev)
     m = _matrix(u, 32, torch.complex64, dev)
     assert torch.allclose(m @ m.t().conj(), torch.eye(32, dtype=torch.complex64, device=dev), atol=1e-5)
