@@ -20,7 +20,7 @@ LIB_OPS = os.path.join(HERE, "_butterfly.so")
 LIB_VERSION = os.path.join(HERE, "_version.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared"]
+              "-Xcompiler", "-fPIC"]
 
 
 def _newer(target, sources):
@@ -43,10 +43,26 @@ def build(force=False, verbose=False):
     if not os.path.exists(nvcc):
         nvcc = "nvcc"
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
-    core_src = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".h"))]
-    core_src.append(os.path.join(HERE, "..", "include", "bfly.h"))
-    if force or _newer(LIB_CORE, core_src):
-        _run([nvcc] + NVCC_FLAGS + [os.path.join(CSRC, "bfly_kernels.cu"), "-o", LIB_CORE], verbose)
+    headers = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".h")]
+    headers.append(os.path.join(HERE, "..", "include", "bfly.h"))
+    units = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu")]
+    # one object per translation unit (compiled side by side), linked into one library
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    objs, jobs = [], []
+    for cu in units:
+        obj = os.path.join(objdir, os.path.basename(cu)[:-3] + ".o")
+        objs.append(obj)
+        if force or _newer(obj, [cu] + headers):
+            cmd = [nvcc] + NVCC_FLAGS + ["-c", cu, "-o", obj]
+            if verbose:
+                print(" ".join(cmd), file=sys.stderr)
+            jobs.append((cmd, subprocess.Popen(cmd)))
+    for cmd, proc in jobs:
+        if proc.wait() != 0:
+            raise subprocess.CalledProcessError(proc.returncode, cmd)
+    if force or jobs or _newer(LIB_CORE, objs):
+        _run([nvcc, "-shared", "-o", LIB_CORE] + objs, verbose)
 
     tdir = os.path.dirname(torch.__file__)
     inc = ["-I" + os.path.join(tdir, "include"), "-I" + os.path.join(tdir, "include", "torch", "csrc", "api", "include"),

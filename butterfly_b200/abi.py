@@ -17,10 +17,10 @@ F32, C64 = 0, 1
 
 # every symbol include/bfly.h declares
 SYMBOLS = (
-    "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64",
+    "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64", "bfly_fw_workspace_bytes",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
-    "bfly_device_error", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
+    "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -38,6 +38,7 @@ def lib():
         L.bfly_strerror.restype = ctypes.c_char_p
         L.bfly_strerror.argtypes = [ctypes.c_int]
         L.bfly_bw_workspace_bytes.restype = ctypes.c_int64
+        L.bfly_fw_workspace_bytes.restype = ctypes.c_int64
         L.bfly4_bw_workspace_bytes.restype = ctypes.c_int64
         L.bfly_launch_count.restype = ctypes.c_int64
         _lib = L
@@ -70,8 +71,16 @@ def _check_rows(t):
     assert t.is_cuda and t.dim() == 3 and (t.size(2) <= 1 or t.stride(2) == 1)
 
 
-def fw(twiddle, x, increasing_stride=True, output_size=None, out=None, check=True):
-    """``bfly_fw_f32`` / ``bfly_fw_c64``.  Returns the (batch, nstacks, n) output buffer and the status."""
+def fw_workspace_bytes(dtype, B, S, log_n, nblocks):
+    code = F32 if dtype == torch.float32 else C64
+    return int(lib().bfly_fw_workspace_bytes(code, int(B), int(S), int(log_n), int(nblocks)))
+
+
+def fw(twiddle, x, increasing_stride=True, output_size=None, out=None, check=True, workspace="auto"):
+    """``bfly_fw_f32`` / ``bfly_fw_c64``.  Returns the (batch, nstacks, n) output buffer and the status.
+
+    ``workspace``: a uint8 CUDA tensor of ``fw_workspace_bytes`` bytes, ``None`` (the call then runs on
+    the generic kernel) or ``"auto"`` (allocated here when the shape can use one)."""
     _check_rows(x)
     S, nblocks, log_n = twiddle.shape[:3]
     n = 1 << log_n
@@ -79,9 +88,14 @@ def fw(twiddle, x, increasing_stride=True, output_size=None, out=None, check=Tru
     output_size = n if output_size is None else output_size
     if out is None:
         out = torch.empty(B, S, n, dtype=x.dtype, device=x.device)
+    if isinstance(workspace, str):
+        need = fw_workspace_bytes(x.dtype, B, S, log_n, nblocks)
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device) if need > 0 else None
+    ws_bytes = 0 if workspace is None else workspace.numel()
     fn = lib().bfly_fw_f32 if x.dtype == torch.float32 else lib().bfly_fw_c64
     rc = fn(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(B), int(S), int(log_n),
-            int(nblocks), int(in_size), int(output_size), int(bool(increasing_stride)), _stream())
+            int(nblocks), int(in_size), int(output_size), int(bool(increasing_stride)), _p(workspace),
+            ctypes.c_size_t(ws_bytes), _stream())
     if check and rc != 0:
         raise BflyError(rc, "bfly_fw")
     return out, rc
@@ -247,12 +261,28 @@ def bw_base4(twiddle4, twiddle2, x, grad, increasing_stride=True, workspace=None
     return d4, d2, d_x, rc
 
 
+def set_option(name, value):
+    """``bfly_set_option``: change a development / test switch of the library (see include/bfly.h)."""
+    rc = lib().bfly_set_option(name.encode(), int(value))
+    if rc != 0:
+        raise BflyError(rc, "bfly_set_option(%s)" % name)
+
+
+def get_option(name):
+    v = ctypes.c_int(0)
+    rc = lib().bfly_get_option(name.encode(), ctypes.byref(v))
+    if rc != 0:
+        raise BflyError(rc, "bfly_get_option(%s)" % name)
+    return int(v.value)
+
+
 def launch_count():
     return int(lib().bfly_launch_count())
 
 
 def device_error():
-    """1 if a kernel gave up on a bounded wait since the last call (its output is invalid), else 0."""
+    """Non-zero if a kernel gave up since the last call (its output is invalid): 1 = a bounded wait
+    ran out, 2 = misaligned shared-memory window; else 0."""
     rc = int(lib().bfly_device_error())
     if rc < 0:
         raise BflyError(rc, "bfly_device_error")

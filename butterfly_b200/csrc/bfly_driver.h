@@ -6,15 +6,80 @@
 //   bool has_bw2(size_t elem_size, int kw) const;          // second-generation backward kernel available
 //   int  threads() const;                                  // threads per CTA of its kernels
 //   int  run_fw(const FwParams<T>&);                       // one forward launch
+//   int  run_fw2(const Fw2Params&, int ctas_per_sm);       // twiddle re-ordering + one launch of the packed-pair
+//                                                          // forward kernel (kFw2Declined: not available for these tensors)
 //   int  run_bw(const BwParams<T>&, int KW);               // one backward-phase launch
 //   int  zero(void* ptr, size_t bytes);                    // async memset
 //   int  zero2d(void* ptr, size_t pitch_bytes, size_t width_bytes, size_t rows);
 #pragma once
 #include <cstdlib>
+#include <cstring>
 
+#include "bfly_fw2.h"
 #include "bfly_plan.h"
 
 namespace bfly {
+
+// Development and test switches.  They are read from the environment once, when first used
+// (BFLY_TMA, BFLY_BW_V2, BFLY_FW2, BFLY_FW_KMAX, BFLY_FW_ROWS, BFLY_FW_LOGCMAX, BFLY_BW_ROWS,
+// BFLY_BW_MAXSG, BFLY_AUTOGRAD_SAVE), and can be changed afterwards with set_option() (C ABI: bfly_set_option); the
+// launch path itself never touches the environment.  -1 = not set (planner's default).
+struct Options {
+  int tma = 1;          // tile traffic through the TMA unit where tensors qualify
+  int bw_v2 = 1;        // second-generation backward phase kernel
+  int fw2 = 1;          // packed-pair forward kernel
+  int fw2_ctas = -1;    // packed-pair forward kernel: CTAs per SM (1 or 2; default 2)
+  int fw_kmax = -1;     // generic forward: widest register window
+  int fw_rows = -1;     // generic forward: rows per tile
+  int fw_logcmax = -1;  // generic forward: widest panel (log2 columns) of a pass
+  int bw_rows = -1;     // backward: rows per batch
+  int bw_maxsg = -1;    // backward: sub-groups per phase
+  int autograd_save = -1;  // torch autograd operator: keep the forward's snapshots for the backward
+};
+struct OptionName { const char* name; const char* env; int Options::*field; };
+inline const OptionName* option_names(int* count) {
+  static const OptionName names[] = {
+      {"tma", "BFLY_TMA", &Options::tma},           {"bw_v2", "BFLY_BW_V2", &Options::bw_v2},
+      {"fw2", "BFLY_FW2", &Options::fw2},           {"fw_kmax", "BFLY_FW_KMAX", &Options::fw_kmax},
+      {"fw2_ctas", "BFLY_FW2_CTAS", &Options::fw2_ctas},
+      {"fw_rows", "BFLY_FW_ROWS", &Options::fw_rows}, {"fw_logcmax", "BFLY_FW_LOGCMAX", &Options::fw_logcmax},
+      {"bw_rows", "BFLY_BW_ROWS", &Options::bw_rows}, {"bw_maxsg", "BFLY_BW_MAXSG", &Options::bw_maxsg},
+      {"autograd_save", "BFLY_AUTOGRAD_SAVE", &Options::autograd_save},
+  };
+  *count = (int)(sizeof(names) / sizeof(names[0]));
+  return names;
+}
+inline Options& options() {
+  static Options opt = [] {
+    Options o;
+    int cnt = 0;
+    const OptionName* names = option_names(&cnt);
+    for (int i = 0; i < cnt; ++i)
+      if (const char* e = std::getenv(names[i].env)) o.*(names[i].field) = std::atoi(e);
+    return o;
+  }();
+  return opt;
+}
+inline int set_option(const char* name, int value) {
+  int cnt = 0;
+  const OptionName* names = option_names(&cnt);
+  for (int i = 0; name && i < cnt; ++i)
+    if (std::strcmp(names[i].name, name) == 0) {
+      options().*(names[i].field) = value;
+      return BFLY_OK;
+    }
+  return BFLY_E_ARG;
+}
+inline int get_option(const char* name, int* value) {
+  int cnt = 0;
+  const OptionName* names = option_names(&cnt);
+  for (int i = 0; name && value && i < cnt; ++i)
+    if (std::strcmp(names[i].name, name) == 0) {
+      *value = options().*(names[i].field);
+      return BFLY_OK;
+    }
+  return BFLY_E_ARG;
+}
 
 template <typename T> struct KernelCfg;
 template <> struct KernelCfg<float> {
@@ -24,10 +89,8 @@ template <> struct KernelCfg<float> {
   static int bw_kw(int log_n, bool /*base4*/) { return log_n >= 2 ? 2 : 1; }
   static int bw_max_sg(int kw) {
     if (kw != 2) return 10;
-    if (const char* e = std::getenv("BFLY_BW_MAXSG")) {  // experiments: other phase lengths
-      const int v = std::atoi(e);
-      if (v >= 1 && v <= 5) return v;
-    }
+    const int v = options().bw_maxsg;  // experiments: other phase lengths
+    if (v >= 1 && v <= 5) return v;
     return 4;  // 8 stages per phase: twiddles and accumulators of 4 sub-groups fill a thread's 128 TMEM columns
   }
 };
@@ -43,22 +106,26 @@ template <> struct KernelCfg<cf> {
 
 // Launch shape of the forward kernel.  The defaults (two CTAs per SM, windows of up to 3 bits
 // for float / 2 for complex; for float radix-4 products 4-bit windows, which hold two radix-4
-// stages, at one CTA per SM) can be overridden for experiments with the environment variables
-// BFLY_FW_KMAX (window bits) and BFLY_FW_ROWS (rows per tile).
+// stages, at one CTA per SM) can be overridden for experiments with the options fw_kmax (window
+// bits) and fw_rows (rows per tile).
 struct FwTuning { int kmax, ctas_per_sm, max_rows; };
 template <typename T> inline FwTuning fw_tuning(bool base4) {
   FwTuning t{KernelCfg<T>::kFwKmaxTwoCtas, 2, 16};
   if (base4 && sizeof(T) == 4) t.kmax = KernelCfg<T>::kFwKmaxOneCta;
-  if (const char* e = std::getenv("BFLY_FW_KMAX")) {
-    const int k = std::atoi(e);
-    if (k >= 1 && k <= KernelCfg<T>::kFwKmaxOneCta) t.kmax = k;
-  }
+  const int k = options().fw_kmax;
+  if (k >= 1 && k <= KernelCfg<T>::kFwKmaxOneCta) t.kmax = k;
   if (t.kmax > KernelCfg<T>::kFwKmaxTwoCtas) t.ctas_per_sm = 1;
-  if (const char* e = std::getenv("BFLY_FW_ROWS")) {
-    const int r = std::atoi(e);
-    if (r >= 1 && r <= 64) t.max_rows = r;
-  }
+  const int r = options().fw_rows;
+  if (r >= 1 && r <= 64) t.max_rows = r;
   return t;
+}
+
+// The packed-pair forward kernel steps aside when it is switched off or when a switch asks for
+// something only the generic forward kernel does (per-thread tile copies, forced panels or tile
+// shapes).
+inline bool fw2_enabled() {
+  const Options& o = options();
+  return o.fw2 != 0 && o.tma != 0 && o.fw_logcmax < 0 && o.fw_kmax < 0 && o.fw_rows < 0;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -96,15 +163,48 @@ inline void twiddle_stack_sizes(const Problem& q, int64_t out[2]) {
 // to that width run in one pass; wider rows would leave too few rows per tile to amortise the
 // twiddle fetches (and beyond 227 KB would not fit at all), so they run as several passes over
 // panels, which measures 1.3x (n = 8192) to 2.7x (n = 16384) faster than one pass with 3 or 1
-// rows per tile.  BFLY_FW_LOGCMAX forces narrower panels (tests run the multi-pass path at small n).
+// rows per tile.  The option fw_logcmax forces narrower panels (tests run the multi-pass path at small n).
 template <typename T> inline int fw_pass_logc(int log_n) {
   int lc = sizeof(T) == 4 ? 12 : 11;
   if (log_n < lc) lc = log_n;
-  if (const char* e = std::getenv("BFLY_FW_LOGCMAX")) {
-    const int v = std::atoi(e);
-    if (v >= 3 && v < lc) lc = v;
-  }
+  const int v = options().fw_logcmax;
+  if (v >= 3 && v < lc) lc = v;
   return lc;
+}
+
+// Stages [t0, t1) through the packed-pair forward kernel (bfly_fw2.h).  Returns kFw2Declined when
+// the shape, the stage list or the tensors do not qualify.
+template <typename E>
+int drive_fw2(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int t1, const std::vector<int>& cuts,
+              float* const* snaps, const float* tw2, const float* x, int64_t x_sB, int64_t x_sS, int x_cols, float* out,
+              int64_t out_sB, int64_t out_sS, int out_cols, void* pack_ws, size_t pack_bytes) {
+  if (q.base4 || !tw2 || !pack_ws || !fw2_enabled()) return kFw2Declined;
+  std::vector<Fw2Group> groups;
+  if (!plan_fw2_groups(st, t0, t1, cuts, q.log_n, groups)) return kFw2Declined;
+  if ((int)cuts.size() > kFw2MaxSnap) return kFw2Declined;
+  Fw2Params p;
+  std::memset(&p, 0, sizeof(p));
+  int64_t stk[2];
+  twiddle_stack_sizes(q, stk);
+  p.tw = tw2; p.tw_stack = stk[0];
+  p.B = q.B; p.S = q.S; p.log_n = q.log_n;
+  const int ctas = options().fw2_ctas == 1 ? 1 : 2;
+  p.P = kFw2Threads / ((1 << q.log_n) / 16);
+  p.Rw = fw2_rows_per_thread(q.B, q.S, p.P, ctas * ex.num_sms(), ctas == 1 ? 14 : 7);
+  p.R = p.P * p.Rw;
+  p.packed = static_cast<float*>(pack_ws);
+  p.packed_stack = (int64_t)groups.back().pk_off + (int64_t)groups.back().nst * 8 * ((1 << q.log_n) / 16);
+  if ((size_t)p.packed_stack * q.S * 16 > pack_bytes) return kFw2Declined;
+  p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
+  p.out = out; p.out_sB = out_sB; p.out_sS = out_sS; p.out_cols = out_cols;
+  for (int i = 0; i < kFw2MaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
+  p.ngroups = (int)groups.size();
+  for (int g = 0; g < p.ngroups; ++g) {
+    p.g[g] = groups[g];
+    if (groups[g].sync == 2 || (groups[g].emit && !groups[g].local)) p.cta_syncs = 1;
+  }
+  if (!groups.back().local) p.cta_syncs = 1;
+  return ex.run_fw2(p, ctas);
 }
 
 // Run stages [t0, t1) of the product with the row-owner forward kernel.  `cuts` lists the
@@ -116,8 +216,15 @@ template <typename T, typename E>
 int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int t1,
                    const std::vector<int>& cuts, T* const* snaps, const T* tw2, const T* tw4, const T* x,
                    int64_t x_sB, int64_t x_sS, int x_cols, T* out, int64_t out_sB, int64_t out_sS,
-                   int out_cols, T* scratch = nullptr, int64_t scratch_sB = 0, int64_t scratch_sS = 0) {
+                   int out_cols, T* scratch = nullptr, int64_t scratch_sB = 0, int64_t scratch_sS = 0,
+                   void* pack_ws = nullptr, size_t pack_bytes = 0) {
   if (q.B == 0 || t1 <= t0) return BFLY_OK;
+  if constexpr (sizeof(T) == 4) {
+    // float rows of 512 .. 4096 columns: the packed-pair kernel, when the tensors qualify
+    const int rc2 = drive_fw2(ex, q, st, t0, t1, cuts, snaps, tw2, x, x_sB, x_sS, x_cols, out, out_sB, out_sS, out_cols,
+                              pack_ws, pack_bytes);
+    if (rc2 != kFw2Declined) return rc2;
+  }
   const int lc = fw_pass_logc<T>(q.log_n);
   if (((int64_t)sizeof(T) << lc) > kSmemMax) return BFLY_E_UNSUPPORTED;
   std::vector<FwPass> passes;
@@ -190,7 +297,7 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
 
 template <typename T, typename E>
 int drive_fw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, int64_t x_sB, int64_t x_sS,
-             T* out) {
+             T* out, void* ws = nullptr, size_t ws_bytes = 0) {
   int rc = check_problem(q);
   if (rc != BFLY_OK) return rc;
   if (q.B == 0) return BFLY_OK;
@@ -198,8 +305,16 @@ int drive_fw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
   if ((tw2 && !aligned16(tw2)) || (tw4 && !aligned16(tw4))) return BFLY_E_ALIGN;
   const std::vector<Stage> st = problem_stages(q);
   const int64_t n = (int64_t)1 << q.log_n;
+  if (ws && !aligned16(ws)) ws = nullptr;  // optional scratch: without it the generic kernel runs
   return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), {}, nullptr, tw2, tw4, x, x_sB, x_sS, q.in_size,
-                           out, (int64_t)q.S * n, n, q.out_size);
+                           out, (int64_t)q.S * n, n, q.out_size, (T*)nullptr, 0, 0, ws, ws ? ws_bytes : 0);
+}
+
+// Scratch the forward can use (0 = none needed): room for the re-ordered twiddles of the
+// packed-pair kernel.  The forward also runs without it, on the generic kernel.
+template <typename T> inline size_t fw_workspace_bytes(const Problem& q) {
+  if (sizeof(T) != 4 || q.base4) return 0;
+  return fw2_packed_bytes(q.S, q.log_n, q.nblocks);
 }
 
 template <typename T> struct BwLayout;
@@ -208,7 +323,8 @@ template <typename T> int plan_bw(const Problem& q, BwLayout<T>& lay);
 template <typename T> struct BwLayout {
   std::vector<BwPhase> phases;
   int kw;
-  size_t ws_bytes;
+  size_t ws_bytes;    // snapshot planes, then the forward's scratch (fw_workspace_bytes)
+  size_t pack_off, pack_bytes;
   // more phases than one forward launch can write snapshots for: the backward then runs in
   // chunks of kMaxSnap phases, each with its own forward pass from the input
   bool chunked;
@@ -226,7 +342,10 @@ int plan_bw(const Problem& q, BwLayout<T>& lay) {
   const size_t plane = (size_t)q.B * q.S * sizeof(T) << q.log_n;
   // chunked: kMaxSnap snapshots plus one plane the forward passes of the later chunks work on
   const size_t planes = lay.chunked ? (size_t)kMaxSnap + 1 : lay.phases.size() - 1;
-  lay.ws_bytes = planes * ((plane + 255) / 256 * 256);
+  lay.pack_off = planes * ((plane + 255) / 256 * 256);
+  // the forward pass over the earlier phases may use the packed-pair kernel: room for its twiddles
+  lay.pack_bytes = planes > 0 ? (fw_workspace_bytes<T>(q) + 255) / 256 * 256 : 0;
+  lay.ws_bytes = lay.pack_off + lay.pack_bytes;
   return BFLY_OK;
 }
 
@@ -257,8 +376,9 @@ int drive_fw_saving(E& ex, const Problem& q, const T* tw2, const T* tw4, const T
       cuts.push_back(lay.phases[ph].t0);
     }
   }
+  void* pack_ws = lay.pack_bytes ? static_cast<char*>(ws) + lay.pack_off : nullptr;
   return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size, out,
-                           (int64_t)q.S * n, n, q.out_size);
+                           (int64_t)q.S * n, n, q.out_size, (T*)nullptr, 0, 0, pack_ws, lay.pack_bytes);
 }
 
 // Backward of the whole product.  d_x is (B, S, max(in_size, n)) contiguous and doubles as
@@ -310,8 +430,9 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
       scratch = reinterpret_cast<T*>(static_cast<char*>(ws) + (size_t)kMaxSnap * plane_pad);
       scr_sB = (int64_t)q.S * n; scr_sS = n;
     }
+    void* pack_ws = lay.pack_bytes ? static_cast<char*>(ws) + lay.pack_off : nullptr;
     rc = drive_fw_range<T>(ex, q, st, 0, lay.phases[pb - 1].t0, cuts, snaps, tw2, tw4, x, x_sB, x_sS, q.in_size,
-                           (T*)nullptr, 0, 0, 0, scratch, scr_sB, scr_sS);
+                           (T*)nullptr, 0, 0, 0, scratch, scr_sB, scr_sS, pack_ws, lay.pack_bytes);
     if (rc != BFLY_OK) return rc;
   }
   for (int ph = pb - 1; ph >= pa; --ph) {
@@ -340,8 +461,8 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     p.v2 = ex.has_bw2(sizeof(T), lay.kw) && P.nsg <= 4 && U == KernelCfg<T>::kThreads && v2_bytes <= (size_t)(228 * 1024) / 2 - 1024 &&
            q.B >= 4;
     int Rb = (int)(kSmemMax / row_bytes);
-    if (const char* e = std::getenv("BFLY_BW_ROWS")) {  // experiments: rows per batch
-      const int v = std::atoi(e);
+    {
+      const int v = options().bw_rows;  // experiments: rows per batch
       if (v >= 1 && v < Rb) Rb = v;
     }
     if (Rb > 16) Rb = 16;

@@ -1,0 +1,17 @@
+// Entry points of the translation units that hold the shape-specialised kernels; called by the
+// executor in bfly_kernels.cu.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "bfly_fw2.h"
+
+namespace bfly {
+
+// Launch the packed-pair forward kernel (after the small kernel that re-orders the twiddles into
+// p.packed).  Returns BFLY_OK, a negative status, or kFw2Declined when a tensor cannot be
+// described to the TMA unit (the caller then runs the generic kernel).
+// `ctas_per_sm`: 1 or 2 (rows per thread up to 14 or 7).  `err`: device address of the flag that a
+// kernel whose bounded wait ran out raises.  `launches`: kernels launched.
+int fw2_launch(const Fw2Params& p, int ctas_per_sm, int sms, cudaStream_t stream, int* err, int* launches);
+
+}  // namespace bfly

@@ -23,6 +23,7 @@
 #include "bfly_core.h"
 #include "bfly_bw2.h"
 #include "bfly_driver.h"
+#include "bfly_fast.h"
 #include "bfly_tma.h"
 
 namespace bfly {
@@ -39,6 +40,25 @@ template <typename T, int KMAX> struct FwOcc {
 // Set when a bounded wait inside a kernel ran out (the kernel then stops early and its output
 // is invalid); read and cleared by bfly_device_error().
 __device__ int g_device_error = 0;
+
+// Device address of the flag on the current device (looked up once per device).
+static int device_error_ptr(int** out) {
+  static std::mutex mu;
+  static int* cache[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BFLY_E_NODEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_error) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return BFLY_E_CUDA;
+    }
+    cache[dev] = static_cast<int*>(p);
+  }
+  *out = cache[dev];
+  return BFLY_OK;
+}
 
 // TMA descriptors of a forward launch (bfly_tma.h): input, output, snapshots.
 struct FwMaps {
@@ -439,14 +459,8 @@ struct CudaExec {
   DeviceInfo dev;
   int num_sms() const { return dev.sms; }
   int threads() const { return kThreads; }
-  static bool use_tma() {
-    if (const char* e = std::getenv("BFLY_TMA")) return std::atoi(e) != 0;
-    return true;
-  }
-  bool has_bw2(size_t elem_size, int kw) const {
-    if (const char* e = std::getenv("BFLY_BW_V2")) return std::atoi(e) != 0 && elem_size == 4 && kw == 2;
-    return elem_size == 4 && kw == 2;
-  }
+  static bool use_tma() { return options().tma != 0; }
+  bool has_bw2(size_t elem_size, int kw) const { return options().bw_v2 != 0 && elem_size == 4 && kw == 2; }
 
   template <typename T, int KW, int LOGC> int launch_bw2(const BwParams<T>& p_in) {
     BwParams<T> p = p_in;
@@ -517,6 +531,18 @@ struct CudaExec {
       if (p.panel.logC == 11 && p.R == 6) return launch_fw<T, KMAX, 11, 6>(p);  // 2048 complex columns
     }
     return launch_fw<T, KMAX, 0, 0>(p);
+  }
+  int run_fw2(const Fw2Params& p, int ctas_per_sm) {
+    int* err = nullptr;
+    int rc = device_error_ptr(&err);
+    if (rc) return rc;
+    int launches = 0;
+    {
+      ProfileScope prof(kKernFw, stream);
+      rc = fw2_launch(p, ctas_per_sm, dev.sms, stream, err, &launches);
+    }
+    if (rc == BFLY_OK) g_launches.fetch_add(launches);
+    return rc;
   }
   template <typename T> int run_fw(const FwParams<T>& p) {
     int kmax = 1;
@@ -597,13 +623,13 @@ static int make_exec(void* stream, CudaExec& ex) {
 template <typename T>
 static int fw_entry(bool base4, const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS,
                     void* out, int B, int S, int log_n, int nblocks, int in_size, int out_size, int inc,
-                    void* stream) {
+                    void* stream, void* ws = nullptr, size_t ws_bytes = 0) {
   CudaExec ex;
   int rc = make_exec(stream, ex);
   if (rc) return rc;
   Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, base4};
   return drive_fw<T>(ex, q, static_cast<const T*>(tw2), static_cast<const T*>(tw4), static_cast<const T*>(x),
-                     x_sB, x_sS, static_cast<T*>(out));
+                     x_sB, x_sS, static_cast<T*>(out), ws, ws_bytes);
 }
 
 template <typename T>
@@ -701,7 +727,9 @@ const char* bfly_strerror(int status) {
   }
 }
 
-int bfly_version(void) { return 100; }
+int bfly_version(void) { return 200; }
+int bfly_set_option(const char* name, int value) { return set_option(name, value); }
+int bfly_get_option(const char* name, int* value) { return get_option(name, value); }
 int bfly_cuda_version(void) { return CUDA_VERSION; }
 int64_t bfly_launch_count(void) { return g_launches.load(); }
 
@@ -711,7 +739,7 @@ int bfly_device_error(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return BFLY_E_CUDA;
   if (cudaMemcpyFromSymbol(&flag, bfly::g_device_error, sizeof(int)) != cudaSuccess) return BFLY_E_CUDA;
   if (flag && cudaMemcpyToSymbol(bfly::g_device_error, &zero, sizeof(int)) != cudaSuccess) return BFLY_E_CUDA;
-  return flag != 0;
+  return flag > 0 ? flag : (flag != 0);
 }
 
 void bfly_profile_enable(int on) {
@@ -741,17 +769,25 @@ int bfly_profile_collect(int64_t* launches, double* total_ms, int n_ids) {
   return rc;
 }
 
+int64_t bfly_fw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks) {
+  Problem q{batch, nstacks, log_n, nblocks, 1, 1, true, false};
+  const int rc = check_problem(q);
+  if (rc) return rc;
+  if (dtype == BFLY_F32) return (int64_t)fw_workspace_bytes<float>(q);
+  if (dtype == BFLY_C64) return (int64_t)fw_workspace_bytes<cf>(q);
+  return BFLY_E_UNSUPPORTED;
+}
 int bfly_fw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, int batch,
                 int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
-                void* stream) {
+                void* workspace, size_t workspace_bytes, void* stream) {
   return fw_entry<float>(false, twiddle, nullptr, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks,
-                         input_size, output_size, increasing_stride, stream);
+                         input_size, output_size, increasing_stride, stream, workspace, workspace_bytes);
 }
 int bfly_fw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, void* out, int batch,
                 int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
-                void* stream) {
+                void* workspace, size_t workspace_bytes, void* stream) {
   return fw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, out, batch, nstacks, log_n, nblocks, input_size,
-                      output_size, increasing_stride, stream);
+                      output_size, increasing_stride, stream, workspace, workspace_bytes);
 }
 int64_t bfly_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks) {
   return ws_entry(false, dtype, batch, nstacks, log_n, nblocks);

@@ -85,14 +85,22 @@ Tensor fw_impl(const Tensor& twiddle, const Tensor& input, bool increasing_strid
                               (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
                               increasing_stride, sp, (size_t)ws_bytes, stream.stream());
     }
-  } else if (dt == BFLY_F32) {
-    rc = bfly_fw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1),
-                     output.data_ptr<float>(), (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
-                     (int)input_size, (int)out_size, increasing_stride, stream.stream());
   } else {
-    rc = bfly_fw_c64(tw.data_ptr(), x.data_ptr(), x.stride(0), x.stride(1), output.data_ptr(), (int)batch,
-                     (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
-                     increasing_stride, stream.stream());
+    // optional scratch of the forward (room for the re-ordered twiddles of its fastest kernel)
+    const int64_t fws = bfly_fw_workspace_bytes(dt, (int)batch, (int)nstacks, (int)log_n, (int)nblocks);
+    TORCH_CHECK(fws >= 0, "butterfly_multiply_fw failed: ", bfly_strerror((int)fws));
+    Tensor ws;
+    if (fws > 0) ws = torch::empty({fws}, input.options().dtype(at::kByte));
+    void* wp = fws > 0 ? ws.data_ptr() : nullptr;
+    if (dt == BFLY_F32) {
+      rc = bfly_fw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1),
+                       output.data_ptr<float>(), (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
+                       (int)input_size, (int)out_size, increasing_stride, wp, (size_t)fws, stream.stream());
+    } else {
+      rc = bfly_fw_c64(tw.data_ptr(), x.data_ptr(), x.stride(0), x.stride(1), output.data_ptr(), (int)batch,
+                       (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
+                       increasing_stride, wp, (size_t)fws, stream.stream());
+    }
   }
   check_status(rc, "butterfly_multiply_fw");
   return out_size < n ? output.slice(2, 0, out_size) : output;
@@ -170,9 +178,11 @@ std::tuple<Tensor, Tensor> butterfly_multiply_bw(const Tensor& twiddle, const Te
 // reference recomputes them, csrc/butterfly.cpp:99-118): that removes one forward-sized pass from
 // every training step at the price of holding (phases - 1) activation-sized buffers per call
 // between forward and backward.  On by default while those buffers stay under 1 GiB per call;
-// BFLY_AUTOGRAD_SAVE=0 always recomputes, =1 always saves.
+// the library option "autograd_save" (environment BFLY_AUTOGRAD_SAVE at load time, or
+// bfly_set_option) = 0 always recomputes, = 1 always saves.
 bool autograd_saves(int64_t snapshot_bytes) {
-  if (const char* e = std::getenv("BFLY_AUTOGRAD_SAVE")) return std::atoi(e) != 0;
+  int v = -1;
+  if (bfly_get_option("autograd_save", &v) == BFLY_OK && v >= 0) return v != 0;
   return snapshot_bytes > 0 && snapshot_bytes <= ((int64_t)1 << 30);
 }
 
@@ -183,12 +193,14 @@ using torch::autograd::variable_list;
 // {twiddle, input} and the direction flag, returns {d_twiddle, d_input, none, none}.
 class ButterflyMultiply : public torch::autograd::Function<ButterflyMultiply> {
  public:
+  // `wants_grad`: a gradient can be asked for later.  The caller decides it, because inside
+  // apply() gradient mode is always off while parameters still report requires_grad: a forward
+  // under torch.no_grad() must not pay for snapshots nobody will read.
   static Tensor forward(AutogradContext* ctx, Tensor twiddle, Tensor input, bool increasing_stride,
-                        c10::optional<int64_t> output_size) {
+                        c10::optional<int64_t> output_size, bool wants_grad) {
     ctx->saved_data["increasing_stride"] = increasing_stride;
     bool save = false;
-    if (twiddle.is_cuda() && input.is_cuda() && twiddle.dim() == 6 && input.dim() == 3 &&
-        (twiddle.requires_grad() || input.requires_grad()) &&
+    if (wants_grad && twiddle.is_cuda() && input.is_cuda() && twiddle.dim() == 6 && input.dim() == 3 &&
         (input.scalar_type() == at::kFloat || input.scalar_type() == at::kComplexFloat)) {
       const int64_t ws = bfly_bw_workspace_bytes(input.scalar_type() == at::kFloat ? BFLY_F32 : BFLY_C64,
                                                  (int)input.size(0), (int)input.size(1), (int)twiddle.size(2),
@@ -208,13 +220,14 @@ class ButterflyMultiply : public torch::autograd::Function<ButterflyMultiply> {
     auto saved = ctx->get_saved_variables();
     auto result = bw_impl(saved[0], saved[1], grad_output[0], ctx->saved_data["increasing_stride"].toBool(),
                           saved.size() > 2 ? &saved[2] : nullptr);
-    return {std::get<0>(result), std::get<1>(result), Tensor(), Tensor()};
+    return {std::get<0>(result), std::get<1>(result), Tensor(), Tensor(), Tensor()};
   }
 };
 
 Tensor butterfly_multiply(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
                           c10::optional<int64_t> output_size) {
-  return ButterflyMultiply::apply(twiddle, input, increasing_stride, output_size);
+  const bool wants_grad = at::GradMode::is_enabled() && (twiddle.requires_grad() || input.requires_grad());
+  return ButterflyMultiply::apply(twiddle, input, increasing_stride, output_size, wants_grad);
 }
 
 // ---------------------------------------------------------------- base-4

@@ -60,19 +60,26 @@ const char* bfly_strerror(int status);
 int bfly_version(void);
 int bfly_cuda_version(void);
 
+/* Scratch bytes the forward can use for this shape (0 = none; dtype is BFLY_F32 or BFLY_C64):
+ * room for a copy of the twiddles re-ordered for the fastest forward kernel (float32 rows of
+ * 512 .. 4096 columns).  Returns a negative status on error. */
+int64_t bfly_fw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks);
+
 /* Forward: out = B_{nblocks-1} ... B_0 x.
  * Replaces butterfly_multiply_fw_cuda (csrc/cuda/butterfly_cuda.h:6-9,
  * csrc/cuda/butterfly_cuda.cu:349-416), reached from the operator
- * torch_butterfly::butterfly_multiply_fw (csrc/butterfly.cpp:20-53). */
+ * torch_butterfly::butterfly_multiply_fw (csrc/butterfly.cpp:20-53).
+ * `workspace` (16-byte aligned, bfly_fw_workspace_bytes long) is optional: with NULL / too few
+ * bytes the call still computes the same result, on the generic (slower) kernel. */
 int bfly_fw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out,
                 int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
-                int increasing_stride, void* stream);
+                int increasing_stride, void* workspace, size_t workspace_bytes, void* stream);
 int bfly_fw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, void* out,
                 int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
-                int increasing_stride, void* stream);
+                int increasing_stride, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Scratch bytes bfly_bw_* needs for this shape (0 when the whole product is one
- * backward phase).  dtype is BFLY_F32 or BFLY_C64.  Returns a negative status on error. */
+ * backward phase; it includes the scratch of the forward pass the backward runs).  dtype is BFLY_F32 or BFLY_C64.  Returns a negative status on error. */
 int64_t bfly_bw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks);
 
 /* Backward: d_twiddle (same layout as twiddle, overwritten) and d_x from grad.
@@ -170,13 +177,23 @@ int bfly_bw_c64_saved(const void* twiddle, const void* x, int64_t x_sB, int64_t 
                       int output_size, int increasing_stride, void* snapshots,
                       size_t snapshot_bytes, void* stream);
 
+/* Development and test switches (no counterpart in the reference).  They are read from the
+ * environment once, when the library first needs them, and can be changed at run time here; the
+ * launch path never reads the environment.  Names (environment variable): "tma" (BFLY_TMA: 0 =
+ * per-thread tile copies instead of the TMA unit), "fw2" (BFLY_FW2: 0 = generic forward kernel
+ * only), "bw_v2" (BFLY_BW_V2), "fw_kmax", "fw_rows", "fw_logcmax", "bw_rows", "bw_maxsg" (planner
+ * overrides; -1 = default), "autograd_save" (BFLY_AUTOGRAD_SAVE: the torch autograd operator keeps
+ * the forward's snapshots: 0 never, 1 always, -1 by size).  Returns BFLY_E_ARG for an unknown name. */
+int bfly_set_option(const char* name, int value);
+int bfly_get_option(const char* name, int* value);
+
 /* Number of kernels the library has launched in this process so far (all entry points). */
 int64_t bfly_launch_count(void);
 
 /* Every wait inside the kernels (on a bulk tensor copy) is bounded; a kernel whose wait ran out
  * stops early, leaves invalid output and raises a flag in device memory.  This call waits for
  * the current device to go idle, returns the flag (0 = no kernel has given up since the last
- * call, 1 = one has) and clears it; a negative status on a CUDA error.  No counterpart in the
+ * call, 1 = a wait ran out, 2 = a kernel found its shared-memory window misaligned) and clears it; a negative status on a CUDA error.  No counterpart in the
  * reference; meant for tests and for hosts that want to double-check a run. */
 int bfly_device_error(void);
 

@@ -47,3 +47,25 @@ def oracle_mod():
     import oracle
     oracle.build()
     return oracle
+
+
+class library_option:
+    """Sets a development switch of libbfly_b200.so (butterfly_b200.abi.set_option) or of the
+    host emulator for the duration of a `with` block and puts the old value back."""
+
+    def __init__(self, setter, getter, name, value):
+        self.setter, self.getter, self.name, self.value = setter, getter, name, value
+
+    def __enter__(self):
+        self.old = self.getter(self.name)
+        self.setter(self.name, self.value)
+        return self
+
+    def __exit__(self, *exc):
+        self.setter(self.name, self.old)
+        return False
+
+
+def abi_option(name, value):
+    from butterfly_b200 import abi
+    return library_option(abi.set_option, abi.get_option, name, value)

@@ -16,6 +16,8 @@ using namespace bfly;
 
 namespace {
 
+long g_fw2_calls = 0;  // launches the emulator ran through the packed-pair forward path
+
 struct EmulExec {
   int sms = 7;       // odd on purpose: exercises ragged row slices
   int threads_ = 64;  // simulated block size (any power of two)
@@ -23,6 +25,48 @@ struct EmulExec {
   int threads() const { return threads_; }
   bool bw2 = true;   // exercise the second-generation backward where the driver selects it
   bool has_bw2(size_t elem_size, int kw) const { return bw2 && elem_size == 4 && kw == 2; }
+
+  // packed-pair forward kernel: boxes copied by plain loops, groups run thread by thread in plan
+  // order (a valid schedule of the device kernel's barriers)
+  bool fw2 = true;
+  int run_fw2(const Fw2Params& p_in, int /*ctas_per_sm*/) {
+    if (!fw2) return kFw2Declined;
+    Fw2Params p = p_in;
+    const int n = 1 << p.log_n;
+    if (p.x_cols % 32 != 0 && p.x_cols < n) return kFw2Declined;  // what the TMA descriptors would refuse
+    if (p.out && p.out_cols % 32 != 0) return kFw2Declined;
+    p.has_out = p.out != nullptr;
+    if (!p.has_out) p.out_cols = n;
+    ++g_fw2_calls;
+    for (int64_t e = 0; e < fw2_pack_entries(p); ++e) fw2_pack_one(p, e);  // the re-ordering kernel
+    std::vector<float> tile((size_t)p.R * n);
+    const int64_t ntiles = fw2_num_tiles(p);
+    auto box_copy = [&](bool load, const float* src, float* dst, int64_t sB, int64_t sS, int cols, int stack, int row0) {
+      for (int r = 0; r < p.R; ++r)
+        for (int c = 0; c < n; ++c) {
+          float& t = tile[fw2_tile_index(p.R, r, c)];
+          const int row = row0 + r;
+          const bool in = row < p.B && c < cols;
+          if (load) t = in ? src[(int64_t)row * sB + (int64_t)stack * sS + c] : 0.f;
+          else if (in) dst[(int64_t)row * sB + (int64_t)stack * sS + c] = t;
+        }
+    };
+    for (int64_t t = 0; t < ntiles; ++t) {
+      const int stack = (int)(t % p.S), row0 = (int)(t / p.S) * p.R;
+      box_copy(true, p.x, nullptr, p.x_sB, p.x_sS, std::min(p.x_cols, n), stack, row0);
+      for (int gi = 0; gi < p.ngroups; ++gi) {
+        for (int tid = 0; tid < kFw2Threads; ++tid) {
+          f2 T[48];
+          fw2_fetch_tw(p, p.g[gi], stack, tid, T);
+          if (tid & 1) fw2_group_dispatch<true>(p, p.g[gi], tile.data(), tid, T);  // both row-loop forms
+          else fw2_group_dispatch<false>(p, p.g[gi], tile.data(), tid, T);
+        }
+        if (p.g[gi].emit) box_copy(false, nullptr, p.snap[p.g[gi].emit - 1], (int64_t)p.S * n, n, n, stack, row0);
+      }
+      if (p.has_out) box_copy(false, nullptr, p.out, p.out_sB, p.out_sS, p.out_cols, stack, row0);
+    }
+    return BFLY_OK;
+  }
 
   template <typename T> int run_fw(const FwParams<T>& p) {
     const int C = 1 << p.panel.logC;
@@ -135,7 +179,9 @@ struct EmulExec {
 template <typename T>
 int emul_fw(const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS, void* out, Problem q, int threads) {
   EmulExec ex; ex.threads_ = threads;
-  return drive_fw<T>(ex, q, (const T*)tw2, (const T*)tw4, (const T*)x, x_sB, x_sS, (T*)out);
+  std::vector<char> ws(fw_workspace_bytes<T>(q) + 256);
+  void* wsp = (void*)(((uintptr_t)ws.data() + 255) / 256 * 256);
+  return drive_fw<T>(ex, q, (const T*)tw2, (const T*)tw4, (const T*)x, x_sB, x_sS, (T*)out, wsp, fw_workspace_bytes<T>(q));
 }
 template <typename T>
 int emul_bw(const void* tw2, const void* tw4, const void* x, int64_t x_sB, int64_t x_sS, const void* g, int64_t g_sB, int64_t g_sS,
@@ -230,6 +276,10 @@ static int max_conflicts(const Problem& q, int kmax) {
 }
 
 extern "C" {
+long bfly_emul_fw2_calls(void) { return g_fw2_calls; }
+// the library's development switches (bfly_driver.h) for this emulator instance
+int bfly_emul_set_option(const char* name, int value) { return set_option(name, value); }
+int bfly_emul_get_option(const char* name) { int v = -1; get_option(name, &v); return v; }
 int bfly_emul_max_conflicts(int dtype, int base4, int log_n, int nblocks, int inc, int kmax) {
   Problem q{4, 1, log_n, nblocks, 1 << log_n, 1 << log_n, inc != 0, base4 != 0};
   return dtype == 0 ? max_conflicts<float>(q, kmax) : max_conflicts<cf>(q, kmax);

@@ -39,9 +39,16 @@ def test_status_text_and_versions():
 def test_workspace_query_and_argument_errors():
     from butterfly_b200 import abi
     assert abi.bw_workspace_bytes(torch.float32, 256, 1, 8, 1) == 0           # 8 stages: one phase, no scratch
-    assert abi.bw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 256 * 1024 * 4  # 10 stages: two phases
+    # the forward's optional scratch: a twiddle-sized buffer for float rows of 512 .. 4096 columns
+    assert abi.fw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 10 * 512 * 16
+    assert abi.fw_workspace_bytes(torch.float32, 256, 3, 12, 2) == 3 * 2 * 12 * 2048 * 16
+    assert abi.fw_workspace_bytes(torch.float32, 256, 1, 8, 1) == 0 and abi.fw_workspace_bytes(torch.float32, 256, 1, 13, 1) == 0
+    assert abi.fw_workspace_bytes(torch.complex64, 256, 1, 10, 1) == 0
+    # 10 stages: two phases = one snapshot, plus the scratch of the forward pass that writes it
+    assert abi.bw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 256 * 1024 * 4 + 10 * 512 * 16
     # n = 4096, two blocks: 24 stages = three phases of 8, i.e. two snapshots (the query covers both directions)
-    assert abi.bw_workspace_bytes(torch.float32, 16384, 1, 12, 2) in (2 * 16384 * 4096 * 4, 3 * 16384 * 4096 * 4)
+    fws = abi.fw_workspace_bytes(torch.float32, 16384, 1, 12, 2)
+    assert abi.bw_workspace_bytes(torch.float32, 16384, 1, 12, 2) in (2 * 16384 * 4096 * 4 + fws, 3 * 16384 * 4096 * 4 + fws)
     assert abi.bw_workspace_bytes(torch.float32, 4, 1, 0, 1) == -1      # log_n < 1
     assert abi.bw_workspace_bytes(torch.float32, 4, 0, 5, 1) == -1      # no stacks
     assert abi.bw_workspace_bytes(torch.complex64, 4, 1, 5, 1, base4=True) >= 0   # complex base-4 is supported

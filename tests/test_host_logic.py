@@ -19,11 +19,17 @@ CSRC = os.path.join(ROOT, "butterfly_b200", "csrc")
 
 @pytest.fixture(scope="module")
 def emul():
-    deps = [EMUL_SRC] + [os.path.join(CSRC, f) for f in ("bfly_core.h", "bfly_bw2.h", "bfly_types.h", "bfly_plan.h", "bfly_driver.h")]
+    deps = [EMUL_SRC] + [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".h")]
     if not os.path.exists(EMUL_LIB) or os.path.getmtime(EMUL_LIB) < max(os.path.getmtime(f) for f in deps):
         subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-unknown-pragmas", "-I", CSRC,
                                EMUL_SRC, "-o", EMUL_LIB])
     return ctypes.CDLL(EMUL_LIB)
+
+
+def emul_option(lib, name, value):
+    from conftest import library_option
+    return library_option(lambda n, v: lib.bfly_emul_set_option(n.encode(), int(v)),
+                          lambda n: lib.bfly_emul_get_option(n.encode()), name, value)
 
 
 def P(t):
@@ -121,11 +127,15 @@ def test_stack_broadcast_and_ragged_slices(emul, oracle_mod):
 
 
 @pytest.mark.parametrize("logc", [6, 7, 8])
-def test_forward_passes_over_panels(emul, oracle_mod, monkeypatch, logc):
+def test_forward_passes_over_panels(emul, oracle_mod, logc):
     """Rows wider than a tile run as several forward launches over panels, in place; the
-    environment switch forces that path at sizes the emulator handles (the product path takes
+    fw_logcmax switch forces that path at sizes the emulator handles (the product path takes
     it for rows beyond one SM's shared memory)."""
-    monkeypatch.setenv("BFLY_FW_LOGCMAX", str(logc))
+    with emul_option(emul, "fw_logcmax", logc):
+        _forward_passes_over_panels(emul, oracle_mod, logc)
+
+
+def _forward_passes_over_panels(emul, oracle_mod, logc):
     torch.manual_seed(40 + logc)
     for dtype in (torch.float32, torch.complex64):
         for log_n, nb, inc in [(9, 1, True), (9, 2, False), (10, 2, True), (11, 1, False)]:
@@ -192,17 +202,17 @@ def test_backward_in_chunks_of_phases(emul, oracle_mod):
         assert rel_err(d2, dtr) < 5e-5 and rel_err(dx, dxr) < 5e-5
     ws = ctypes.c_int64(0)
     assert emul.bfly_emul_bw_plan(0, 0, 16, 1, 10, 9, 1, ctypes.byref(ws)) > 9  # 90 stages: chunked
-    assert ws.value == 9 * 16 * 1024 * 4
+    assert ws.value == 9 * 16 * 1024 * 4 + 9 * 10 * 512 * 16  # 9 planes + the forward pass's re-ordered twiddles
 
 
 def test_backward_phase_plan_sizes(emul):
     ws = ctypes.c_int64(0)
     # float: a phase holds at most 8 stages (4 sub-groups of 2) on a panel of 1024 columns
     assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 8, 1, 1, ctypes.byref(ws)) == 1 and ws.value == 0
-    assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 10, 1, 1, ctypes.byref(ws)) == 2 and ws.value == 64 * 1024 * 4
+    assert emul.bfly_emul_bw_plan(0, 0, 64, 1, 10, 1, 1, ctypes.byref(ws)) == 2 and ws.value == 64 * 1024 * 4 + 10 * 512 * 16
     # n = 4096, two blocks: 24 stages = three phases of 8 -> two (B,S,n) float snapshots
     assert emul.bfly_emul_bw_plan(0, 0, 16384, 1, 12, 2, 1, ctypes.byref(ws)) == 3
-    assert ws.value == 2 * 16384 * 4096 * 4
+    assert ws.value == 2 * 16384 * 4096 * 4 + 24 * 2048 * 16  # two snapshots + re-ordered twiddles of the forward pass
     # complex: panels of 512 columns, up to 10 stages per phase
     nph = emul.bfly_emul_bw_plan(1, 0, 8192, 1, 11, 1, 1, ctypes.byref(ws))
     assert nph == 2 and ws.value == 8192 * 2048 * 8
@@ -231,3 +241,33 @@ def test_shared_memory_accesses_are_bank_conflict_free(emul):
     # base-4 (float): radix-4 windows of 2 bits
     for log_n in (10, 12, 14):
         assert emul.bfly_emul_max_conflicts(0, 1, log_n, 1, 1, 2) == 1
+
+
+@pytest.mark.parametrize("log_n", [9, 10, 11, 12])
+def test_packed_pair_forward_path(emul, oracle_mod, log_n):
+    """Float rows of 512 .. 4096 columns take the packed-pair forward kernel (two columns per
+    64-bit register, warps that own a 512-column chunk of the tile).  Its per-thread routines run
+    here thread by thread; with the kernel switched off the generic kernel must give the same bits
+    (both evaluate a butterfly output as fma(own, x, rn(partner * z)))."""
+    torch.manual_seed(700 + log_n)
+    emul.bfly_emul_fw2_calls.restype = ctypes.c_long
+    n = 1 << log_n
+    for nb, inc in [(1, True), (2, False), (3, True)]:
+        for B, S, insz, outsz in [(2, 1, n, n), (37, 2, n - 32, n - 64), (9, 3, n + 3, 64)]:
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
+            x = torch.randn(B, S, insz)
+            before = emul.bfly_emul_fw2_calls()
+            y = emul_fw(emul, tw, None, x, inc, outsz, log_n, nb, False, 256)
+            assert emul.bfly_emul_fw2_calls() == before + 1
+            with emul_option(emul, "fw2", 0):
+                y0 = emul_fw(emul, tw, None, x, inc, outsz, log_n, nb, False, 256)
+            assert emul.bfly_emul_fw2_calls() == before + 1
+            assert torch.equal(y, y0)
+            assert rel_err(y, oracle_mod.multiply_fw(tw, x, inc, outsz)) < 2e-5
+    # a ragged width (not a multiple of 32 columns) cannot be described to the TMA unit: generic kernel
+    x = torch.randn(3, 1, n - 5)
+    tw = torch.randn(1, 1, log_n, n // 2, 2, 2) / 2 ** 0.5
+    before = emul.bfly_emul_fw2_calls()
+    y = emul_fw(emul, tw, None, x, True, n, log_n, 1, False, 256)
+    assert emul.bfly_emul_fw2_calls() == before
+    assert rel_err(y, oracle_mod.multiply_fw(tw, x, True, n)) < 2e-5

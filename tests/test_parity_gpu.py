@@ -10,7 +10,7 @@ rtol/atol form directly.
 import pytest
 import torch
 
-from conftest import golden_files, load_golden, rel_err
+from conftest import abi_option, golden_files, load_golden, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -133,11 +133,12 @@ def test_rows_wider_than_one_sm(abi, dev, oracle_mod, dtype, log_n):
 
 
 @pytest.mark.parametrize("log_n,S", [(12, 3), (10, 2)], ids=["n4096", "n1024"])
-def test_tma_tile_path_edges(abi, dev, oracle_mod, monkeypatch, log_n, S):
+def test_tma_tile_path_edges(abi, dev, oracle_mod, log_n, S):
     """Shapes whose tiles travel through the TMA unit (4096- and 1024-column float rows), at the
     edges the descriptors have to get right: stack-broadcast input, rows with a padded pitch,
     zero-padded input, sliced output, batches that end inside a tile.  The per-thread copy path
-    (BFLY_TMA=0) must give the same bits, and both must match the oracle."""
+    (option tma = 0, which also means the generic forward kernel) must give the same bits, and
+    both must match the oracle."""
     torch.manual_seed(900 + log_n)
     n = 1 << log_n
     nb = 2
@@ -159,10 +160,10 @@ def test_tma_tile_path_edges(abi, dev, oracle_mod, monkeypatch, log_n, S):
             xd = xb[:, :1].to(dev).expand(B, S, n)
         res = {}
         for tma in ("1", "0"):
-            monkeypatch.setenv("BFLY_TMA", tma)
-            out, _ = abi.fw(tw.to(dev), xd, True, outsz)
-            d_tw, d_x, _ = abi.bw(tw.to(dev), xd, g.to(dev), True)
-            torch.cuda.synchronize()
+            with abi_option("tma", int(tma)):
+                out, _ = abi.fw(tw.to(dev), xd, True, outsz)
+                d_tw, d_x, _ = abi.bw(tw.to(dev), xd, g.to(dev), True)
+                torch.cuda.synchronize()
             res[tma] = (out[:, :, :outsz].clone(), d_tw.clone(), d_x.clone())
         assert abi.device_error() == 0
         assert torch.equal(res["1"][0], res["0"][0]), name
@@ -174,7 +175,7 @@ def test_tma_tile_path_edges(abi, dev, oracle_mod, monkeypatch, log_n, S):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.complex64], ids=["f32", "c64"])
-def test_saving_forward_and_saved_backward(abi, dev, oracle_mod, monkeypatch, dtype):
+def test_saving_forward_and_saved_backward(abi, dev, oracle_mod, dtype):
     """bfly_fw_*_saving / bfly_bw_*_saved through the C ABI, and the autograd operator that uses
     them: same bits as the recomputing pair for output and d_input (same arithmetic, the activations
     are stored instead of recomputed), d_twiddle up to the order of the final adds."""
@@ -198,11 +199,11 @@ def test_saving_forward_and_saved_backward(abi, dev, oracle_mod, monkeypatch, dt
             # autograd operator, saving on and off
             res = {}
             for mode in ("1", "0"):
-                monkeypatch.setenv("BFLY_AUTOGRAD_SAVE", mode)
-                twp = tw.clone().requires_grad_(True)
-                xp = x.clone().requires_grad_(True)
-                y = bb.butterfly_multiply(twp, xp, inc, outsz)
-                y.backward(g)
+                with abi_option("autograd_save", int(mode)):
+                    twp = tw.clone().requires_grad_(True)
+                    xp = x.clone().requires_grad_(True)
+                    y = bb.butterfly_multiply(twp, xp, inc, outsz)
+                    y.backward(g)
                 res[mode] = (y.detach(), twp.grad, xp.grad)
             assert torch.equal(res["1"][0], res["0"][0]) and torch.equal(res["1"][2], res["0"][2])
             assert rel_err(res["1"][1], res["0"][1]) < 1e-5
@@ -231,8 +232,8 @@ def test_many_blocks_backward_in_chunks(abi, dev, oracle_mod, dtype):
 
 
 @pytest.mark.parametrize("logc", [7, 9, 10])
-def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, logc):
-    """The multi-pass forward (environment switch BFLY_FW_LOGCMAX) must give what the one-pass
+def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, logc):
+    """The multi-pass forward (option fw_logcmax) must give what the one-pass
     forward gives, for radix-2 and base-4 products, float and complex."""
     torch.manual_seed(logc)
     log_n, B, S = 12, 33, 2
@@ -242,22 +243,20 @@ def test_forward_passes_forced_at_small_n(abi, dev, oracle_mod, monkeypatch, log
             tw = (torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5).to(dev)
             x = torch.randn(B, S, n - 64, dtype=dtype).to(dev)
             g = torch.randn(B, S, n - 32, dtype=dtype).to(dev)
-            monkeypatch.delenv("BFLY_FW_LOGCMAX", raising=False)
             y1, _ = abi.fw(tw, x, inc, n - 32)
             dt1, dx1, _ = abi.bw(tw, x, g, inc)
-            monkeypatch.setenv("BFLY_FW_LOGCMAX", str(logc))
-            y2, _ = abi.fw(tw, x, inc, n - 32)
-            dt2, dx2, _ = abi.bw(tw, x, g, inc)
+            with abi_option("fw_logcmax", logc):
+                y2, _ = abi.fw(tw, x, inc, n - 32)
+                dt2, dx2, _ = abi.bw(tw, x, g, inc)
             torch.cuda.synchronize()
             assert torch.equal(y1[:, :, :n - 32], y2[:, :, :n - 32])  # same arithmetic, different tiling
             assert rel_err(dt2, dt1) < 1e-5 and torch.equal(dx1, dx2)
     tw4 = (torch.randn(S, 2, log_n // 2, n // 4, 4, 4) / 2).to(dev)
     tw2 = torch.zeros(S, 2, 0, n // 2, 2, 2, device=dev)
     x = torch.randn(B, S, n).to(dev)
-    monkeypatch.delenv("BFLY_FW_LOGCMAX", raising=False)
     y1, _ = abi.fw_base4(tw4, tw2, x, True, n)
-    monkeypatch.setenv("BFLY_FW_LOGCMAX", str(logc))
-    y2, _ = abi.fw_base4(tw4, tw2, x, True, n)
+    with abi_option("fw_logcmax", logc):
+        y2, _ = abi.fw_base4(tw4, tw2, x, True, n)
     torch.cuda.synchronize()
     assert rel_err(y2, y1) < 1e-6  # window widths (and so the FMA grouping) may differ between tilings
 
