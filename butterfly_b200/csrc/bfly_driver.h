@@ -9,12 +9,15 @@
 //   int  run_fw2(const Fw2Params&, int ctas_per_sm);       // twiddle re-ordering + one launch of the packed-pair
 //                                                          // forward kernel (kFw2Declined: not available for these tensors)
 //   int  run_bw(const BwParams<T>&, int KW);               // one backward-phase launch
+//   int  run_bw3(const Bw3Params&);                        // one launch of the packed-pair backward phase kernel
+//                                                          // (kFw2Declined: not available for these tensors)
 //   int  zero(void* ptr, size_t bytes);                    // async memset
 //   int  zero2d(void* ptr, size_t pitch_bytes, size_t width_bytes, size_t rows);
 #pragma once
 #include <cstdlib>
 #include <cstring>
 
+#include "bfly_bw3.h"
 #include "bfly_fw2.h"
 #include "bfly_plan.h"
 
@@ -27,6 +30,7 @@ namespace bfly {
 struct Options {
   int tma = 1;          // tile traffic through the TMA unit where tensors qualify
   int bw_v2 = 1;        // second-generation backward phase kernel
+  int bw3 = 1;          // packed-pair backward phase kernel
   int fw2 = 1;          // packed-pair forward kernel
   int fw2_ctas = -1;    // packed-pair forward kernel: CTAs per SM (1 or 2; default 2)
   int fw_kmax = -1;     // generic forward: widest register window
@@ -40,6 +44,7 @@ struct OptionName { const char* name; const char* env; int Options::*field; };
 inline const OptionName* option_names(int* count) {
   static const OptionName names[] = {
       {"tma", "BFLY_TMA", &Options::tma},           {"bw_v2", "BFLY_BW_V2", &Options::bw_v2},
+      {"bw3", "BFLY_BW3", &Options::bw3},
       {"fw2", "BFLY_FW2", &Options::fw2},           {"fw_kmax", "BFLY_FW_KMAX", &Options::fw_kmax},
       {"fw2_ctas", "BFLY_FW2_CTAS", &Options::fw2_ctas},
       {"fw_rows", "BFLY_FW_ROWS", &Options::fw_rows}, {"fw_logcmax", "BFLY_FW_LOGCMAX", &Options::fw_logcmax},
@@ -453,6 +458,32 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
     for (int j = 0; j < P.nsg; ++j) {
       p.sg[j] = P.sg[j];
       bw2_assign_kase(p.sg[j], lay.kw);
+    }
+    if constexpr (sizeof(T) == 4) {
+      // float radix-2 phases on full 1024-column panels: the packed-pair kernel, when the tensors qualify
+      const Options& o = options();
+      if (o.bw3 != 0 && o.tma != 0 && o.bw_rows < 0 && o.bw_v2 != 0 && lay.kw == 2 && q.B >= kBw3Rows) {
+        Bw3Params p3;
+        std::memset(&p3, 0, sizeof(p3));
+        p3.b = p;
+        if (bw3_plan(p3.b, p3.sg)) {
+          BwParams<float>& b = p3.b;
+          b.Rb = kBw3Rows;
+          b.xin_cols = (int)std::min<int64_t>(b.xin_cols, n);  // input columns beyond n are never read
+          const int groups3 = (1 << P.panel.npanels_log) * q.S;
+          int nsl = std::max(1, 2 * ex.num_sms() / groups3);
+          int rows3 = (q.B + nsl - 1) / nsl;
+          rows3 = (rows3 + kBw3Rows - 1) / kBw3Rows * kBw3Rows;
+          b.rows_per_cta = rows3;
+          b.nslices = (q.B + rows3 - 1) / rows3;
+          b.vec_x = vec_ok<T>(b.xin, b.xin_sB, b.xin_sS);
+          b.vec_g = vec_ok<T>(b.gin, b.gin_sB, b.gin_sS);
+          b.vec_o = vec_ok<T>(b.gout, b.gout_sB, b.gout_sS);
+          const int rc3 = ex.run_bw3(p3);
+          if (rc3 == BFLY_OK) continue;
+          if (rc3 != kFw2Declined) return rc3;
+        }
+      }
     }
     const size_t row_bytes = (size_t)(P.nsg + 1) * sizeof(T) << P.panel.logC;
     const int U = (1 << P.panel.logC) >> lay.kw;

@@ -3,6 +3,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <cuda.h>
+
+#include "bfly_bw3.h"
 #include "bfly_fw2.h"
 
 namespace bfly {
@@ -13,5 +16,10 @@ namespace bfly {
 // `ctas_per_sm`: 1 or 2 (rows per thread up to 14 or 7).  `err`: device address of the flag that a
 // kernel whose bounded wait ran out raises.  `launches`: kernels launched.
 int fw2_launch(const Fw2Params& p, int ctas_per_sm, int sms, cudaStream_t stream, int* err, int* launches);
+
+// Launch the packed-pair backward phase kernel.  The three descriptors (activation in, gradient
+// in, gradient out) describe boxes of kBw3Rows rows of the phase's panel (bfly_tma.h).
+int bw3_launch(const Bw3Params& p, const CUtensorMap& mx, const CUtensorMap& mg, const CUtensorMap& mo, cudaStream_t stream,
+               int* err);
 
 }  // namespace bfly

@@ -206,6 +206,7 @@ bfly_bw_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ CU
     tma_load_tile(tma_smem(smG), &map_g, bar_g, c1, c2, p.tma_sg ? stack : 0, row0);
   };
   uint32_t parity = 0;
+  bool gave_up = false;  // a bounded wait ran out: the partial sums stay out of d_twiddle
   if (p.tma && tid == 0 && row_begin < row_end) {
     issue_load_x(row_begin);
     issue_load_g(row_begin);
@@ -217,6 +218,7 @@ bfly_bw_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ CU
       parity ^= 1;
       if (__syncthreads_or(!ok)) {  // uniform decision: give up on this CTA's rows
         if (tid == 0) atomicExch(&g_device_error, 1);
+        gave_up = true;
         break;
       }
     } else {
@@ -257,7 +259,7 @@ bfly_bw_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ CU
     }
   }
   if (p.tma && tid == 0) tma_store_wait_all();
-  bw_flush_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
+  if (!gave_up) bw_flush_state<T, KW, NSG>(p, st, stack, pbase, tid, kThreads);
 }
 
 // Second-generation backward phase (bfly_bw2.h): accumulators in tensor memory, four-row
@@ -322,6 +324,7 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
     tma_load_tile(tma_smem(smG), &map_g, bar_g, c1, c2, sg_, row0);
   };
   uint32_t parity = 0;
+  bool gave_up = false;  // a bounded wait ran out: the partial sums stay out of d_twiddle
   if (p.tma && tid == 0 && row_begin < row_end) {
     issue_load_x(row_begin);
     issue_load_g(row_begin);
@@ -333,6 +336,7 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
       parity ^= 1;
       if (__syncthreads_or(!ok)) {  // uniform decision: give up on this CTA's rows
         if (tid == 0) atomicExch(&g_device_error, 1);
+        gave_up = true;
         break;
       }
     } else {
@@ -349,6 +353,7 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
       const bool ok = mbar_wait(bar_g, parity ^ 1);
       if (__syncthreads_or(!ok)) {
         if (tid == 0) atomicExch(&g_device_error, 1);
+        gave_up = true;
         break;
       }
     }
@@ -374,7 +379,7 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
     }
   }
   if (p.tma && tid == 0) tma_store_wait_all();
-  bw2_flush<T, KW>(p, accs, meta, stack, tid, kThreads);
+  if (!gave_up) bw2_flush<T, KW>(p, accs, meta, stack, tid, kThreads);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
@@ -542,6 +547,21 @@ struct CudaExec {
       rc = fw2_launch(p, ctas_per_sm, dev.sms, stream, err, &launches);
     }
     if (rc == BFLY_OK) g_launches.fetch_add(launches);
+    return rc;
+  }
+  int run_bw3(const Bw3Params& p_in) {
+    Bw3Params p = p_in;
+    CUtensorMap mx, mg, mo;
+    describe_bw(p.b, kBw3Rows, mx, mg, mo);
+    if (!p.b.tma) return kFw2Declined;
+    int* err = nullptr;
+    int rc = device_error_ptr(&err);
+    if (rc) return rc;
+    {
+      ProfileScope prof(kKernBw, stream);
+      rc = bw3_launch(p, mx, mg, mo, stream, err);
+    }
+    if (rc == BFLY_OK) g_launches.fetch_add(1);
     return rc;
   }
   template <typename T> int run_fw(const FwParams<T>& p) {

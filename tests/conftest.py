@@ -42,6 +42,50 @@ def rel_err(a, b):
     return ((a - b).abs().max() / (b.abs().max() + 1e-30)).item() if b.numel() else 0.0
 
 
+def tol_ratio(a, b, rtol=1e-5, atol=1e-5):
+    """Per-component |a - b| / (atol + rtol |b|) (complex: real and imaginary parts separately).
+    <= 1 everywhere means agreement within rtol / atol."""
+    a = a.detach().cpu()
+    b = b.detach().cpu()
+    a = torch.view_as_real(a) if a.is_complex() else a
+    b = torch.view_as_real(b) if b.is_complex() else b
+    return (a - b).abs() / (atol + rtol * b.abs())
+
+
+def assert_rtol_atol(a, b, what="", rtol=1e-5, atol=1e-5, outliers=0.0, worst_allowed=1.0):
+    """Per-component rtol 1e-5 / atol 1e-5 (the tolerance the product is specified to).  Strict by
+    default; `outliers` = fraction of components that may exceed it, up to `worst_allowed` times
+    the tolerance (for comparisons of two different float32 evaluation orders over very many
+    components, where a few land just outside)."""
+    if not b.numel():
+        return
+    r = tol_ratio(a, b, rtol, atol)
+    worst = r.max().item()
+    frac = (r > 1).float().mean().item()
+    assert frac <= outliers and worst <= max(worst_allowed, 1.0), (
+        "%s: %.4f %% of components outside rtol %g / atol %g, worst %.2fx the tolerance" % (what, 100.0 * frac, rtol, atol, worst))
+
+
+def assert_sum_accuracy(ours, ref32, ref64, what=""):
+    """Grade a float32 twiddle gradient (a sum over the batch) against the double-precision
+    oracle: per component it must be as close to it as the float32 oracle is, or within 1e-5 of
+    the gradient's scale -- two valid summation orders of thousands of float32 terms differ by
+    more than rtol 1e-5 on the entries whose true sum is near zero."""
+    if not ref64.numel():
+        return
+    o = ours.detach().cpu()
+    o = (torch.view_as_real(o) if o.is_complex() else o).double()
+    r32 = (torch.view_as_real(ref32) if ref32.is_complex() else ref32).double()
+    r64 = (torch.view_as_real(ref64) if ref64.is_complex() else ref64).double()
+    scale = r64.abs().max().item()
+    # the float32 oracle's own error, as a floor per component and over the tensor
+    allowed = torch.maximum((r32 - r64).abs(), torch.full_like(r64, 1e-5 * scale))
+    err = (o - r64).abs()
+    bad = err > allowed
+    assert not bad.any(), "%s: %d components further from the double-precision oracle than allowed (worst %.3g, scale %.3g)" % (
+        what, int(bad.sum()), (err - allowed).max().item(), scale)
+
+
 @pytest.fixture(scope="session")
 def oracle_mod():
     import oracle

@@ -10,6 +10,7 @@
 
 #include "bfly_core.h"
 #include "bfly_bw2.h"
+#include "bfly_bw3.h"
 #include "bfly_driver.h"
 
 using namespace bfly;
@@ -17,6 +18,7 @@ using namespace bfly;
 namespace {
 
 long g_fw2_calls = 0;  // launches the emulator ran through the packed-pair forward path
+long g_bw3_calls = 0;  // ... and through the packed-pair backward phase path
 
 struct EmulExec {
   int sms = 7;       // odd on purpose: exercises ragged row slices
@@ -64,6 +66,47 @@ struct EmulExec {
         if (p.g[gi].emit) box_copy(false, nullptr, p.snap[p.g[gi].emit - 1], (int64_t)p.S * n, n, n, stack, row0);
       }
       if (p.has_out) box_copy(false, nullptr, p.out, p.out_sB, p.out_sS, p.out_cols, stack, row0);
+    }
+    return BFLY_OK;
+  }
+
+  // packed-pair backward phase: the device kernel's steps, thread by thread, accumulators in a heap array
+  bool bw3 = true;
+  int run_bw3(const Bw3Params& p) {
+    if (!bw3) return kFw2Declined;
+    const BwParams<float>& q = p.b;
+    // what the TMA descriptors would refuse: widths that are not whole 32-column blocks
+    if (!q.vec_x || !q.vec_g || !q.vec_o || q.xin_cols % 32 || q.gin_cols % 32 || q.gout_cols % 32) return kFw2Declined;
+    ++g_bw3_calls;
+    const int C = 1024, nthr = kBw3Threads;
+    std::vector<float> smem((size_t)(q.nsg + 1) * kBw3Rows * C);
+    float* smX = smem.data();
+    float* smG = smem.data() + (size_t)q.nsg * kBw3Rows * C;
+    std::vector<uint32_t> meta((size_t)q.nsg * nthr * 4 + 8);
+    std::vector<float> accmem((size_t)nthr * kBw3MaxSg * 64);
+    std::vector<float> pf((size_t)nthr * 64);  // per-thread fetch buffers (twiddles, accumulators of the next step)
+    const int nctas = bw_num_ctas(q);
+    for (int cta = 0; cta < nctas; ++cta) {
+      int pbase, stack, rb, re;
+      bw_cta_coords(q, cta, pbase, stack, rb, re);
+      std::vector<Acc3Host> accs(nthr);
+      for (int tid = 0; tid < nthr; ++tid) {
+        accs[tid].mem = accmem.data() + (size_t)tid * kBw3MaxSg * 64;
+        bw3_init(p, accs[tid], meta.data(), stack, pbase, tid);
+        bw3_prefetch(p, accs[tid], 0, pf.data() + (size_t)tid * 64, pf.data() + (size_t)tid * 64 + 32);
+      }
+      for (int row0 = rb; row0 < re; row0 += kBw3Rows) {
+        for (int tid = 0; tid < nthr; ++tid) {
+          tile_load_auto<float>(q.xin, q.xin_sB, q.xin_sS, q.xin_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smX, tid, nthr);
+          tile_load_auto<float>(q.gin, q.gin_sB, q.gin_sS, q.gin_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smG, tid, nthr);
+        }
+        for (int step = 0; step < bw3_num_steps(q.nsg); ++step)
+          for (int tid = 0; tid < nthr; ++tid)
+            bw3_step(p, accs[tid], meta.data(), step, smem.data(), tid, pf.data() + (size_t)tid * 64, pf.data() + (size_t)tid * 64 + 32);
+        for (int tid = 0; tid < nthr; ++tid)
+          tile_store_auto<float>(q.gout, q.gout_sB, q.gout_sS, q.gout_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smG, tid, nthr);
+      }
+      for (int tid = 0; tid < nthr; ++tid) bw3_flush(p, accs[tid], stack, pbase, tid);
     }
     return BFLY_OK;
   }
@@ -277,6 +320,7 @@ static int max_conflicts(const Problem& q, int kmax) {
 
 extern "C" {
 long bfly_emul_fw2_calls(void) { return g_fw2_calls; }
+long bfly_emul_bw3_calls(void) { return g_bw3_calls; }
 // the library's development switches (bfly_driver.h) for this emulator instance
 int bfly_emul_set_option(const char* name, int value) { return set_option(name, value); }
 int bfly_emul_get_option(const char* name) { int v = -1; get_option(name, &v); return v; }

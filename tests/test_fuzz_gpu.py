@@ -8,7 +8,7 @@ import random
 import pytest
 import torch
 
-from conftest import rel_err
+from conftest import assert_rtol_atol, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -59,10 +59,14 @@ def test_random_cases_against_oracle(oracle_mod, seed):
             d4, d2, dx, _ = abi.bw_base4(tw4.to(dev), tw2.to(dev), xd, g.to(dev), inc)
             assert rel_err(out[:, :, :outsz], yr) < 3e-5, what
             assert rel_err(dx[:, :, :insz], dxr) < 3e-5, what
+            assert_rtol_atol(out[:, :, :outsz], yr, str(what), outliers=3e-4, worst_allowed=3.0)
+            assert_rtol_atol(dx[:, :, :insz], dxr, str(what), outliers=3e-4, worst_allowed=3.0)
             if tw4.numel():
                 assert rel_err(d4, d4r) < 3e-5, what
+                assert_rtol_atol(d4, d4r, str(what), outliers=3e-4, worst_allowed=3.0)
             if tw2.numel():
                 assert rel_err(d2, d2r) < 3e-5, what
+                assert_rtol_atol(d2, d2r, str(what), outliers=3e-4, worst_allowed=3.0)
             continue
         tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
         yr = oracle_mod.multiply_fw(tw, xh, inc, outsz)
@@ -74,4 +78,7 @@ def test_random_cases_against_oracle(oracle_mod, seed):
         for a, b in ((out[:, :, :outsz], yr), (dt, dtr), (dx[:, :, :insz], dxr), (y2[:, :, :outsz], yr), (dt2, dtr),
                      (dx2[:, :, :insz], dxr)):
             assert rel_err(a, b) < 3e-5, what
+            # per component: rtol 1e-5 / atol 1e-5.  The oracle rounds every product, the GPU fuses
+            # multiply-adds: over millions of components a handful land just outside
+            assert_rtol_atol(a, b, str(what), outliers=3e-4, worst_allowed=3.0)
     assert abi.device_error() == 0

@@ -271,3 +271,31 @@ def test_packed_pair_forward_path(emul, oracle_mod, log_n):
     y = emul_fw(emul, tw, None, x, True, n, log_n, 1, False, 256)
     assert emul.bfly_emul_fw2_calls() == before
     assert rel_err(y, oracle_mod.multiply_fw(tw, x, True, n)) < 2e-5
+
+
+@pytest.mark.parametrize("log_n", [10, 11, 12])
+def test_packed_pair_backward_path(emul, oracle_mod, log_n):
+    """Float radix-2 phases on full 1024-column panels take the packed-pair backward kernel (two
+    columns per 64-bit register, twiddles and accumulators paired in tensor memory).  Its step
+    routines run here thread by thread; with the kernel switched off the scalar kernels must give
+    the same input gradient bits (same rounding order) and the same twiddle gradient up to the
+    order of the row sums."""
+    torch.manual_seed(800 + log_n)
+    emul.bfly_emul_bw3_calls.restype = ctypes.c_long
+    n = 1 << log_n
+    for nb, inc in [(1, True), (2, False), (2, True)]:
+        for B, S, insz, outsz in [(5, 1, n, n), (23, 2, n - 32, n - 64), (9, 1, n + 32, 64)]:
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
+            x = torch.randn(B, S, insz)
+            g = torch.randn(B, S, outsz)
+            before = emul.bfly_emul_bw3_calls()
+            d2, _, dx = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, 256)
+            assert emul.bfly_emul_bw3_calls() > before
+            with emul_option(emul, "bw3", 0):
+                mid = emul.bfly_emul_bw3_calls()
+                d2s, _, dxs = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, 256)
+                assert emul.bfly_emul_bw3_calls() == mid
+            dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+            assert torch.equal(dx, dxs)
+            assert rel_err(d2, d2s) < 1e-5
+            assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5

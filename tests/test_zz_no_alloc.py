@@ -17,7 +17,7 @@ def _rel(a, b):
     return ((a - b).abs().max() / (b.abs().max() + 1e-30)).item()
 
 
-def test_noalloc_backward_matches_workspace_backward_twice_in_a_row():
+def test_noalloc_backward_matches_workspace_backward_twice_in_a_row(oracle_mod):
     from butterfly_b200 import abi
     assert torch.cuda.is_available()
     dev = torch.device("cuda", 0)
@@ -50,6 +50,10 @@ def test_noalloc_backward_matches_workspace_backward_twice_in_a_row():
         # d_input is deterministic; d_twiddle differs only by the order of the final atomic adds
         assert torch.equal(got_dx[:, :, :in_size], ref_dx[:, :, :in_size]), "call %d" % call
         assert _rel(got_dtw, ref_dtw) < 2e-5, "call %d" % call
+        if call == 1:
+            # and once against the CPU oracle (not only against the other CUDA entry point)
+            o_dtw, o_dx = oracle_mod.multiply_bw(tw.cpu(), x.cpu(), g.cpu(), True)
+            assert _rel(got_dx[:, :, :in_size].cpu(), o_dx) < 2e-5 and _rel(got_dtw.cpu(), o_dtw) < 2e-5
         results.append(got_dtw)
     assert not torch.equal(results[0], results[1])  # two different problems were really solved
 
