@@ -80,9 +80,15 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        return self.snapshot()
+
+    def snapshot(self):
+        """Summary of the samples taken so far."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in list(self.lines):
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -95,6 +101,16 @@ class ClockSampler:
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def load_configs():
+    """The configuration table, loaded by path: importing the package would map the product's
+    libraries into a process that is only meant to run the reference."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bfly_bench_configs", os.path.join(ROOT, "butterfly_b200", "configs.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 # ------------------------------------------------------------------------------ CPU reference arm
@@ -131,7 +147,7 @@ def cpu_reference_time(cfg_name, rows, cores, reps=1):
     (the operator call releases the GIL) and the twiddle gradients of the chunks are summed.
     """
     from concurrent.futures import ThreadPoolExecutor
-    from butterfly_b200 import configs
+    configs = load_configs()
     kind, run = _cpu_reference_runner()
     torch.set_num_threads(1)
     if (cfg_name, rows) not in _CPU_INPUTS:
@@ -158,7 +174,7 @@ def cpu_reference_time(cfg_name, rows, cores, reps=1):
 
 
 def run_reference_arm(args):
-    from butterfly_b200 import configs
+    configs = load_configs()
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -192,19 +208,21 @@ def run_reference_arm(args):
 
 # ------------------------------------------------------------------------------ GPU arm
 
-# (config, kernel) -> (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch of the capture);
-# mean of the three phase launches in profiles/bfly_bw2_kernel_cfg2_batch4096.md
-NCU_DRAM_BYTES = {("cfg2", "bfly_bw_kernel"): (165.1e6, 4096)}
+# (config, kernel) -> (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch of the capture):
+# mean over the phase launches of one backward call in the ncu capture summarised under profiles/
+NCU_DRAM_BYTES = {("cfg2", "bfly_bw3_kernel"): (174.6e6, 4096), ("cfg2", "bfly_bw2_kernel"): (165.1e6, 4096),
+                  ("cfg2", "bfly_fw2_kernel"): (85.9e6, 4096)}
 
 
-def fp32_ceiling_gbs(cfg, B, step_bytes, sms=148, sm_mhz=1965.0):
+def fp32_ceiling_gbs(cfg, B, step_bytes, sm_mhz, sms=148):
     """Algorithmic GB/s of fw+bw if only the FP32 pipes limited it (real radix-2 products).
 
-    Per element and stage: forward 2 multiply-add instructions; backward 4 (twiddle gradient and
+    Per element and stage: forward 2 multiply-add lane operations; backward 4 (twiddle gradient and
     input gradient) + 2 for each recomputed stage (the snapshot pass covers all but the last phase,
-    the phases recompute all but their last sub-group; 3/4 and 2/3 of the stages for 24 stages)."""
+    the phases recompute all but their last sub-group; 3/4 and 2/3 of the stages for 24 stages),
+    at 128 lanes per SM and the SM clock sampled during the run."""
     import torch
-    if cfg["base4"] or cfg["dtype"] != torch.float32:
+    if cfg["base4"] or cfg["dtype"] != torch.float32 or not sm_mhz:
         return None
     stages = cfg["nblocks"] * cfg["log_n"]
     elem_stages = float(B) * cfg["nstacks"] * (1 << cfg["log_n"]) * stages
@@ -213,10 +231,91 @@ def fp32_ceiling_gbs(cfg, B, step_bytes, sms=148, sm_mhz=1965.0):
     return step_bytes / seconds / 1e9
 
 
+def _events_ms(fn, iters, warm):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def _host_us_per_call(fn, iters=200):
+    """Host time of one operator call (enqueue only: the stream is drained before and after)."""
+    import torch
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        fn()
+    t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    return 1e6 * (t1 - t0) / iters
+
+
+def measure_config(bb, configs, name, dev, peak, make=None, iters=5, warm=3, ref_ops=None):
+    """fw and bw of one configuration, timed separately with CUDA events (inputs resident in HBM):
+    ms, algorithmic GB/s and the fraction of the HBM peak; with `ref_ops` the same through the
+    reference's CUDA extension."""
+    import torch
+    d = make() if make else configs.make_inputs(name, device=dev)
+    inc = d["increasing_stride"]
+    x, g = d["input"], d.get("grad")
+    fwb, bwb = d["bytes"] if "bytes" in d else configs.algorithmic_bytes(name, batch=d["batch"])
+    if d.get("base4"):
+        t4, t2 = d["twiddle4"], d["twiddle2"]
+        fw = lambda: bb.butterfly_multiply_base4_fw(t4, t2, x, inc)
+        bw = (lambda: bb.butterfly_multiply_base4_bw(t4, t2, x, g, inc)) if g is not None else None
+    else:
+        tw = d["twiddle"]
+        fw = lambda: bb.butterfly_multiply_fw(tw, x, inc)
+        bw = (lambda: bb.butterfly_multiply_bw(tw, x, g, inc)) if g is not None else None
+    out = {"name": name, "n": d["n"], "batch": d["batch"], "nstacks": int(x.shape[1]),
+           "dtype": "f32" if x.dtype == torch.float32 else "c64"}
+    fw_ms = _events_ms(fw, iters, warm)
+    out.update(fw_ms=fw_ms, fw_gbs=fwb / fw_ms / 1e6, fw_frac_of_hbm_peak=fwb / fw_ms / 1e6 / peak)
+    if bw is not None:
+        bw_ms = _events_ms(bw, iters, warm)
+        out.update(bw_ms=bw_ms, bw_gbs=bwb / bw_ms / 1e6,
+                   fw_bw_gbs=(fwb + bwb) / (fw_ms + bw_ms) / 1e6,
+                   fw_bw_frac_of_hbm_peak=(fwb + bwb) / (fw_ms + bw_ms) / 1e6 / peak)
+    else:
+        out["fw_host_us_per_call"] = _host_us_per_call(fw)  # latency-bound case: the launch path matters
+    if ref_ops is not None and not d.get("base4"):
+        n = d["n"]
+        rfw = lambda: ref_ops.butterfly_multiply_fw(tw, x, inc, n)
+        out["reference_cuda_fw_ms"] = _events_ms(rfw, 3, 1)
+        if g is not None:
+            rbw = lambda: ref_ops.butterfly_multiply_bw(tw, x, g, inc)
+            out["reference_cuda_bw_ms"] = _events_ms(rbw, 3, 1)
+    return out
+
+
+def two_block_inputs(log_n, dev, elements=1 << 26):
+    """Real fp32 two-block product (increasing then decreasing stride) over `elements` elements."""
+    import math
+    import torch
+    n = 1 << log_n
+    B = elements // n
+    g = torch.Generator().manual_seed(log_n)
+    tw = (torch.randn(1, 2, log_n, n // 2, 2, 2, generator=g) / math.sqrt(2)).to(dev)
+    x = torch.randn(B, 1, n, generator=g).to(dev)
+    gr = torch.randn(B, 1, n, generator=g).to(dev)
+    twb = tw.numel() * 4
+    plane = B * n * 4
+    return dict(twiddle=tw, input=x, grad=gr, increasing_stride=True, n=n, batch=B, base4=False,
+                bytes=(2 * plane + twb, 3 * plane + 2 * twb))
+
+
 def run_gpu_arm(args):
     import torch.distributed as dist
     import butterfly_b200 as bb
     from butterfly_b200 import abi, configs
+    from butterfly_b200.distributed import AsyncTwiddleReducer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -231,21 +330,26 @@ def run_gpu_arm(args):
 
     cfg = configs.CONFIGS[args.config]
     if cfg["base4"] or cfg.get("forward_only"):
-        raise SystemExit("bench.py times fw+bw of a radix-2 config (cfg2, cfg3, cfg5)")
+        raise SystemExit("bench.py's headline loop times fw+bw of a radix-2 config (cfg2, cfg3, cfg5); "
+                         "cfg1 and cfg4 are measured in other_configs")
     d = configs.make_inputs(args.config, batch=args.batch, rank=rank, device=dev)
     tw, x, g, inc = d["twiddle"], d["input"], d["grad"], d["increasing_stride"]
     B, S, n = d["batch"], cfg["nstacks"], d["n"]
     fwb, bwb = configs.algorithmic_bytes(args.config, batch=args.batch)
     step_bytes = fwb + bwb
+    # the twiddle gradient of step k is all-reduced on a side stream while step k+1 computes
+    reducer = AsyncTwiddleReducer(dev) if world > 1 else None
 
     def step():
         y = bb.butterfly_multiply_fw(tw, x, inc)
         d_tw, d_x = bb.butterfly_multiply_bw(tw, x, g, inc)
-        if world > 1:
-            dist.all_reduce(d_tw)
+        if reducer is not None:
+            reducer.submit(d_tw)
         return y, d_tw, d_x
 
     def barrier():
+        if reducer is not None:
+            reducer.wait()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -265,6 +369,8 @@ def run_gpu_arm(args):
     e0.record()
     for _ in range(args.steps):
         step()
+    if reducer is not None:
+        reducer.wait()  # the timed region ends when the last all-reduce has finished
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -276,45 +382,92 @@ def run_gpu_arm(args):
     ms_per_step = ms / args.steps
     value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
 
-    # ---- per-kernel durations (separate untimed steps, CUDA events around every launch)
+    # ---- per-kernel durations (separate untimed passes, CUDA events around every launch): the
+    # forward calls and the backward calls apart, so that the backward's own forward pass (the
+    # snapshot pass) is not mixed up with the forward operator
+    NPROF = 3
     abi.profile_enable(True)
-    for _ in range(3):
-        step()
+    for _ in range(NPROF):
+        bb.butterfly_multiply_fw(tw, x, inc)
     torch.cuda.synchronize()
-    prof = abi.profile_collect()
+    prof_fw = abi.profile_collect()
+    for _ in range(NPROF):
+        bb.butterfly_multiply_bw(tw, x, g, inc)
+    torch.cuda.synchronize()
+    prof_bw = abi.profile_collect()
     abi.profile_enable(False)
     peak, peak_src = measured_hbm_peak()
-    dom = max(prof, key=lambda k: prof[k][1])
-    dom_launches, dom_ms = prof[dom]
-    sz = 4 if cfg["dtype"] == torch.float32 else 8
-    tw_bytes = tw.numel() * sz
-    plane = B * S * n * sz
-    if dom == "bfly_bw_kernel":
-        # one phase launch reads the phase's input activation and the gradient, writes the
-        # gradient, and reads/accumulates its share of the twiddles
-        per_step = dom_launches // 3
-        alg = 3 * plane + 2 * tw_bytes / max(per_step, 1)
+
+    clocks_mid = sampler.snapshot() if rank == 0 else None
+    # dominant kernel = largest time share of a step.  Its algorithmic bytes: the operator's
+    # algorithmic bytes (forward: input + output + twiddle; backward: input + grad + d_input +
+    # twiddle + d_twiddle -- each tensor once, never the design's own snapshot traffic) divided
+    # over the launches of that kernel which do the operator's work
+    shares = {}
+    for k, (nl, tms) in prof_fw.items():
+        if nl:
+            shares[("fw", k)] = (nl / NPROF, tms / NPROF)
+    for k, (nl, tms) in prof_bw.items():
+        if nl:
+            shares[("bw", k)] = (nl / NPROF, tms / NPROF)
+    (dom_op, dom), (dom_launches, dom_ms) = max(shares.items(), key=lambda kv: kv[1][1])
+    # the backward's phase launches carry the backward's algorithmic bytes; its forward pass
+    # (snapshots) is extra work of the design and gets none
+    phase_kernels = [k for (op, k) in shares if op == "bw" and k.startswith("bfly_bw")]
+    if dom_op == "fw":
+        alg = fwb / dom_launches
+    elif dom in phase_kernels:
+        alg = bwb / sum(shares[("bw", k)][0] for k in phase_kernels)
     else:
-        per_step = dom_launches // 3
-        alg = 2 * plane + tw_bytes
-    avg_ms = dom_ms / max(dom_launches, 1)
+        alg = 0.0
+    avg_ms = dom_ms / dom_launches
     achieved = alg / (avg_ms * 1e-3) / 1e9
-    # DRAM bytes per launch of the dominant kernel from an ncu capture of a smaller batch of the
-    # same configuration, scaled by the rows (the summaries under profiles/ give the captures)
     traffic = None
     cap = NCU_DRAM_BYTES.get((args.config, dom))
     if cap is not None:
         traffic = cap[0] * B / cap[1]
-    # what the FP32 pipes alone allow for this step: multiply-add instructions of forward, snapshot
-    # pass, recompute and reverse sweep at 128 lanes per SM and the sampled clock
-    fp32_ceiling = fp32_ceiling_gbs(cfg, B, step_bytes)
-    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "peak_source": peak_src,
+    kernel_ms = {"forward: " + k: v[1] for (op, k), v in shares.items() if op == "fw"}
+    kernel_ms.update({"backward: " + k: v[1] for (op, k), v in shares.items() if op == "bw"})
+    bw_total_ms = sum(v[1] for (op, k), v in shares.items() if op == "bw")
+    roofline = {"bound": "hbm", "kernel": dom, "operator": "forward" if dom_op == "fw" else "backward",
+                "achieved": achieved, "peak": peak, "peak_source": peak_src,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                "traffic_over_algorithmic": (traffic / alg) if (traffic and alg) else None,
                 "traffic_source": ("ncu dram__bytes_read+write of a batch-%d capture, scaled by rows" % cap[1]) if cap else None,
-                "fp32_ceiling_gbs": fp32_ceiling, "launches_per_step": per_step,
-                "avg_launch_ms": avg_ms, "algorithmic_bytes_per_launch": alg,
-                "kernel_ms_per_step": {k: v[1] / 3 for k, v in prof.items()},
+                "launches_per_step": dom_launches, "avg_launch_ms": avg_ms, "algorithmic_bytes_per_launch": alg,
+                "kernel_ms_per_step": kernel_ms,
+                "forward_frac_of_hbm_peak": fwb / (sum(v[1] for (op, k), v in shares.items() if op == "fw") * 1e-3) / 1e9 / peak,
+                "backward_frac_of_hbm_peak": bwb / (bw_total_ms * 1e-3) / 1e9 / peak,
                 "op_frac_of_hbm_peak": (step_bytes / (ms_per_step * 1e-3) / 1e9) / peak}
+
+    # ---- the other configurations and the reference's CUDA extension (the kernel to beat), untimed
+    # by the headline loop
+    other, ref_cuda_note = None, None
+    if rank == 0 and world == 1 and not args.no_other and args.batch is None:
+        ref_ops = None
+        if not args.no_refcuda:
+            try:
+                import oracle
+                if oracle.reference_available(cuda=True):
+                    ref_ops = oracle.load_reference_ops(cuda=True)
+                else:
+                    ref_cuda_note = {"kind": "unavailable", "why": "oracle/_ref/_butterfly_ref_cuda.so not built"}
+            except Exception as e:  # the comparison column is optional
+                ref_cuda_note = {"kind": "unavailable", "why": repr(e)[:200]}
+        other = []
+        for name in ("cfg1", "cfg2", "cfg3", "cfg4", "cfg5"):
+            other.append(measure_config(bb, configs, name, dev, peak, ref_ops=ref_ops))
+        for log_n in (10, 11, 13):
+            other.append(measure_config(bb, configs, "two-block n=%d" % (1 << log_n), dev, peak,
+                                        make=lambda: two_block_inputs(log_n, dev), ref_ops=ref_ops if log_n <= 11 else None))
+        if ref_ops is not None:
+            ref_cuda_note = {"kind": "reference", "library": "oracle/_ref/_butterfly_ref_cuda.so",
+                             "what": "csrc/cuda/butterfly_cuda.cu of the reference compiled unmodified for sm_100; "
+                                     "reference_cuda_*_ms in other_configs"}
+    elif rank == 0 and world > 1 and not args.no_other:
+        # the multi-GPU configuration: this rank's shard of cfg5 (8192 rows, stack-broadcast input)
+        other = [measure_config(bb, configs, "cfg5", dev, peak,
+                                make=lambda: configs.make_inputs("cfg5", rank=rank, device=dev))]
 
     # ---- end to end through the public operator with host buffers
     e2e = None
@@ -325,6 +478,7 @@ def run_gpu_arm(args):
         hy = torch.empty((B, S, n), dtype=x.dtype).pin_memory()
         hdx = torch.empty((B, S, n), dtype=x.dtype).pin_memory()
         hdt = torch.empty(tw.shape, dtype=tw.dtype).pin_memory()
+        sz = 4 if cfg["dtype"] == torch.float32 else 8
 
         from butterfly_b200.host import HostPipeline
         pipe = HostPipeline(dev, chunks=args.e2e_chunks)
@@ -332,8 +486,8 @@ def run_gpu_arm(args):
         def e2e_step():
             # public host-side API: chunked upload / fw+bw / download on three streams
             d_tw = pipe.fw_bw(tw, hx, hg, inc, hy, hdx, hdt)
-            if world > 1:
-                dist.all_reduce(d_tw)
+            if reducer is not None:
+                reducer.submit(d_tw)
         h2d = hx.numel() * sz + hg.numel() * sz
         d2h = (hy.numel() + hdx.numel() + hdt.numel()) * sz
         e2e_steps = max(1, min(args.steps, 5))
@@ -344,19 +498,28 @@ def run_gpu_arm(args):
         a.record()
         for _ in range(e2e_steps):
             e2e_step()
+        if reducer is not None:
+            reducer.wait()
         b.record()
         barrier()
         ems = a.elapsed_time(b)
+        # the two copy directions alone (same pinned buffers, same chunking), to show what bounds the pipeline
+        h2d_ms = _events_ms(lambda: pipe.upload_only(hx, hg), 3, 1)
+        d2h_ms = _events_ms(lambda: pipe.download_only(hy, hdx), 3, 1)
         if world > 1:
-            t = torch.tensor([ems], device=dev)
+            t = torch.tensor([ems, h2d_ms, d2h_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ems = float(t.item())
+            ems, h2d_ms, d2h_ms = [float(v) for v in t.tolist()]
         e2e = {"value": step_bytes * world / (ems / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ems / e2e_steps,
-               "steps": e2e_steps, "api": "butterfly_b200.host.HostPipeline.fw_bw (%d row chunks, 3 streams)" % args.e2e_chunks}
+               "steps": e2e_steps, "api": "butterfly_b200.host.HostPipeline.fw_bw (%d row chunks, 3 streams)" % args.e2e_chunks,
+               "h2d_alone_gbs_per_rank": h2d / h2d_ms / 1e6, "d2h_alone_gbs_per_rank": (d2h - hdt.numel() * sz) / d2h_ms / 1e6,
+               "pcie_gbs_aggregate": (h2d + d2h) * world / (ems / e2e_steps) / 1e6}
 
     # the sampler ran through the kernel-timed loop, the per-kernel pass and the end-to-end loop
     clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        roofline["fp32_ceiling_gbs"] = fp32_ceiling_gbs(cfg, B, step_bytes, (clocks_mid or clocks or {}).get("sm_mhz"))
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -380,11 +543,12 @@ def run_gpu_arm(args):
             "config": {"workload": args.config, "n": n, "nblocks": cfg["nblocks"], "nstacks": S,
                        "batch_per_gpu": B, "global_batch": B * world, "parallelism": "batch-sharded x%d" % world,
                        "l2": "inputs (%.0f MB per step per GPU) exceed the 126 MB L2; no flush" % (step_bytes / 1e6),
-                       "collective": "one NCCL all-reduce(sum) of d_twiddle per step" if world > 1 else "none"},
+                       "collective": ("one NCCL all-reduce(sum) of d_twiddle per step, on a side stream while the next "
+                                      "step computes") if world > 1 else "none"},
             "batch_n_per_s": B * S * n * world / (ms_per_step * 1e-3),
             "frac_of_hbm_peak": value / world / peak,
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
-            "gpu_launches": launches,
+            "gpu_launches": launches, "other_configs": other, "reference_cuda": ref_cuda_note,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -403,6 +567,8 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=8, help="row chunks of the host-memory pipeline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-other", action="store_true", help="skip the other configurations (other_configs)")
+    ap.add_argument("--no-refcuda", action="store_true", help="skip the reference's CUDA extension in other_configs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -289,7 +289,7 @@ def device_error():
     return rc
 
 
-KERNEL_NAMES = ("bfly_fw_kernel", "bfly_bw_kernel")
+KERNEL_NAMES = ("bfly_fw_kernel", "bfly_bw_kernel", "bfly_fw2_kernel", "bfly_bw2_kernel", "bfly_bw3_kernel")
 
 
 def profile_enable(on=True):

@@ -393,7 +393,7 @@ static std::atomic<int64_t> g_launches{0};
 
 // Optional per-launch timing (bfly_profile_*): while enabled, every kernel launch is
 // bracketed by a pair of CUDA events on the launching stream.
-enum KernelId : int { kKernFw = 0, kKernBw = 1, kNumKernelIds = 2 };
+enum KernelId : int { kKernFw = 0, kKernBw = 1, kKernFw2 = 2, kKernBw2 = 3, kKernBw3 = 4, kNumKernelIds = 5 };
 struct ProfileRec { int id; cudaEvent_t a, b; };
 static std::mutex g_prof_mu;
 static bool g_prof_on = false;
@@ -476,7 +476,7 @@ struct CudaExec {
     CUtensorMap mx, mg, mo;
     describe_bw(p, kBw2Rows, mx, mg, mo);
     {
-      ProfileScope prof(kKernBw, stream);
+      ProfileScope prof(kKernBw2, stream);
       bfly_bw2_kernel<T, KW, LOGC><<<bw_num_ctas(p), kThreads, smem, stream>>>(p, mx, mg, mo);
     }
     g_launches.fetch_add(1);
@@ -543,7 +543,7 @@ struct CudaExec {
     if (rc) return rc;
     int launches = 0;
     {
-      ProfileScope prof(kKernFw, stream);
+      ProfileScope prof(kKernFw2, stream);
       rc = fw2_launch(p, ctas_per_sm, dev.sms, stream, err, &launches);
     }
     if (rc == BFLY_OK) g_launches.fetch_add(launches);
@@ -558,7 +558,7 @@ struct CudaExec {
     int rc = device_error_ptr(&err);
     if (rc) return rc;
     {
-      ProfileScope prof(kKernBw, stream);
+      ProfileScope prof(kKernBw3, stream);
       rc = bw3_launch(p, mx, mg, mo, stream, err);
     }
     if (rc == BFLY_OK) g_launches.fetch_add(1);

@@ -44,3 +44,41 @@ def sync_twiddle_grad(twiddle: torch.Tensor, group=None) -> torch.Tensor:
     is all-reduced (SUM) over the ranks.  Use it on the replicated parameter of a batch-sharded
     layer:  ``y = butterfly_multiply(sync_twiddle_grad(layer.twiddle), x_local, True)``."""
     return _SyncTwiddleGrad.apply(twiddle, group)
+
+
+class AsyncTwiddleReducer:
+    """All-reduce(SUM) of twiddle gradients on a side stream, off the compute stream's critical path.
+
+    The all-reduce of a latency-sized message (the twiddle gradient is a few hundred KB) costs
+    tens of microseconds that nothing on the compute stream needs to wait for: the reduced
+    gradient is only read by the optimizer step.  ``submit(d_twiddle)`` makes the side stream wait
+    for the kernels that produce the gradient (an event on the current stream) and enqueues the
+    all-reduce there; the next step's forward starts at once.  ``wait()`` makes the current stream
+    (and therefore whatever reads the gradients next) wait for every all-reduce submitted so far.
+    Without a process group both are no-ops.
+    """
+
+    def __init__(self, device, group=None):
+        self.device = torch.device(device)
+        self.group = group
+        self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.stream = torch.cuda.Stream(self.device) if self.active else None
+        self.pending = []
+
+    def submit(self, d_twiddle: torch.Tensor) -> torch.Tensor:
+        if not self.active:
+            return d_twiddle
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        d_twiddle.record_stream(self.stream)
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(ready)
+            allreduce_twiddle_grad(d_twiddle, self.group)
+        self.pending.append(d_twiddle)
+        return d_twiddle
+
+    def wait(self):
+        if self.active:
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        done, self.pending = self.pending, []
+        return done

@@ -19,7 +19,11 @@ class HostPipeline:
         pipe.fw_bw(twiddle_dev, x_host, grad_host, increasing_stride, out_host, d_x_host, d_twiddle_host)
 
     x_host (B, Sx, n) with Sx = 1 (one row shared by all stacks) or Sx = nstacks; grad_host,
-    out_host, d_x_host (B, nstacks, n); all pinned.  Returns after the last download finished.
+    out_host, d_x_host (B, nstacks, n); all pinned.
+
+    fw_bw only ENQUEUES the work: when it returns, the caller's current stream has been made to
+    wait for the copies, but the host has not.  Call ``wait()`` (or synchronise the current
+    stream) before reading out_host / d_x_host / d_twiddle_host on the CPU.
     """
 
     def __init__(self, device, chunks=8):
@@ -70,6 +74,40 @@ class HostPipeline:
             if d_tw_total is not None:
                 d_tw_total.record_stream(self.s_out)
                 d_twiddle_host.copy_(d_tw_total, non_blocking=True)
+            self.done = torch.cuda.Event()
+            self.done.record(self.s_out)
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_comp)
         return d_tw_total
+
+    def wait(self):
+        """Blocks the host until the downloads of the last fw_bw call have landed in host memory."""
+        if getattr(self, "done", None) is not None:
+            self.done.synchronize()
+
+    # The two copy directions alone, with the same chunking and streams: what each direction of the
+    # host link sustains without the other (benchmarks report them beside the pipelined number).
+    def upload_only(self, x_host, grad_host):
+        B = x_host.shape[0]
+        cur = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            for c in range(self.chunks):
+                lo, hi = B * c // self.chunks, B * (c + 1) // self.chunks
+                if hi > lo:
+                    x_host[lo:hi].to(self.device, non_blocking=True)
+                    grad_host[lo:hi].to(self.device, non_blocking=True)
+        cur.wait_stream(self.s_in)
+
+    def download_only(self, out_host, d_x_host):
+        B = out_host.shape[0]
+        cur = torch.cuda.current_stream(self.device)
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_out):
+            for c in range(self.chunks):
+                lo, hi = B * c // self.chunks, B * (c + 1) // self.chunks
+                if hi > lo:
+                    src = torch.empty((hi - lo,) + tuple(out_host.shape[1:]), dtype=out_host.dtype, device=self.device)
+                    out_host[lo:hi].copy_(src, non_blocking=True)
+                    d_x_host[lo:hi].copy_(src, non_blocking=True)
+        cur.wait_stream(self.s_out)

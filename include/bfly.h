@@ -199,11 +199,15 @@ int bfly_device_error(void);
 
 /* Per-kernel timing for benchmarks.  While enabled, every launch is bracketed by a pair of
  * CUDA events on its stream.  bfly_profile_collect waits for the recorded launches, adds
- * their count and device time into launches[id] / total_ms[id] (id 0 = forward kernel,
- * 1 = backward-phase kernel; n_ids entries each) and forgets them.  Leave it disabled in
- * production: the events serialise nothing but do cost host time. */
-#define BFLY_KERNEL_FW 0
-#define BFLY_KERNEL_BW 1
+ * their count and device time into launches[id] / total_ms[id] (ids below; n_ids entries each)
+ * and forgets them.  Leave it disabled in production: the events serialise nothing but do cost
+ * host time. */
+#define BFLY_KERNEL_FW 0   /* generic forward kernel (bfly_fw_kernel) */
+#define BFLY_KERNEL_BW 1   /* first-generation backward phase kernel (bfly_bw_kernel) */
+#define BFLY_KERNEL_FW2 2  /* packed-pair forward kernel with its twiddle re-ordering kernel (bfly_fw2_kernel) */
+#define BFLY_KERNEL_BW2 3  /* backward phase kernel with accumulators in tensor memory (bfly_bw2_kernel) */
+#define BFLY_KERNEL_BW3 4  /* packed-pair backward phase kernel (bfly_bw3_kernel) */
+#define BFLY_KERNEL_IDS 5
 void bfly_profile_enable(int on);
 int bfly_profile_collect(int64_t* launches, double* total_ms, int n_ids);
 
