@@ -8,5 +8,5 @@ Only the tests, the smoke check and the benchmark's CPU-baseline leg may import 
 package; the shipped CUDA path never does.
 """
 from .oracle import (  # noqa: F401
-    multiply_fw, multiply_bw, base4_fw, base4_bw, build, load_reference_ops, reference_available,
+    multiply_fw, multiply_bw, base4_fw, base4_bw, build, load_reference_ops, reference_available, reference_dir, REF_PKG,
 )

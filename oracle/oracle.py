@@ -28,9 +28,23 @@ def build(force=False):
                                               for f in ("bfly_oracle.c", "bfly_oracle_impl.h"))):
         subprocess.check_call(["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared",
                                os.path.join(_HERE, "bfly_oracle.c"), "-o", _LIB_PATH])
-    ref_src = os.environ.get("BFLY_REFERENCE_DIR", "/root/reference")
-    if os.path.exists(os.path.join(ref_src, "csrc", "cpu", "butterfly_cpu.cpp")) and not os.path.exists(_REF_CPU):
-        subprocess.check_call(["make", "-C", _HERE, "refcpu", f"REF={ref_src}"])
+    ref_src = reference_dir()
+    if ref_src and os.path.exists(os.path.join(ref_src, "csrc", "cpu", "butterfly_cpu.cpp")):
+        if not os.path.exists(_REF_CPU):
+            subprocess.check_call(["make", "-C", _HERE, "refcpu", f"REF={ref_src}"])
+        if not os.path.exists(os.path.join(REF_PKG, "torch_butterfly", "__init__.py")):
+            subprocess.check_call(["make", "-C", _HERE, "refpy", f"REF={ref_src}"])
+
+
+# the reference's Python package and three of its test files, staged by `make refpy`
+REF_PKG = os.path.join(_HERE, "_ref", "pkg")
+
+
+def reference_dir():
+    """Root of the reference tree: $BFLY_REFERENCE_DIR, else a directory named `reference` beside
+    this repository; None when neither exists."""
+    cand = os.environ.get("BFLY_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(cand) else None
 
 
 def _load():

@@ -77,10 +77,11 @@ def test_reference_package_imports_on_top_of_these_libraries(tmp_path):
     """The reference's unmodified Python package loads `_version` and `_butterfly` from its own
     directory (torch_butterfly/__init__.py:8-11); link its .py files beside our libraries and
     import it in a fresh interpreter."""
-    ref = os.environ.get("BFLY_REFERENCE_DIR", "/root/reference")
-    pkg = os.path.join(ref, "torch_butterfly")
+    import oracle
+    ref = oracle.reference_dir()
+    pkg = os.path.join(ref, "torch_butterfly") if ref else os.path.join(oracle.REF_PKG, "torch_butterfly")
     if not os.path.isdir(pkg):
-        pytest.skip("reference tree not present")
+        pytest.skip("reference tree not present and not staged (make -C oracle refpy)")
     import subprocess
     import sys
     shim = tmp_path / "torch_butterfly"
