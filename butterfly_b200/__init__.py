@@ -34,7 +34,9 @@ def _load_native():
 
 _load_native()
 
-from .multiply import butterfly_multiply, butterfly_multiply_fw, butterfly_multiply_bw  # noqa: E402,F401
+from .multiply import (  # noqa: E402,F401
+    butterfly_multiply, butterfly_multiply_fw, butterfly_multiply_bw, butterfly_linear, butterfly_linear_fw, butterfly_linear_bw,
+)
 from .multiply_base4 import (  # noqa: E402,F401
     butterfly_multiply_base4, butterfly_multiply_base4_fw, butterfly_multiply_base4_bw, twiddle_base2_to_base4,
 )
@@ -44,6 +46,7 @@ from . import permutation, special, host, distributed  # noqa: E402,F401
 
 __all__ = [
     "butterfly_multiply", "butterfly_multiply_fw", "butterfly_multiply_bw",
+    "butterfly_linear", "butterfly_linear_fw", "butterfly_linear_bw",
     "butterfly_multiply_base4", "butterfly_multiply_base4_fw", "butterfly_multiply_base4_bw",
     "twiddle_base2_to_base4", "abi", "__version__", "Butterfly", "ButterflyUnitary", "ButterflyBmm", "ButterflyBase4",
     "permutation", "special",

@@ -20,7 +20,7 @@ SYMBOLS = (
     "bfly_strerror", "bfly_version", "bfly_cuda_version", "bfly_fw_f32", "bfly_fw_c64", "bfly_fw_workspace_bytes",
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
-    "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
+    "bfly_linear_fw_f32", "bfly_linear_bw_f32", "bfly_linear_bw_workspace_bytes", "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -39,6 +39,7 @@ def lib():
         L.bfly_strerror.argtypes = [ctypes.c_int]
         L.bfly_bw_workspace_bytes.restype = ctypes.c_int64
         L.bfly_fw_workspace_bytes.restype = ctypes.c_int64
+        L.bfly_linear_bw_workspace_bytes.restype = ctypes.c_int64
         L.bfly4_bw_workspace_bytes.restype = ctypes.c_int64
         L.bfly_launch_count.restype = ctypes.c_int64
         _lib = L
@@ -210,6 +211,49 @@ def bw_noalloc(twiddle, x, grad, increasing_stride=True, d_twiddle=None, d_x=Non
     if check and rc != 0:
         raise BflyError(rc, "bfly_bw_f32_noalloc")
     return d_twiddle, d_x, rc
+
+
+def linear_fw(twiddle, x2d, bias=None, increasing_stride=True, output_size=None, check=True):
+    """``bfly_linear_fw_f32``: x2d (batch, in) -> the (batch, nstacks * n) output buffer (the layer's output
+    is its first output_size columns, bias included) and the status."""
+    assert x2d.is_cuda and x2d.dim() == 2 and x2d.dtype == torch.float32 and x2d.stride(1) == 1
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, in_size = x2d.shape
+    output_size = S * n if output_size is None else output_size
+    out = torch.empty(B, S * n, dtype=x2d.dtype, device=x2d.device)
+    need = fw_workspace_bytes(x2d.dtype, B, S, log_n, nblocks)
+    ws = torch.empty(need, dtype=torch.uint8, device=x2d.device) if need > 0 else None
+    rc = lib().bfly_linear_fw_f32(_p(twiddle), _p(x2d), _i64(x2d.stride(0)), _p(out), _p(bias), int(B), int(S), int(log_n),
+                                  int(nblocks), int(in_size), int(output_size), int(bool(increasing_stride)), _p(ws),
+                                  ctypes.c_size_t(need if ws is not None else 0), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_linear_fw_f32")
+    return out, rc
+
+
+def linear_bw(twiddle, x2d, grad2d, increasing_stride=True, with_bias=True, check=True):
+    """``bfly_linear_bw_f32``: (d_twiddle, d_input (batch, in), d_bias or None, status).  Status -2
+    (BFLY_E_UNSUPPORTED) = the fused route does not apply; nothing was written."""
+    S, nblocks, log_n = twiddle.shape[:3]
+    B, in_size = x2d.shape
+    out_size = grad2d.shape[1]
+    d_tw = torch.empty_like(twiddle)
+    d_in = torch.empty(B, in_size, dtype=x2d.dtype, device=x2d.device)
+    d_b = torch.empty(out_size, dtype=x2d.dtype, device=x2d.device) if with_bias else None
+    need = int(lib().bfly_linear_bw_workspace_bytes(int(B), int(S), int(log_n), int(nblocks)))
+    if need < 0:
+        if check:
+            raise BflyError(need, "bfly_linear_bw_workspace_bytes")
+        return d_tw, d_in, d_b, need
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x2d.device)
+    rc = lib().bfly_linear_bw_f32(_p(twiddle), _p(x2d), _i64(x2d.stride(0)), _p(grad2d), _i64(grad2d.stride(0)), _p(d_tw),
+                                  _p(d_in), _i64(d_in.stride(0)), _p(d_b), int(B), int(S), int(log_n), int(nblocks),
+                                  int(in_size), int(out_size), int(bool(increasing_stride)), _p(ws),
+                                  ctypes.c_size_t(ws.numel()), _stream())
+    if check and rc != 0:
+        raise BflyError(rc, "bfly_linear_bw_f32")
+    return d_tw, d_in, d_b, rc
 
 
 def fw_base4(twiddle4, twiddle2, x, increasing_stride=True, output_size=None, out=None, check=True):

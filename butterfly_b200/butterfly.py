@@ -11,7 +11,7 @@ import numbers
 import torch
 from torch import nn
 
-from .multiply import butterfly_multiply
+from .multiply import butterfly_linear, butterfly_multiply
 from .multiply_base4 import butterfly_multiply_base4, twiddle_base2_to_base4
 
 _COMPLEX = {torch.float32: torch.complex64, torch.float64: torch.complex128}
@@ -116,8 +116,19 @@ class Butterfly(nn.Module):
         """input (..., in_size) -> (..., out_size).
 
         transpose / conjugate apply the transposed / conjugated matrix; subtwiddle uses the
-        leading part of the parameters for a shorter input (output size nstacks * n')."""
+        leading part of the parameters for a shorter input (the output then has the n' columns of
+        the first stack, as in the reference: torch_butterfly/butterfly.py:147-150)."""
         twiddle = self._effective_twiddle()
+        if (not subtwiddle and twiddle.dtype == torch.float32 and input.dtype == torch.float32 and input.is_cuda
+                and type(self).pre_process is Butterfly.pre_process and type(self).post_process is Butterfly.post_process):
+            # real float32 layer: one fused operator instead of expand / multiply / flatten / slice / bias
+            inc = self.increasing_stride
+            if transpose:
+                twiddle = twiddle.transpose(-1, -2).flip([1, 2])
+                inc = not (self.increasing_stride != ((self.nblocks - 1) % 2 == 1))
+            rows = _as_rows(input, input.size(-1))
+            out = butterfly_linear(twiddle, rows, self.bias, inc, self.out_size)
+            return out.reshape(*input.shape[:-1], self.out_size)
         rows = self.pre_process(input)
         output_size = self.out_size if self.nstacks == 1 else None
         if subtwiddle:
@@ -134,7 +145,7 @@ class Butterfly(nn.Module):
             twiddle = twiddle.transpose(-1, -2).flip([1, 2])
             last_increasing = self.increasing_stride != ((self.nblocks - 1) % 2 == 1)
             out = butterfly_multiply(twiddle, rows, not last_increasing, output_size)
-        return self.post_process(input, out, out_size=out.size(-1) * self.nstacks if subtwiddle else None)
+        return self.post_process(input, out, out_size=out.size(-1) if subtwiddle else None)
 
     def pre_process(self, input):
         rows = _as_rows(input, input.size(-1))

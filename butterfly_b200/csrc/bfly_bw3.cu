@@ -75,6 +75,9 @@ bfly_bw3_kernel(const __grid_constant__ Bw3Params p, const __grid_constant__ CUt
   float tr[32], ar[32];  // tensor-memory fetch buffers (operands of the step that comes next, when prefetching)
   if (kBw3Prefetch) bw3_prefetch(p, acc, 0, tr, ar);
   const int nsteps = bw3_num_steps(q.nsg);
+  // bias gradient of a fused linear layer: this thread's 8 columns of the panel, summed over the
+  // rows of the incoming gradient
+  float db[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   bool gave_up = false;  // a bounded wait ran out: stop, and keep the partial sums out of d_twiddle
 
   for (int row0 = row_begin; row0 < row_end; row0 += kBw3Rows) {
@@ -100,6 +103,16 @@ bfly_bw3_kernel(const __grid_constant__ Bw3Params p, const __grid_constant__ CUt
         break;
       }
     }
+    if (q.dbias) {  // column sums of the gradient tile as it arrived (16-byte chunks 2 tid, 2 tid + 1 of every row)
+#pragma unroll
+      for (int r = 0; r < kBw3Rows; ++r)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int l = 8 * tid + 4 * h;
+          const float4 v = *reinterpret_cast<const float4*>(sm + (size_t)(q.nsg * kBw3Rows + r) * 1024 + swz<2>(l));
+          db[4 * h + 0] += v.x; db[4 * h + 1] += v.y; db[4 * h + 2] += v.z; db[4 * h + 3] += v.w;
+        }
+    }
     for (; step < nsteps; ++step) {
       bw3_step(p, acc, meta, step, sm, tid, tr, ar);
       if (step + 1 == nsteps) fence_async_smem();  // the gradient tile is read by the TMA unit next
@@ -108,7 +121,8 @@ bfly_bw3_kernel(const __grid_constant__ Bw3Params p, const __grid_constant__ CUt
     if (tid == 0) {
       const bool more = row0 + kBw3Rows < row_end;
       if (more) issue_load_x(row0 + kBw3Rows);  // the snapshot tiles are free already
-      tma_store_tile(&map_o, smG, c1, c2, so, row0);
+      if (q.gout_reduce) tma_reduce_add_tile(&map_o, smG, c1, c2, so, row0);
+      else tma_store_tile(&map_o, smG, c1, c2, so, row0);
       tma_store_commit();
       if (more) {
         tma_store_wait_read();  // the gradient tile is free again
@@ -119,6 +133,13 @@ bfly_bw3_kernel(const __grid_constant__ Bw3Params p, const __grid_constant__ CUt
   if (tid == 0) tma_store_wait_all();
   if (kBw3Prefetch) acc.wait_ld();  // the fetch issued by the last step
   if (!gave_up) bw3_flush(p, acc, stack, pbase, tid);
+  if (!gave_up && q.dbias) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int flat = stack * (1 << q.log_n) + q.panel.col(pbase, 8 * tid + e);
+      if (flat < q.dbias_len) atomicAdd(q.dbias + flat, db[e]);
+    }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {

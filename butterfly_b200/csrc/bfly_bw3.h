@@ -90,7 +90,7 @@ inline bool bw3_plan(const BwParams<float>& p, Bw3Sg* out) {
     const BwSg& s = p.sg[j];
     Bw3Sg& o = out[j];
     std::memset(&o, 0, sizeof(o));
-    if (s.radix != 2 || s.nst < 1 || s.nst > 2 || (s.lbit & 1)) return false;
+    if (s.radix != 2 || s.nst < 1 || s.nst > 2 || s.lbit == 1) return false;  // (a window on local bits 1, 2 has no 8-byte pairing)
     o.nst = s.nst;
     o.contig = s.lbit == 0;
     o.lbit = s.lbit;

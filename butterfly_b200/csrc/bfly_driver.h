@@ -11,8 +11,10 @@
 //   int  run_bw(const BwParams<T>&, int KW);               // one backward-phase launch
 //   int  run_bw3(const Bw3Params&);                        // one launch of the packed-pair backward phase kernel
 //                                                          // (kFw2Declined: not available for these tensors)
+//   bool can_run_bw3(const Bw3Params&);                    // would run_bw3 accept these tensors?
 //   int  zero(void* ptr, size_t bytes);                    // async memset
 //   int  zero2d(void* ptr, size_t pitch_bytes, size_t width_bytes, size_t rows);
+//   int  add_bias(float* out, const float* bias, int64_t B, int len, int64_t pitch);   // out[b, f] += bias[f], f < len
 #pragma once
 #include <cstdlib>
 #include <cstring>
@@ -182,7 +184,8 @@ template <typename T> inline int fw_pass_logc(int log_n) {
 template <typename E>
 int drive_fw2(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int t1, const std::vector<int>& cuts,
               float* const* snaps, const float* tw2, const float* x, int64_t x_sB, int64_t x_sS, int x_cols, float* out,
-              int64_t out_sB, int64_t out_sS, int out_cols, void* pack_ws, size_t pack_bytes) {
+              int64_t out_sB, int64_t out_sS, int out_cols, void* pack_ws, size_t pack_bytes, const float* bias = nullptr,
+              int bias_len = 0) {
   if (q.base4 || !tw2 || !pack_ws || !fw2_enabled()) return kFw2Declined;
   std::vector<Fw2Group> groups;
   if (!plan_fw2_groups(st, t0, t1, cuts, q.log_n, groups)) return kFw2Declined;
@@ -202,6 +205,7 @@ int drive_fw2(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int
   if ((size_t)p.packed_stack * q.S * 16 > pack_bytes) return kFw2Declined;
   p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
   p.out = out; p.out_sB = out_sB; p.out_sS = out_sS; p.out_cols = out_cols;
+  p.bias = bias; p.bias_len = bias_len;
   for (int i = 0; i < kFw2MaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
   p.ngroups = (int)groups.size();
   for (int g = 0; g < p.ngroups; ++g) {
@@ -524,6 +528,139 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
   if (q.in_size > n) {
     rc = ex.zero2d(d_x + n, (size_t)DX * sizeof(T), (size_t)(q.in_size - n) * sizeof(T), (size_t)q.B * q.S);
     if (rc != BFLY_OK) return rc;
+  }
+  return BFLY_OK;
+}
+
+// ------------------------------------------------------------------ fused linear layer (float32)
+//
+// Butterfly as a linear layer (torch_butterfly/butterfly.py:152-169 of the reference): every stack
+// multiplies the same input row (B, in); the outputs of the stacks side by side form (B, S * n), of
+// which the first out_total columns are the layer's output, plus a bias.  Fused here:
+//   forward   the bias is added in the forward kernel's store epilogue (no extra pass over the output);
+//   backward  the input gradient is summed over the stacks by the last phase's store (a float32
+//             reduce-add of its tiles into (B, in)), and the bias gradient (column sums of grad)
+//             is accumulated by the first phase while it holds the gradient tiles.
+// The backward runs only when every phase qualifies for the packed-pair kernel; otherwise it returns
+// BFLY_E_UNSUPPORTED before touching any output, and the caller composes the unfused operators.
+
+template <typename E>
+int drive_linear_fw(E& ex, const Problem& q, const float* tw, const float* x, int64_t x_sB, float* out, const float* bias,
+                    int out_total, void* ws, size_t ws_bytes) {
+  int rc = check_problem(q);
+  if (rc != BFLY_OK) return rc;
+  if (q.base4 || out_total < 0 || out_total > ((int64_t)q.S << q.log_n)) return BFLY_E_ARG;
+  if (q.B == 0) return BFLY_OK;
+  if (!x || !out || !tw) return BFLY_E_ARG;
+  if (!aligned16(tw)) return BFLY_E_ALIGN;
+  const std::vector<Stage> st = problem_stages(q);
+  const int64_t n = (int64_t)1 << q.log_n;
+  if (ws && !aligned16(ws)) ws = nullptr;
+  // the packed-pair kernel adds the bias itself; any other route adds it afterwards
+  bool fused_bias = false;
+  if (bias) {
+    const int rc2 = drive_fw2(ex, q, st, 0, (int)st.size(), {}, (float* const*)nullptr, tw, x, x_sB, 0, q.in_size, out,
+                              (int64_t)q.S * n, n, (int)n, ws, ws ? ws_bytes : 0, bias, out_total);
+    if (rc2 == BFLY_OK) return BFLY_OK;
+    if (rc2 != kFw2Declined) return rc2;
+  }
+  rc = drive_fw_range<float>(ex, q, st, 0, (int)st.size(), {}, nullptr, tw, (const float*)nullptr, x, x_sB, 0, q.in_size, out,
+                             (int64_t)q.S * n, n, (int)n, (float*)nullptr, 0, 0, ws, ws ? ws_bytes : 0);
+  if (rc != BFLY_OK || !bias || fused_bias) return rc;
+  return ex.add_bias(out, bias, q.B, out_total, (int64_t)q.S * n);
+}
+
+struct LinearBwLayout {
+  BwLayout<float> lay;
+  size_t gbuf_off, ws_bytes;  // the gradient plane between phases follows the backward's own scratch
+};
+inline int plan_linear_bw(const Problem& q, LinearBwLayout& L) {
+  const int rc = plan_bw<float>(q, L.lay);
+  if (rc != BFLY_OK) return rc;
+  const size_t plane = ((size_t)q.B * q.S * sizeof(float) << q.log_n);
+  L.gbuf_off = L.lay.ws_bytes;
+  L.ws_bytes = L.lay.ws_bytes + (plane + 255) / 256 * 256;
+  return BFLY_OK;
+}
+
+template <typename E>
+int drive_linear_bw(E& ex, const Problem& q, const float* tw, const float* x, int64_t x_sB, const float* grad, int64_t g_sB,
+                    float* d_tw, float* d_in, int64_t din_sB, float* d_bias, int out_total, void* ws, size_t ws_bytes) {
+  int rc = check_problem(q);
+  if (rc != BFLY_OK) return rc;
+  const int64_t n = (int64_t)1 << q.log_n;
+  const Options& o = options();
+  // the fused route: all stacks full, every tensor describable to the TMA unit, every phase on the
+  // packed-pair kernel
+  if (q.base4 || out_total != q.S * n || q.in_size > n || q.in_size % 32 != 0 || q.B < kBw3Rows) return BFLY_E_UNSUPPORTED;
+  if (o.bw3 == 0 || o.tma == 0 || o.bw_rows >= 0 || o.bw_v2 == 0 || !fw2_enabled()) return BFLY_E_UNSUPPORTED;
+  if (!tw || !d_tw || !x || !grad || !d_in || !ws) return BFLY_E_ARG;
+  if (!aligned16(tw) || !aligned16(d_tw)) return BFLY_E_ALIGN;
+  if (!vec_ok<float>(x, x_sB, 0) || !vec_ok<float>(grad, g_sB, n) || !vec_ok<float>(d_in, din_sB, 0) || !aligned16(ws))
+    return BFLY_E_UNSUPPORTED;
+  LinearBwLayout L;
+  rc = plan_linear_bw(q, L);
+  if (rc != BFLY_OK) return rc;
+  if (ws_bytes < L.ws_bytes) return BFLY_E_WORKSPACE;
+  const BwLayout<float>& lay = L.lay;
+  const int nph = (int)lay.phases.size();
+  if (lay.chunked || lay.kw != 2) return BFLY_E_UNSUPPORTED;
+  int64_t stk[2];
+  twiddle_stack_sizes(q, stk);
+  const std::vector<Stage> st = problem_stages(q);
+  std::vector<Bw3Params> launches((size_t)nph);
+  const size_t plane = ((size_t)q.B * q.S * sizeof(float) << q.log_n);
+  const size_t plane_pad = (plane + 255) / 256 * 256;
+  float* gbuf = reinterpret_cast<float*>(static_cast<char*>(ws) + L.gbuf_off);
+  float* snaps[kMaxSnap] = {nullptr};
+  std::vector<int> cuts;
+  for (int ph = 1; ph < nph; ++ph) {
+    snaps[ph - 1] = reinterpret_cast<float*>(static_cast<char*>(ws) + (size_t)(ph - 1) * plane_pad);
+    cuts.push_back(lay.phases[ph].t0);
+  }
+  for (int ph = 0; ph < nph; ++ph) {
+    const BwPhase& P = lay.phases[ph];
+    Bw3Params& p3 = launches[ph];
+    std::memset(&p3, 0, sizeof(p3));
+    BwParams<float>& b = p3.b;
+    b.tw[0] = tw; b.dtw[0] = d_tw; b.tw_stack[0] = stk[0];
+    if (ph == 0) { b.xin = x; b.xin_sB = x_sB; b.xin_sS = 0; b.xin_cols = q.in_size; }
+    else { b.xin = snaps[ph - 1]; b.xin_sB = (int64_t)q.S * n; b.xin_sS = n; b.xin_cols = (int)n; }
+    if (ph == nph - 1) { b.gin = grad; b.gin_sB = g_sB; b.gin_sS = n; b.gin_cols = (int)n; }
+    else { b.gin = gbuf; b.gin_sB = (int64_t)q.S * n; b.gin_sS = n; b.gin_cols = (int)n; }
+    if (ph == 0) { b.gout = d_in; b.gout_sB = din_sB; b.gout_sS = 0; b.gout_cols = q.in_size; b.gout_reduce = 1; }
+    else { b.gout = gbuf; b.gout_sB = (int64_t)q.S * n; b.gout_sS = n; b.gout_cols = (int)n; }
+    if (ph == nph - 1 && d_bias) { b.dbias = d_bias; b.dbias_len = out_total; }
+    b.B = q.B; b.S = q.S; b.log_n = q.log_n;
+    b.panel = P.panel;
+    b.nsg = P.nsg;
+    for (int j = 0; j < P.nsg; ++j) b.sg[j] = P.sg[j];
+    if (!bw3_plan(b, p3.sg)) return BFLY_E_UNSUPPORTED;
+    b.Rb = kBw3Rows;
+    const int groups3 = (1 << P.panel.npanels_log) * q.S;
+    const int nsl = std::max(1, 2 * ex.num_sms() / groups3);
+    int rows3 = (q.B + nsl - 1) / nsl;
+    rows3 = (rows3 + kBw3Rows - 1) / kBw3Rows * kBw3Rows;
+    b.rows_per_cta = rows3;
+    b.nslices = (q.B + rows3 - 1) / rows3;
+    b.vec_x = b.vec_g = b.vec_o = 1;
+    if (!ex.can_run_bw3(p3)) return BFLY_E_UNSUPPORTED;  // a tensor of this phase cannot be described to the TMA unit
+  }
+  // nothing has been written so far; from here on every step must succeed
+  rc = ex.zero(d_tw, (size_t)q.S * stk[0] * sizeof(float));
+  if (rc) return rc;
+  rc = ex.zero2d(d_in, (size_t)din_sB * sizeof(float), (size_t)q.in_size * sizeof(float), (size_t)q.B);
+  if (rc) return rc;
+  if (d_bias) { rc = ex.zero(d_bias, (size_t)out_total * sizeof(float)); if (rc) return rc; }
+  if (!cuts.empty()) {
+    void* pack_ws = lay.pack_bytes ? static_cast<char*>(ws) + lay.pack_off : nullptr;
+    rc = drive_fw_range<float>(ex, q, st, 0, lay.phases[nph - 1].t0, cuts, snaps, tw, (const float*)nullptr, x, x_sB, 0,
+                               q.in_size, (float*)nullptr, 0, 0, 0, gbuf, (int64_t)q.S * n, n, pack_ws, lay.pack_bytes);
+    if (rc != BFLY_OK) return rc;
+  }
+  for (int ph = nph - 1; ph >= 0; --ph) {
+    rc = ex.run_bw3(launches[ph]);
+    if (rc != BFLY_OK) return rc == kFw2Declined ? BFLY_E_UNSUPPORTED : rc;
   }
   return BFLY_OK;
 }

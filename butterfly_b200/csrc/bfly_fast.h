@@ -17,6 +17,9 @@ namespace bfly {
 // kernel whose bounded wait ran out raises.  `launches`: kernels launched.
 int fw2_launch(const Fw2Params& p, int ctas_per_sm, int sms, cudaStream_t stream, int* err, int* launches);
 
+// out[b, f] += bias[f], f < len, on a (B, width) matrix with row pitch `pitch` (elements).
+int bias_add_launch(float* out, const float* bias, int64_t B, int len, int64_t pitch, int sms, cudaStream_t stream);
+
 // Launch the packed-pair backward phase kernel.  The three descriptors (activation in, gradient
 // in, gradient out) describe boxes of kBw3Rows rows of the phase's panel (bfly_tma.h).
 int bw3_launch(const Bw3Params& p, const CUtensorMap& mx, const CUtensorMap& mg, const CUtensorMap& mo, cudaStream_t stream,

@@ -88,8 +88,30 @@ bfly_fw2_kernel(const __grid_constant__ Fw2Params p, const __grid_constant__ Fw2
     mbar_expect_tx(mybar, box_bytes);
     tma_load_box4(mybox, &maps.in, mybar, chunk * 16, p.x_stack ? stack : 0, row0);
   };
+  // Bias epilogue: every lane adds bias[stack * n + column] to its 16 columns of each row of the
+  // warp's box (16-byte accesses; the swizzle moves whole 16-byte chunks).
+  auto add_bias = [&](int stack) {
+    const int col0 = chunk * 512 + lane * 16;
+    const int flat0 = stack * (1 << p.log_n) + col0;
+    float4 b[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int f = flat0 + 4 * k;
+      b[k] = make_float4(f + 0 < p.bias_len ? __ldg(p.bias + f + 0) : 0.f, f + 1 < p.bias_len ? __ldg(p.bias + f + 1) : 0.f,
+                         f + 2 < p.bias_len ? __ldg(p.bias + f + 2) : 0.f, f + 3 < p.bias_len ? __ldg(p.bias + f + 3) : 0.f);
+    }
+    for (int i = 0; i < Rw; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float4* q = reinterpret_cast<float4*>(tile + fw2_tile_index(p.R, rg * Rw + i, col0 + 4 * k));
+        float4 v = *q;
+        v.x += b[k].x; v.y += b[k].y; v.z += b[k].z; v.w += b[k].w;
+        *q = v;
+      }
+    }
+  };
   // store the warp's box; `local`: only this warp wrote it since the last CTA barrier
-  auto store_box = [&](const CUtensorMap* map, bool local, int stack, int row0, bool wanted) -> bool {
+  auto store_box = [&](const CUtensorMap* map, bool local, int stack, int row0, bool wanted, bool with_bias) -> bool {
     fence_async_smem();  // the box is read by the TMA unit next
     if (local) {
       __syncwarp();
@@ -97,8 +119,13 @@ bfly_fw2_kernel(const __grid_constant__ Fw2Params p, const __grid_constant__ Fw2
       __syncthreads();
       if (*give_up) return false;
     }
+    if (with_bias) {  // the box is complete and this warp's alone
+      add_bias(stack);
+      fence_async_smem();
+      __syncwarp();
+    }
     if (lane == 0 && wanted) {
-      tma_store_box4(map, mybox, chunk * 16, stack, row0);
+      tma_store_box4(map, mybox, chunk * 16, (map == &maps.out && !p.out_stack) ? 0 : stack, row0);
       tma_store_commit();
       tma_store_wait_read();  // the box may be overwritten
     }
@@ -155,11 +182,11 @@ bfly_fw2_kernel(const __grid_constant__ Fw2Params p, const __grid_constant__ Fw2
         fw2_fetch_tw(p, g, stack, tid, TA);
         fw2_group_dispatch<false>(p, g, tile, tid, TA);
       }
-      if (g.emit) alive = store_box(&maps.snap[g.emit - 1], g.local != 0, stack, row0, true);  // snapshots are full width
+      if (g.emit) alive = store_box(&maps.snap[g.emit - 1], g.local != 0, stack, row0, true, false);  // snapshots are full width
     }
     if (!alive) break;
     if (p.has_out) {
-      if (!store_box(&maps.out, p.g[p.ngroups - 1].local != 0, p.out_stack ? stack : 0, row0, store_chunk)) break;
+      if (!store_box(&maps.out, p.g[p.ngroups - 1].local != 0, stack, row0, store_chunk, p.bias != nullptr)) break;
     } else if (!p.g[p.ngroups - 1].local) {
       __syncthreads();  // other warps still read this box in the last group
       if (*give_up) break;
@@ -185,6 +212,24 @@ __global__ void __launch_bounds__(256) bfly_fw2_pack_kernel(const __grid_constan
     fw2_pack_entry(p, p.g[gi], stack, (int)(w % (uint32_t)U), (int)(w / (uint32_t)U) >> 3, (int)(w / (uint32_t)U) & 7, q);
     reinterpret_cast<float4*>(p.packed)[e] = make_float4(q[0], q[1], q[2], q[3]);
   }
+}
+
+// out[b, f] += bias[f] for f < len on a (B, width) matrix with row pitch `pitch`: the bias of a
+// fused linear layer when the forward ran on a kernel without the bias epilogue.
+__global__ void __launch_bounds__(256) bfly_bias_kernel(float* __restrict__ out, const float* __restrict__ bias, int64_t B,
+                                                         int len, int64_t pitch) {
+  const int64_t total = B * len;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / len;
+    const int f = (int)(e - r * len);
+    out[r * pitch + f] += __ldg(bias + f);
+  }
+}
+int bias_add_launch(float* out, const float* bias, int64_t B, int len, int64_t pitch, int sms, cudaStream_t stream) {
+  if (B <= 0 || len <= 0) return BFLY_OK;
+  const int64_t blocks = std::min<int64_t>((B * len + 255) / 256, (int64_t)sms * 8);
+  bfly_bias_kernel<<<(int)blocks, 256, 0, stream>>>(out, bias, B, len, pitch);
+  return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
 }
 
 template <int CTAS>

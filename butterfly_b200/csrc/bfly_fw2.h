@@ -148,6 +148,10 @@ struct Fw2Params {
   const float* x; int64_t x_sB, x_sS; int x_cols;
   float* out; int64_t out_sB, out_sS;
   float* snap[kFw2MaxSnap];
+  // optional bias added to the output before it is stored: bias[stack * n + column] for flat
+  // output positions below bias_len (the output buffer is then one (B, S * n) matrix)
+  const float* bias;
+  int bias_len;
   int ngroups;
   Fw2Group g[kFw2MaxGroups];
 };

@@ -549,6 +549,12 @@ struct CudaExec {
     if (rc == BFLY_OK) g_launches.fetch_add(launches);
     return rc;
   }
+  bool can_run_bw3(const Bw3Params& p_in) {
+    Bw3Params p = p_in;
+    CUtensorMap mx, mg, mo;
+    describe_bw(p.b, kBw3Rows, mx, mg, mo);
+    return p.b.tma != 0;
+  }
   int run_bw3(const Bw3Params& p_in) {
     Bw3Params p = p_in;
     CUtensorMap mx, mg, mo;
@@ -624,6 +630,11 @@ struct CudaExec {
       if (p.nsg <= 2 && p.Rb == 16) return launch_bw<cf, 1, 5, 9, 16>(p);
     }
     return p.nsg <= 5 ? launch_bw<cf, 1, 5, 0, 0>(p) : launch_bw<cf, 1, 10, 0, 0>(p);
+  }
+  int add_bias(float* out, const float* bias, int64_t B, int len, int64_t pitch) {
+    const int rc = bias_add_launch(out, bias, B, len, pitch, dev.sms, stream);
+    if (rc == BFLY_OK) g_launches.fetch_add(1);
+    return rc;
   }
   int zero(void* ptr, size_t bytes) {
     if (bytes == 0) return BFLY_OK;
@@ -827,6 +838,40 @@ int bfly_bw_c64(const void* twiddle, const void* x, int64_t x_sB, int64_t x_sS, 
   return bw_entry<cf>(false, twiddle, nullptr, x, x_sB, x_sS, grad, g_sB, g_sS, d_twiddle, nullptr, d_x, batch,
                       nstacks, log_n, nblocks, input_size, output_size, increasing_stride, workspace,
                       workspace_bytes, stream);
+}
+int bfly_linear_fw_f32(const float* twiddle, const float* x, int64_t x_sB, float* out, const float* bias, int batch,
+                       int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  CudaExec ex;
+  int rc = make_exec(stream, ex);
+  if (rc) return rc;
+  Problem q{batch, nstacks, log_n, nblocks, input_size, 1 << log_n, increasing_stride != 0, false};
+  return drive_linear_fw(ex, q, twiddle, x, x_sB, out, bias, output_size, workspace, workspace_bytes);
+}
+int64_t bfly_linear_bw_workspace_bytes(int batch, int nstacks, int log_n, int nblocks) {
+  Problem q{batch, nstacks, log_n, nblocks, 1, 1, true, false};
+  int rc = check_problem(q);
+  if (rc) return rc;
+  int64_t best = 0;
+  for (int inc = 0; inc < 2; ++inc) {
+    q.inc = inc != 0;
+    LinearBwLayout L;
+    rc = plan_linear_bw(q, L);
+    if (rc) return rc;
+    best = std::max<int64_t>(best, (int64_t)L.ws_bytes);
+  }
+  return best;
+}
+int bfly_linear_bw_f32(const float* twiddle, const float* x, int64_t x_sB, const float* grad, int64_t g_sB, float* d_twiddle,
+                       float* d_input, int64_t d_input_sB, float* d_bias, int batch, int nstacks, int log_n, int nblocks,
+                       int input_size, int output_size, int increasing_stride, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+  CudaExec ex;
+  int rc = make_exec(stream, ex);
+  if (rc) return rc;
+  Problem q{batch, nstacks, log_n, nblocks, input_size, 1 << log_n, increasing_stride != 0, false};
+  return drive_linear_bw(ex, q, twiddle, x, x_sB, grad, g_sB, d_twiddle, d_input, d_input_sB, d_bias, output_size, workspace,
+                         workspace_bytes);
 }
 int bfly_fw_f32_saving(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, int batch,
                        int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,

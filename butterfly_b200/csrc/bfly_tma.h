@@ -151,6 +151,12 @@ __device__ __forceinline__ void tma_store_tile(const CUtensorMap* map, uint32_t 
   asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
                ::"l"(map), "r"(src), "r"(0), "r"(c1), "r"(c2), "r"(stack), "r"(row) : "memory");
 }
+// the same box added (float32) onto what global memory holds
+__device__ __forceinline__ void tma_reduce_add_tile(const CUtensorMap* map, uint32_t src, int c1, int c2, int stack,
+                                                    int row) {
+  asm volatile("cp.reduce.async.bulk.tensor.5d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+               ::"l"(map), "r"(src), "r"(0), "r"(c1), "r"(c2), "r"(stack), "r"(row) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all committed stores have finished READING shared memory (the tile may be overwritten)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

@@ -225,6 +225,12 @@ template <typename T> struct BwParams {
   // tile traffic through the TMA unit (set by the launcher when all three tensors qualify):
   // tma_s*: the tensor's descriptor has a stack dimension; tma_pbe, tma_f: see bfly_tma.h
   int tma, tma_sx, tma_sg, tma_so, tma_pbe, tma_f;
+  // fused linear layer (packed-pair kernel only): add the phase's output into gout instead of
+  // storing it (gout then has stack stride 0: the input gradient summed over the stacks), and
+  // accumulate the column sums of gin into dbias[stack * n + column] for flat positions < dbias_len
+  int gout_reduce;
+  T* dbias;
+  int dbias_len;
   Panel panel;
   int nsg;
   BwSg sg[kMaxSg];

@@ -230,6 +230,113 @@ Tensor butterfly_multiply(const Tensor& twiddle, const Tensor& input, bool incre
   return ButterflyMultiply::apply(twiddle, input, increasing_stride, output_size, wants_grad);
 }
 
+// ---------------------------------------------------------------- fused linear layer (float32)
+
+// Butterfly as a linear layer without the PyTorch glue of the reference's module
+// (torch_butterfly/butterfly.py:152-169): input (batch, in_size) shared by the stacks, output the
+// first out_size columns of the stacks' outputs side by side, bias added in the kernel.
+Tensor butterfly_linear_fw(const Tensor& twiddle, const Tensor& input, const c10::optional<Tensor>& bias,
+                           bool increasing_stride, int64_t out_size) {
+  BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_SAME_DEVICE(twiddle, input);
+  BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 2);
+  TORCH_CHECK(input.scalar_type() == at::kFloat && twiddle.scalar_type() == at::kFloat,
+              "butterfly_linear_fw: float32 only");
+  const int64_t batch = input.size(0), input_size = input.size(1);
+  const int64_t nstacks = twiddle.size(0), nblocks = twiddle.size(1), log_n = twiddle.size(2);
+  TORCH_CHECK(log_n >= 1 && log_n <= 24, "butterfly_linear_fw: n must be a power of 2 (2 <= n <= 2^24)");
+  const int64_t n = (int64_t)1 << log_n;
+  TORCH_CHECK(twiddle.sizes() == torch::IntArrayRef({nstacks, nblocks, log_n, n / 2, 2, 2}),
+              "twiddle must have shape (nstacks, nblocks, log_n, n / 2, 2, 2)");
+  TORCH_CHECK(out_size >= 0 && out_size <= nstacks * n, "butterfly_linear_fw: out_size must be <= nstacks * n");
+  const float* bp = nullptr;
+  Tensor b;
+  if (bias.has_value() && bias->defined()) {
+    BFLY_CHECK_CUDA((*bias)); BFLY_CHECK_SAME_DEVICE((*bias), input);
+    TORCH_CHECK(bias->scalar_type() == at::kFloat && bias->dim() == 1 && bias->size(0) >= out_size,
+                "bias must be a float32 vector of at least out_size entries");
+    b = bias->contiguous();
+    bp = b.data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor tw = dense_twiddle(twiddle);
+  Tensor x = input.stride(1) == 1 || input.size(1) <= 1 ? input : input.contiguous();
+  if (x.size(1) <= 1 && x.stride(1) != 1) x = x.contiguous();
+  Tensor output = torch::empty({batch, nstacks * n}, input.options());
+  const int64_t fws = bfly_fw_workspace_bytes(BFLY_F32, (int)batch, (int)nstacks, (int)log_n, (int)nblocks);
+  TORCH_CHECK(fws >= 0, "butterfly_linear_fw failed: ", bfly_strerror((int)fws));
+  Tensor ws;
+  if (fws > 0) ws = torch::empty({fws}, input.options().dtype(at::kByte));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int rc = bfly_linear_fw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), output.data_ptr<float>(), bp,
+                                    (int)batch, (int)nstacks, (int)log_n, (int)nblocks, (int)input_size, (int)out_size,
+                                    increasing_stride, fws > 0 ? ws.data_ptr() : nullptr, (size_t)fws, stream.stream());
+  check_status(rc, "butterfly_linear_fw");
+  return out_size < nstacks * n ? output.slice(1, 0, out_size) : output;
+}
+
+// (d_twiddle, d_input (batch, in_size), d_bias (out_size) or an undefined tensor)
+std::tuple<Tensor, Tensor, Tensor> butterfly_linear_bw(const Tensor& twiddle, const Tensor& input, const Tensor& grad,
+                                                        bool increasing_stride, bool need_bias) {
+  BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_CUDA(grad);
+  BFLY_CHECK_SAME_DEVICE(twiddle, input); BFLY_CHECK_SAME_DEVICE(input, grad);
+  BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 2); BFLY_CHECK_DIM(grad, 2);
+  TORCH_CHECK(input.scalar_type() == at::kFloat && twiddle.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat,
+              "butterfly_linear_bw: float32 only");
+  const int64_t batch = input.size(0), input_size = input.size(1), out_size = grad.size(1);
+  const int64_t nstacks = twiddle.size(0), nblocks = twiddle.size(1), log_n = twiddle.size(2);
+  const int64_t n = (int64_t)1 << log_n;
+  TORCH_CHECK(grad.size(0) == batch && out_size <= nstacks * n, "grad must have shape (batch_size, out_size <= nstacks * n)");
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor tw = dense_twiddle(twiddle);
+  const Tensor x = input.contiguous();
+  const Tensor g = grad.contiguous();
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (out_size == nstacks * n) {
+    const int64_t wsb = bfly_linear_bw_workspace_bytes((int)batch, (int)nstacks, (int)log_n, (int)nblocks);
+    if (wsb >= 0) {
+      Tensor d_twiddle = torch::empty_like(tw);
+      Tensor d_input = torch::empty({batch, input_size}, input.options());
+      Tensor d_bias = need_bias ? torch::empty({out_size}, input.options()) : Tensor();
+      Tensor ws = torch::empty({std::max<int64_t>(wsb, 16)}, input.options().dtype(at::kByte));
+      const int rc = bfly_linear_bw_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), g.data_ptr<float>(), g.stride(0),
+                                        d_twiddle.data_ptr<float>(), d_input.data_ptr<float>(), d_input.stride(0),
+                                        need_bias ? d_bias.data_ptr<float>() : nullptr, (int)batch, (int)nstacks, (int)log_n,
+                                        (int)nblocks, (int)input_size, (int)out_size, increasing_stride, ws.data_ptr(),
+                                        (size_t)ws.numel(), stream.stream());
+      if (rc == BFLY_OK) return std::make_tuple(d_twiddle, d_input, d_bias);
+      if (rc != BFLY_E_UNSUPPORTED) check_status(rc, "butterfly_linear_bw");
+    }
+  }
+  // unfused composition: the operator on the expanded input, then the reductions autograd would run
+  Tensor gp = g;
+  if (out_size < nstacks * n) gp = torch::constant_pad_nd(g, {0, nstacks * n - out_size});
+  auto r = bw_impl(tw, x.unsqueeze(1).expand({batch, nstacks, input_size}), gp.view({batch, nstacks, n}), increasing_stride,
+                   nullptr);
+  return std::make_tuple(std::get<0>(r), std::get<1>(r).sum(1), need_bias ? g.sum(0) : Tensor());
+}
+
+class ButterflyLinear : public torch::autograd::Function<ButterflyLinear> {
+ public:
+  static Tensor forward(AutogradContext* ctx, Tensor twiddle, Tensor input, c10::optional<Tensor> bias, bool increasing_stride,
+                        int64_t out_size) {
+    ctx->saved_data["increasing_stride"] = increasing_stride;
+    ctx->saved_data["has_bias"] = bias.has_value() && bias->defined();
+    ctx->save_for_backward({twiddle, input});
+    return butterfly_linear_fw(twiddle, input, bias, increasing_stride, out_size);
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grad_output) {
+    auto saved = ctx->get_saved_variables();
+    auto r = butterfly_linear_bw(saved[0], saved[1], grad_output[0], ctx->saved_data["increasing_stride"].toBool(),
+                                 ctx->saved_data["has_bias"].toBool());
+    return {std::get<0>(r), std::get<1>(r), std::get<2>(r), Tensor(), Tensor()};
+  }
+};
+
+Tensor butterfly_linear(const Tensor& twiddle, const Tensor& input, const c10::optional<Tensor>& bias, bool increasing_stride,
+                        int64_t out_size) {
+  return ButterflyLinear::apply(twiddle, input, bias, increasing_stride, out_size);
+}
+
 // ---------------------------------------------------------------- base-4
 
 struct Base4Shape {
@@ -359,6 +466,12 @@ TORCH_LIBRARY(torch_butterfly, m) {
         butterfly_multiply_bw);
   m.def("butterfly_multiply(Tensor twiddle, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
         butterfly_multiply);
+  m.def("butterfly_linear_fw(Tensor twiddle, Tensor input, Tensor? bias, bool increasing_stride, int out_size) -> Tensor",
+        butterfly_linear_fw);
+  m.def("butterfly_linear_bw(Tensor twiddle, Tensor input, Tensor grad, bool increasing_stride, bool need_bias) -> (Tensor, Tensor, Tensor)",
+        butterfly_linear_bw);
+  m.def("butterfly_linear(Tensor twiddle, Tensor input, Tensor? bias, bool increasing_stride, int out_size) -> Tensor",
+        butterfly_linear);
   m.def("butterfly_multiply_base4_fw(Tensor twiddle4, Tensor twiddle2, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
         butterfly_multiply_base4_fw);
   m.def("butterfly_multiply_base4_bw(Tensor twiddle4, Tensor twiddle2, Tensor input, Tensor grad, bool increasing_stride) -> (Tensor, Tensor, Tensor)",

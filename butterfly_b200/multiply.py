@@ -28,3 +28,24 @@ def butterfly_multiply(twiddle: torch.Tensor, input: torch.Tensor, increasing_st
                        output_size: Optional[int] = None) -> torch.Tensor:
     """Differentiable product of the nblocks * log_n butterfly factors with ``input``."""
     return torch.ops.torch_butterfly.butterfly_multiply(twiddle, input, increasing_stride, output_size)
+
+
+def butterfly_linear(twiddle: torch.Tensor, input: torch.Tensor, bias: Optional[torch.Tensor], increasing_stride: bool,
+                     out_size: int) -> torch.Tensor:
+    """Butterfly as a linear layer, fused (float32): ``input`` (batch, in_size) is shared by all stacks,
+    the result is the first ``out_size`` columns of the stacks' outputs side by side plus ``bias``.
+    Replaces the expand / flatten / slice / bias-add glue of the reference's module
+    (torch_butterfly/butterfly.py:152-169) and, in the backward, the reductions autograd derives
+    from it (input gradient summed over the stacks, bias gradient)."""
+    return torch.ops.torch_butterfly.butterfly_linear(twiddle, input, bias, increasing_stride, out_size)
+
+
+def butterfly_linear_fw(twiddle: torch.Tensor, input: torch.Tensor, bias: Optional[torch.Tensor], increasing_stride: bool,
+                        out_size: int) -> torch.Tensor:
+    return torch.ops.torch_butterfly.butterfly_linear_fw(twiddle, input, bias, increasing_stride, out_size)
+
+
+def butterfly_linear_bw(twiddle: torch.Tensor, input: torch.Tensor, grad: torch.Tensor, increasing_stride: bool,
+                        need_bias: bool = True) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Returns (d_twiddle, d_input (batch, in_size), d_bias (out_size))."""
+    return torch.ops.torch_butterfly.butterfly_linear_bw(twiddle, input, grad, increasing_stride, need_bias)

@@ -187,6 +187,31 @@ int bfly_bw_c64_saved(const void* twiddle, const void* x, int64_t x_sB, int64_t 
 int bfly_set_option(const char* name, int value);
 int bfly_get_option(const char* name, int* value);
 
+/* Butterfly as a linear layer, fused (float32).  Replaces the PyTorch glue around the operator in
+ * the reference's Butterfly module (torch_butterfly/butterfly.py:152-169: pre_process expands the
+ * input over the stacks, post_process flattens the stacks, slices and adds the bias) and what
+ * autograd makes of it in the backward (sum of the input gradient over the stacks, column sum of
+ * grad for the bias).
+ *   x       (batch, input_size) rows with pitch x_sB, shared by all stacks
+ *   out     (batch, nstacks * n) contiguous; the layer's output is its first output_size columns
+ *           (output_size <= nstacks * n; columns beyond it are working space)
+ *   bias    (output_size) or NULL: added in the forward kernel's store epilogue
+ * bfly_linear_bw_f32 returns d_twiddle, d_input (batch, input_size; pitch d_input_sB) already summed
+ * over the stacks (the last phase adds its tiles into it: float32 additions in no fixed order, so
+ * the last bits can differ between runs) and d_bias (output_size, or NULL).  It needs grad
+ * (batch, output_size; pitch g_sB) with output_size == nstacks * n, input_size a multiple of 32 and
+ * <= n, 16-byte aligned rows and batch >= 5; otherwise, or when a phase does not fit its kernel, it
+ * returns BFLY_E_UNSUPPORTED before writing anything and the caller composes bfly_bw_f32 with its
+ * own reductions.  Workspace: bfly_linear_bw_workspace_bytes (forward: bfly_fw_workspace_bytes). */
+int bfly_linear_fw_f32(const float* twiddle, const float* x, int64_t x_sB, float* out, const float* bias,
+                       int batch, int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                       int increasing_stride, void* workspace, size_t workspace_bytes, void* stream);
+int64_t bfly_linear_bw_workspace_bytes(int batch, int nstacks, int log_n, int nblocks);
+int bfly_linear_bw_f32(const float* twiddle, const float* x, int64_t x_sB, const float* grad, int64_t g_sB,
+                       float* d_twiddle, float* d_input, int64_t d_input_sB, float* d_bias, int batch,
+                       int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                       int increasing_stride, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Number of kernels the library has launched in this process so far (all entry points). */
 int64_t bfly_launch_count(void);
 

@@ -65,6 +65,10 @@ struct EmulExec {
         }
         if (p.g[gi].emit) box_copy(false, nullptr, p.snap[p.g[gi].emit - 1], (int64_t)p.S * n, n, n, stack, row0);
       }
+      if (p.has_out && p.bias)  // the store epilogue of the device kernel
+        for (int r = 0; r < p.R; ++r)
+          for (int c = 0; c < n; ++c)
+            if (stack * n + c < p.bias_len) tile[fw2_tile_index(p.R, r, c)] += p.bias[stack * n + c];
       if (p.has_out) box_copy(false, nullptr, p.out, p.out_sB, p.out_sS, p.out_cols, stack, row0);
     }
     return BFLY_OK;
@@ -72,11 +76,21 @@ struct EmulExec {
 
   // packed-pair backward phase: the device kernel's steps, thread by thread, accumulators in a heap array
   bool bw3 = true;
-  int run_bw3(const Bw3Params& p) {
-    if (!bw3) return kFw2Declined;
+  bool can_run_bw3(const Bw3Params& p) const {
     const BwParams<float>& q = p.b;
-    // what the TMA descriptors would refuse: widths that are not whole 32-column blocks
-    if (!q.vec_x || !q.vec_g || !q.vec_o || q.xin_cols % 32 || q.gin_cols % 32 || q.gout_cols % 32) return kFw2Declined;
+    // what the TMA descriptors would refuse: widths that are not whole 32-column blocks, and, for
+    // panels made of strided segments, rows that are not whole groups of segments
+    if (!bw3 || !q.vec_x || !q.vec_g || !q.vec_o || q.xin_cols % 32 || q.gin_cols % 32 || q.gout_cols % 32) return false;
+    if (q.panel.lseg != q.panel.logC) {
+      const int grp = 1 << q.panel.pb;
+      for (int cols : {q.xin_cols, q.gin_cols, q.gout_cols})
+        if (cols % grp != 0 && cols >= grp) return false; else if (cols < grp) return false;
+    }
+    return true;
+  }
+  int run_bw3(const Bw3Params& p) {
+    if (!can_run_bw3(p)) return kFw2Declined;
+    const BwParams<float>& q = p.b;
     ++g_bw3_calls;
     const int C = 1024, nthr = kBw3Threads;
     std::vector<float> smem((size_t)(q.nsg + 1) * kBw3Rows * C);
@@ -100,11 +114,25 @@ struct EmulExec {
           tile_load_auto<float>(q.xin, q.xin_sB, q.xin_sS, q.xin_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smX, tid, nthr);
           tile_load_auto<float>(q.gin, q.gin_sB, q.gin_sS, q.gin_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smG, tid, nthr);
         }
+        if (q.dbias)  // column sums of the gradient tile as it arrived
+          for (int r = 0; r < kBw3Rows; ++r)
+            for (int l = 0; l < C; ++l) {
+              const int flat = stack * (1 << q.log_n) + q.panel.col(pbase, l);
+              if (flat < q.dbias_len) q.dbias[flat] += smG[r * C + swz<2>(l)];
+            }
         for (int step = 0; step < bw3_num_steps(q.nsg); ++step)
           for (int tid = 0; tid < nthr; ++tid)
             bw3_step(p, accs[tid], meta.data(), step, smem.data(), tid, pf.data() + (size_t)tid * 64, pf.data() + (size_t)tid * 64 + 32);
-        for (int tid = 0; tid < nthr; ++tid)
-          tile_store_auto<float>(q.gout, q.gout_sB, q.gout_sS, q.gout_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smG, tid, nthr);
+        if (q.gout_reduce) {  // the device kernel's reduce-add store
+          for (int r = 0; r < kBw3Rows && row0 + r < q.B; ++r)
+            for (int l = 0; l < C; ++l) {
+              const int col = q.panel.col(pbase, l);
+              if (col < q.gout_cols) q.gout[(int64_t)(row0 + r) * q.gout_sB + (int64_t)stack * q.gout_sS + col] += smG[r * C + swz<2>(l)];
+            }
+        } else {
+          for (int tid = 0; tid < nthr; ++tid)
+            tile_store_auto<float>(q.gout, q.gout_sB, q.gout_sS, q.gout_cols, q.B, stack, row0, kBw3Rows, q.panel, pbase, true, smG, tid, nthr);
+        }
       }
       for (int tid = 0; tid < nthr; ++tid) bw3_flush(p, accs[tid], stack, pbase, tid);
     }
@@ -211,6 +239,11 @@ struct EmulExec {
   }
   template <typename T> int run_bw(const BwParams<T>& p, int KW) {
     return KW == 2 ? run_bw_kw<T, 2>(p) : run_bw_kw<T, 1>(p);
+  }
+  int add_bias(float* out, const float* bias, int64_t B, int len, int64_t pitch) {
+    for (int64_t b = 0; b < B; ++b)
+      for (int f = 0; f < len; ++f) out[b * pitch + f] += bias[f];
+    return BFLY_OK;
   }
   int zero(void* ptr, size_t bytes) { std::memset(ptr, 0, bytes); return BFLY_OK; }
   int zero2d(void* ptr, size_t pitch, size_t width, size_t rows) {
@@ -347,6 +380,31 @@ int bfly_emul_fw_bw_saved(int dtype, const void* tw, const void* x, int64_t x_sB
   Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, false};
   return dtype == 0 ? emul_fw_bw_saved<float>(tw, x, x_sB, x_sS, out, g, g_sB, g_sS, d_tw, dx, q, threads, sms)
                     : emul_fw_bw_saved<cf>(tw, x, x_sB, x_sS, out, g, g_sB, g_sS, d_tw, dx, q, threads, sms);
+}
+// fused linear layer: forward into out (B, S * n), backward with d_input summed over the stacks and d_bias
+int bfly_emul_linear_fw(const void* tw, const void* x, int64_t x_sB, void* out, const void* bias, int B, int S, int log_n,
+                        int nblocks, int in_size, int out_total, int inc) {
+  EmulExec ex; ex.threads_ = 256;
+  Problem q{B, S, log_n, nblocks, in_size, 1 << log_n, inc != 0, false};
+  std::vector<char> ws(fw_workspace_bytes<float>(q) + 256);
+  void* wsp = (void*)(((uintptr_t)ws.data() + 255) / 256 * 256);
+  return drive_linear_fw(ex, q, (const float*)tw, (const float*)x, x_sB, (float*)out, (const float*)bias, out_total, wsp,
+                         fw_workspace_bytes<float>(q));
+}
+int bfly_emul_linear_bw(const void* tw, const void* x, int64_t x_sB, const void* g, int64_t g_sB, void* d_tw, void* d_in,
+                        int64_t din_sB, void* d_bias, int B, int S, int log_n, int nblocks, int in_size, int out_total, int inc,
+                        int sms) {
+  EmulExec ex; ex.threads_ = 256; ex.sms = sms;
+  Problem q{B, S, log_n, nblocks, in_size, 1 << log_n, inc != 0, false};
+  LinearBwLayout L;
+  int rc = check_problem(q);
+  if (rc) return rc;
+  rc = plan_linear_bw(q, L);
+  if (rc) return rc;
+  std::vector<char> ws(L.ws_bytes + 256);
+  void* wsp = (void*)(((uintptr_t)ws.data() + 255) / 256 * 256);
+  return drive_linear_bw(ex, q, (const float*)tw, (const float*)x, x_sB, (const float*)g, g_sB, (float*)d_tw, (float*)d_in,
+                         din_sB, (float*)d_bias, out_total, wsp, L.ws_bytes);
 }
 // number of backward phases and workspace bytes the planner chooses (for tests of the planner)
 int bfly_emul_bw_plan(int dtype, int base4, int B, int S, int log_n, int nblocks, int inc, int64_t* ws_bytes) {

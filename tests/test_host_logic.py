@@ -299,3 +299,46 @@ def test_packed_pair_backward_path(emul, oracle_mod, log_n):
             assert torch.equal(dx, dxs)
             assert rel_err(d2, d2s) < 1e-5
             assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
+
+
+@pytest.mark.parametrize("log_n,S", [(10, 4), (11, 2), (12, 1)])
+def test_fused_linear_layer(emul, oracle_mod, log_n, S):
+    """Butterfly as a linear layer, fused: the forward adds the bias in its store epilogue, the backward
+    sums the input gradient over the stacks in its last store and collects the bias gradient from
+    the gradient tiles -- against the oracle composed with the reference's PyTorch glue
+    (torch_butterfly/butterfly.py:152-169: expand, flatten, slice, add bias)."""
+    torch.manual_seed(900 + log_n)
+    n = 1 << log_n
+    for nb, inc in [(1, True), (2, True), (2, False)]:
+        for B, in_size in [(5, n), (23, n - 64)]:
+            out_total = S * n
+            tw = torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
+            x = torch.randn(B, in_size)
+            bias = torch.randn(out_total)
+            g = torch.randn(B, out_total)
+            # the unfused composition on the oracle
+            xe = x.unsqueeze(1).expand(B, S, in_size)
+            yr = oracle_mod.multiply_fw(tw, xe, inc).reshape(B, S * n) + bias
+            dtr, dxr = oracle_mod.multiply_bw(tw, xe, g.reshape(B, S, n), inc)
+            dxr, dbr = dxr.sum(1), g.sum(0)
+            out = torch.full((B, S * n), float("nan"))
+            rc = emul.bfly_emul_linear_fw(P(tw), P(x), I64(x.stride(0)), P(out), P(bias), B, S, log_n, nb, in_size, out_total, int(inc))
+            assert rc == 0
+            assert rel_err(out, yr) < 2e-5
+            d_tw = torch.full_like(tw, float("nan")); d_in = torch.full((B, in_size), float("nan")); d_b = torch.full((out_total,), float("nan"))
+            rc = emul.bfly_emul_linear_bw(P(tw), P(x), I64(x.stride(0)), P(g), I64(g.stride(0)), P(d_tw), P(d_in), I64(d_in.stride(0)),
+                                          P(d_b), B, S, log_n, nb, in_size, out_total, int(inc), 7)
+            if rc == -2:
+                # a phase on strided column segments takes only rows that are whole groups of segments
+                # (what the TMA descriptors can express): refused before anything is written
+                assert in_size != n and torch.isnan(d_in).all() and torch.isnan(d_tw).all()
+                continue
+            assert rc == 0
+            assert rel_err(d_tw, dtr) < 2e-5 and rel_err(d_in, dxr) < 2e-5 and rel_err(d_b, dbr) < 2e-5
+    # a ragged input width is refused before anything is written
+    x = torch.randn(8, n - 3); g = torch.randn(8, S * n); d_in = torch.full((8, n - 3), 7.0)
+    tw = torch.randn(S, 1, log_n, n // 2, 2, 2)
+    d_tw = torch.full_like(tw, 7.0)
+    rc = emul.bfly_emul_linear_bw(P(tw), P(x), I64(x.stride(0)), P(g), I64(g.stride(0)), P(d_tw), P(d_in), I64(d_in.stride(0)),
+                                  P(None), 8, S, log_n, 1, n - 3, S * n, 1, 7)
+    assert rc == -2 and (d_in == 7.0).all() and (d_tw == 7.0).all()
