@@ -295,6 +295,41 @@ def measure_config(bb, configs, name, dev, peak, make=None, iters=5, warm=3, ref
     return out
 
 
+def measure_linear_layer(bb, configs, dev, peak, rank=0, iters=5, warm=3):
+    """Configuration 5 as what it is in a model -- a 1024 -> 4096 linear layer with bias: the fused
+    operators (bias in the forward's store, input gradient summed over the stacks and bias
+    gradient inside the backward kernels) beside the same layer through the multiply operators
+    plus PyTorch glue (expand, flatten, bias add; sum over stacks, column sum of grad)."""
+    import torch
+    d = configs.make_inputs("cfg5", rank=rank, device=dev)
+    tw, inc, S, n = d["twiddle"], d["increasing_stride"], 4, d["n"]
+    B = d["batch"]
+    x2 = d["input"][:, 0].contiguous()          # (B, 1024)
+    g2 = d["grad"].reshape(B, S * n)            # (B, 4096)
+    bias = torch.randn(S * n, device=dev)
+    twb = tw.numel() * 4
+    fwb = 4 * (B * n + B * S * n + S * n) + twb
+    bwb = 4 * (B * n + B * S * n + B * n + S * n) + 2 * twb
+    fused_fw = lambda: bb.butterfly_linear_fw(tw, x2, bias, inc, S * n)
+    fused_bw = lambda: bb.butterfly_linear_bw(tw, x2, g2, inc, True)
+
+    def glue_fw():
+        rows = x2.unsqueeze(1).expand(B, S, n)
+        return bb.butterfly_multiply_fw(tw, rows, inc).reshape(B, S * n) + bias
+
+    def glue_bw():
+        rows = x2.unsqueeze(1).expand(B, S, n)
+        d_tw, d_x = bb.butterfly_multiply_bw(tw, rows, g2.view(B, S, n), inc)
+        return d_tw, d_x.sum(1), g2.sum(0)
+    out = {"name": "cfg5 as a linear layer with bias (1024 -> 4096)", "n": n, "batch": B, "nstacks": S, "dtype": "f32",
+           "fw_ms": _events_ms(fused_fw, iters, warm), "bw_ms": _events_ms(fused_bw, iters, warm),
+           "unfused_fw_ms": _events_ms(glue_fw, iters, warm), "unfused_bw_ms": _events_ms(glue_bw, iters, warm),
+           "fw_algorithmic_bytes": fwb, "bw_algorithmic_bytes": bwb}
+    out["fw_bw_gbs"] = (fwb + bwb) / (out["fw_ms"] + out["bw_ms"]) / 1e6
+    out["fw_bw_frac_of_hbm_peak"] = out["fw_bw_gbs"] / peak
+    return out
+
+
 def two_block_inputs(log_n, dev, elements=1 << 26):
     """Real fp32 two-block product (increasing then decreasing stride) over `elements` elements."""
     import math
@@ -460,6 +495,7 @@ def run_gpu_arm(args):
         for log_n in (10, 11, 13):
             other.append(measure_config(bb, configs, "two-block n=%d" % (1 << log_n), dev, peak,
                                         make=lambda: two_block_inputs(log_n, dev), ref_ops=ref_ops if log_n <= 11 else None))
+        other.append(measure_linear_layer(bb, configs, dev, peak))
         if ref_ops is not None:
             ref_cuda_note = {"kind": "reference", "library": "oracle/_ref/_butterfly_ref_cuda.so",
                              "what": "csrc/cuda/butterfly_cuda.cu of the reference compiled unmodified for sm_100; "
@@ -467,7 +503,8 @@ def run_gpu_arm(args):
     elif rank == 0 and world > 1 and not args.no_other:
         # the multi-GPU configuration: this rank's shard of cfg5 (8192 rows, stack-broadcast input)
         other = [measure_config(bb, configs, "cfg5", dev, peak,
-                                make=lambda: configs.make_inputs("cfg5", rank=rank, device=dev))]
+                                make=lambda: configs.make_inputs("cfg5", rank=rank, device=dev)),
+                 measure_linear_layer(bb, configs, dev, peak, rank=rank)]
 
     # ---- end to end through the public operator with host buffers
     e2e = None
