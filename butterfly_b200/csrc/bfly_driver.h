@@ -145,9 +145,16 @@ struct Problem {
   bool inc, base4;
 };
 
+inline void twiddle_stack_sizes(const Problem& q, int64_t out[2]);
 inline int check_problem(const Problem& q) {
   if (q.B < 0 || q.S < 1 || q.log_n < 1 || q.log_n > 24 || q.nblocks < 1) return BFLY_E_ARG;
   if (q.in_size < 0 || q.out_size < 0 || q.out_size > (1 << q.log_n)) return BFLY_E_ARG;
+  // The kernels address a stage's twiddles with 32-bit element offsets inside one stack (and the
+  // re-ordered copy of the packed-pair forward, twice as many floats, the same way): a stack of
+  // 2^31 twiddle elements or more (8 GB of float32 per stack) is refused rather than wrapped.
+  int64_t per_stack[2];
+  twiddle_stack_sizes(q, per_stack);
+  if (per_stack[0] >= ((int64_t)1 << 31) || per_stack[1] >= ((int64_t)1 << 31)) return BFLY_E_UNSUPPORTED;
   return BFLY_OK;
 }
 

@@ -409,7 +409,8 @@ int bfly_emul_linear_bw(const void* tw, const void* x, int64_t x_sB, const void*
 // number of backward phases and workspace bytes the planner chooses (for tests of the planner)
 int bfly_emul_bw_plan(int dtype, int base4, int B, int S, int log_n, int nblocks, int inc, int64_t* ws_bytes) {
   Problem q{B, S, log_n, nblocks, 1 << log_n, 1 << log_n, inc != 0, base4 != 0};
-  int rc;
+  int rc = check_problem(q);
+  if (rc) return rc;
   size_t ws = 0; int nph = 0;
   if (dtype == 0) { BwLayout<float> l; rc = plan_bw<float>(q, l); ws = l.ws_bytes; nph = (int)l.phases.size(); }
   else { BwLayout<cf> l; rc = plan_bw<cf>(q, l); ws = l.ws_bytes; nph = (int)l.phases.size(); }

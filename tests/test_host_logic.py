@@ -218,6 +218,21 @@ def test_backward_phase_plan_sizes(emul):
     assert nph == 2 and ws.value == 8192 * 2048 * 8
 
 
+def test_twiddle_stacks_beyond_32bit_offsets_are_refused(emul):
+    """The kernels address twiddles with 32-bit element offsets inside a stack: the planner and
+    the library's size queries refuse a stack of 2^31 elements or more instead of wrapping."""
+    from butterfly_b200 import abi
+    ws = ctypes.c_int64(0)
+    # n = 2^20: a stack holds nblocks * 20 * 2^21 elements -- 51 blocks fit under 2^31, 52 do not
+    assert emul.bfly_emul_bw_plan(0, 0, 4, 1, 20, 51, 1, ctypes.byref(ws)) > 0
+    assert emul.bfly_emul_bw_plan(0, 0, 4, 1, 20, 52, 1, ctypes.byref(ws)) == -2
+    assert emul.bfly_emul_bw_plan(1, 0, 4, 1, 24, 6, 1, ctypes.byref(ws)) == -2
+    assert abi.bw_workspace_bytes(torch.float32, 4, 1, 20, 51) > 0
+    assert abi.bw_workspace_bytes(torch.float32, 4, 1, 20, 52) == -2
+    assert abi.fw_workspace_bytes(torch.float32, 4, 1, 20, 52) == -2
+    assert abi.bw_workspace_bytes(torch.float32, 4, 1, 24, 3, base4=True) == -2  # 3 * 12 * 2^22 * 16 elements
+
+
 @pytest.mark.parametrize("path", golden_files("radix2")[::4], ids=lambda p: p.split("/")[-1])
 def test_emulated_kernels_on_golden(emul, path):
     d = load_golden(path)

@@ -396,6 +396,41 @@ def test_operator_semantics(dev, oracle_mod):
         assert torch.equal(y_all[:, s:s + 1], y_one)
 
 
+def test_forward_without_grad_mode_saves_nothing(dev):
+    """A forward under torch.no_grad() on parameters that require grad is the plain forward: the
+    same launches and no snapshot planes, where the recording forward of a two-block product
+    keeps (batch, nstacks, n) planes for the backward.  The two give the same bits."""
+    import butterfly_b200 as bb
+    from butterfly_b200 import abi
+    torch.manual_seed(11)
+    B, S, nb, log_n = 4096, 1, 2, 12
+    n = 1 << log_n
+    tw = (torch.randn(S, nb, log_n, n // 2, 2, 2, device=dev) / 2 ** 0.5).requires_grad_(True)
+    x = torch.randn(B, S, n, device=dev)
+    plane = B * S * n * 4
+
+    def run(fn):
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        before, launches = torch.cuda.memory_allocated(), abi.launch_count()
+        y = fn()
+        torch.cuda.synchronize()
+        return y, abi.launch_count() - launches, torch.cuda.max_memory_allocated() - before
+
+    with abi_option("autograd_save", 1):
+        plain = lambda: bb.butterfly_multiply_fw(tw.detach(), x, True)
+        run(plain)  # first call: lazy initialisation out of the way
+        y0, l0, m0 = run(plain)
+        with torch.no_grad():
+            y1, l1, m1 = run(lambda: bb.butterfly_multiply(tw, x, True))
+        y2, l2, m2 = run(lambda: bb.butterfly_multiply(tw, x, True))
+    assert torch.equal(y0, y1) and torch.equal(y0, y2)
+    assert not y1.requires_grad and y2.requires_grad
+    assert l1 == l0 and m1 == m0, (l0, l1, m0, m1)
+    assert m0 < 2 * plane            # the output and the re-ordered twiddles
+    assert m2 >= m0 + 2 * plane - 4096  # the recording forward also holds two snapshot planes
+
+
 # ------------------------------------------------------------------ the benchmark configurations at full size
 
 def _run_cfg(name, dev, batch=None):
