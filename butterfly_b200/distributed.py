@@ -62,11 +62,18 @@ class AsyncTwiddleReducer:
         self.device = torch.device(device)
         self.group = group
         self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
-        self.stream = torch.cuda.Stream(self.device) if self.active else None
+        # CUDA: a side stream.  CPU tensors (gloo): the collective's own asynchronous handle.
+        self.stream = torch.cuda.Stream(self.device) if self.active and self.device.type == "cuda" else None
         self.pending = []
+        self.handles = []
 
     def submit(self, d_twiddle: torch.Tensor) -> torch.Tensor:
         if not self.active:
+            return d_twiddle
+        if self.stream is None:
+            flat = torch.view_as_real(d_twiddle) if d_twiddle.is_complex() else d_twiddle
+            self.handles.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            self.pending.append(d_twiddle)
             return d_twiddle
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream(self.device))
@@ -78,7 +85,10 @@ class AsyncTwiddleReducer:
         return d_twiddle
 
     def wait(self):
-        if self.active:
+        if self.active and self.stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        for h in self.handles:
+            h.wait()
+        self.handles = []
         done, self.pending = self.pending, []
         return done

@@ -41,6 +41,14 @@ def _worker(rank, world, port, out_dir):
         # same terms summed in a different order: equal up to float rounding of the sums
         assert (d_tw - d_tw_full).abs().max() <= 2e-6 * d_tw_full.abs().max()
         assert torch.equal(d_x_local, d_x_full[rows])   # no cross-rank term in the input gradient
+        # the same sum through the reducer that runs off the critical path (submit now, wait later)
+        red = bd.AsyncTwiddleReducer("cpu")
+        assert red.active
+        mine = red.submit(d_tw_local.clone())
+        other = red.submit(torch.full((3,), float(rank + 1)))
+        done = red.wait()
+        assert len(done) == 2 and red.wait() == []
+        assert torch.equal(mine, d_tw) and torch.equal(other, torch.full((3,), float(sum(range(1, world + 1)))))
     # the autograd hook: gradient of a replicated parameter is summed over ranks
     p = torch.ones(4, requires_grad=True)
     loss = (bd.sync_twiddle_grad(p) * (rank + 1)).sum()
