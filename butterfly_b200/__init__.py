@@ -36,18 +36,20 @@ _load_native()
 
 from .multiply import (  # noqa: E402,F401
     butterfly_multiply, butterfly_multiply_fw, butterfly_multiply_bw, butterfly_linear, butterfly_linear_fw, butterfly_linear_bw,
+    unitary_twiddle, unitary_twiddle_fw, unitary_twiddle_bw,
 )
 from .multiply_base4 import (  # noqa: E402,F401
     butterfly_multiply_base4, butterfly_multiply_base4_fw, butterfly_multiply_base4_bw, twiddle_base2_to_base4,
 )
 from . import abi  # noqa: E402,F401
 from .butterfly import Butterfly, ButterflyUnitary, ButterflyBmm, ButterflyBase4  # noqa: E402,F401
-from . import permutation, special, host, distributed  # noqa: E402,F401
+from . import permutation, special, host, distributed, combine, kops  # noqa: E402,F401
 
 __all__ = [
     "butterfly_multiply", "butterfly_multiply_fw", "butterfly_multiply_bw",
     "butterfly_linear", "butterfly_linear_fw", "butterfly_linear_bw",
+    "unitary_twiddle", "unitary_twiddle_fw", "unitary_twiddle_bw",
     "butterfly_multiply_base4", "butterfly_multiply_base4_fw", "butterfly_multiply_base4_bw",
     "twiddle_base2_to_base4", "abi", "__version__", "Butterfly", "ButterflyUnitary", "ButterflyBmm", "ButterflyBase4",
-    "permutation", "special",
+    "permutation", "special", "combine", "kops",
 ]

@@ -21,6 +21,7 @@ SYMBOLS = (
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
     "bfly_linear_fw_f32", "bfly_linear_bw_f32", "bfly_linear_bw_workspace_bytes", "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
+    "bfly_unitary_twiddle_fw", "bfly_unitary_twiddle_bw",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -254,6 +255,26 @@ def linear_bw(twiddle, x2d, grad2d, increasing_stride=True, with_bias=True, chec
     if check and rc != 0:
         raise BflyError(rc, "bfly_linear_bw_f32")
     return d_tw, d_in, d_b, rc
+
+
+def unitary_twiddle_fw(angles, check=True):
+    """``bfly_unitary_twiddle_fw``: (..., 4) float32 angles -> (..., 2, 2) complex64 blocks."""
+    a = angles.contiguous()
+    tw = torch.empty(a.shape[:-1] + (2, 2), dtype=torch.complex64, device=a.device)
+    rc = lib().bfly_unitary_twiddle_fw(_p(a), _p(tw), _i64(a.numel() // 4), _stream())
+    if check and rc:
+        raise BflyError(rc, "bfly_unitary_twiddle_fw")
+    return tw, rc
+
+
+def unitary_twiddle_bw(angles, d_twiddle, check=True):
+    """``bfly_unitary_twiddle_bw``: gradient of the angles from the gradient of the blocks."""
+    a, g = angles.contiguous(), d_twiddle.contiguous()
+    d = torch.empty_like(a)
+    rc = lib().bfly_unitary_twiddle_bw(_p(a), _p(g), _p(d), _i64(a.numel() // 4), _stream())
+    if check and rc:
+        raise BflyError(rc, "bfly_unitary_twiddle_bw")
+    return d, rc
 
 
 def fw_base4(twiddle4, twiddle2, x, increasing_stride=True, output_size=None, out=None, check=True):

@@ -11,7 +11,7 @@ import numbers
 import torch
 from torch import nn
 
-from .multiply import butterfly_linear, butterfly_multiply
+from .multiply import butterfly_linear, butterfly_multiply, unitary_twiddle
 from .multiply_base4 import butterfly_multiply_base4, twiddle_base2_to_base4
 
 _COMPLEX = {torch.float32: torch.complex64, torch.float64: torch.complex128}
@@ -213,6 +213,8 @@ class ButterflyUnitary(Butterfly):
             nn.init.uniform_(self.bias, -bound, bound)
 
     def _effective_twiddle(self):
+        if self.twiddle.is_cuda and self.twiddle.dtype == torch.float32:
+            return unitary_twiddle(self.twiddle)  # one kernel each way
         phi, alpha, psi, chi = torch.unbind(self.twiddle, -1)
         c, s = torch.cos(phi), torch.sin(phi)
 

@@ -390,6 +390,7 @@ bfly_bw2_kernel(const __grid_constant__ BwParams<T> p, const __grid_constant__ C
 // ------------------------------------------------------------------ launch side
 
 static std::atomic<int64_t> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add(n); }
 
 // Optional per-launch timing (bfly_profile_*): while enabled, every kernel launch is
 // bracketed by a pair of CUDA events on the launching stream.

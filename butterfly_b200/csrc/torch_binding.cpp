@@ -451,6 +451,53 @@ Tensor butterfly_multiply_base4(const Tensor& twiddle4, const Tensor& twiddle2, 
   return ButterflyMultiplyBase4::apply(twiddle4, twiddle2, input, increasing_stride, output_size);
 }
 
+// ---------------------------------------------------------------- unitary twiddle synthesis
+//
+// (..., 4) float32 angles -> (..., 2, 2) complex64 blocks and back, one kernel each, in place of
+// the cos / sin / stack chain of the reference's ButterflyUnitary.forward
+// (torch_butterfly/butterfly.py:271-280) and autograd's backward of that chain.
+Tensor unitary_twiddle_fw(const Tensor& angles) {
+  BFLY_CHECK_CUDA(angles);
+  TORCH_CHECK(angles.scalar_type() == at::kFloat && angles.dim() >= 1 && angles.size(-1) == 4,
+              "unitary_twiddle: angles must be float32 with last dimension 4 (phi, alpha, psi, chi)");
+  c10::cuda::CUDAGuard guard(angles.device());
+  const Tensor a = angles.contiguous();
+  auto shape = a.sizes().vec();
+  shape.back() = 2;
+  shape.push_back(2);
+  Tensor tw = torch::empty(shape, a.options().dtype(at::kComplexFloat));
+  check_status(bfly_unitary_twiddle_fw(a.data_ptr<float>(), tw.data_ptr(), a.numel() / 4, at::cuda::getCurrentCUDAStream().stream()),
+               "unitary_twiddle");
+  return tw;
+}
+
+Tensor unitary_twiddle_bw(const Tensor& angles, const Tensor& grad) {
+  BFLY_CHECK_CUDA(angles); BFLY_CHECK_CUDA(grad); BFLY_CHECK_SAME_DEVICE(angles, grad);
+  TORCH_CHECK(angles.scalar_type() == at::kFloat && grad.scalar_type() == at::kComplexFloat &&
+                  grad.numel() == angles.numel() && angles.dim() >= 1 && angles.size(-1) == 4,
+              "unitary_twiddle_bw: angles (..., 4) float32 and grad (..., 2, 2) complex64 expected");
+  c10::cuda::CUDAGuard guard(angles.device());
+  const Tensor a = angles.contiguous(), g = grad.resolve_conj().contiguous();
+  Tensor d = torch::empty_like(a);
+  check_status(bfly_unitary_twiddle_bw(a.data_ptr<float>(), g.data_ptr(), d.data_ptr<float>(), a.numel() / 4,
+                                       at::cuda::getCurrentCUDAStream().stream()),
+               "unitary_twiddle_bw");
+  return d;
+}
+
+class UnitaryTwiddle : public torch::autograd::Function<UnitaryTwiddle> {
+ public:
+  static Tensor forward(AutogradContext* ctx, Tensor angles) {
+    ctx->save_for_backward({angles});
+    return unitary_twiddle_fw(angles);
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grad_output) {
+    return {unitary_twiddle_bw(ctx->get_saved_variables()[0], grad_output[0])};
+  }
+};
+
+Tensor unitary_twiddle(const Tensor& angles) { return UnitaryTwiddle::apply(angles); }
+
 // The reference's import-time check (torch_butterfly/__init__.py:13-31) compares this
 // with torch.version.cuda, so report the CUDA runtime torch itself runs on.
 int64_t cuda_version() { return at::detail::getCUDAHooks().versionCUDART(); }
@@ -472,6 +519,9 @@ TORCH_LIBRARY(torch_butterfly, m) {
         butterfly_linear_bw);
   m.def("butterfly_linear(Tensor twiddle, Tensor input, Tensor? bias, bool increasing_stride, int out_size) -> Tensor",
         butterfly_linear);
+  m.def("unitary_twiddle_fw(Tensor angles) -> Tensor", unitary_twiddle_fw);
+  m.def("unitary_twiddle_bw(Tensor angles, Tensor grad) -> Tensor", unitary_twiddle_bw);
+  m.def("unitary_twiddle(Tensor angles) -> Tensor", unitary_twiddle);
   m.def("butterfly_multiply_base4_fw(Tensor twiddle4, Tensor twiddle2, Tensor input, bool increasing_stride, int? output_size=None) -> Tensor",
         butterfly_multiply_base4_fw);
   m.def("butterfly_multiply_base4_bw(Tensor twiddle4, Tensor twiddle2, Tensor input, Tensor grad, bool increasing_stride) -> (Tensor, Tensor, Tensor)",

@@ -49,3 +49,20 @@ def butterfly_linear_bw(twiddle: torch.Tensor, input: torch.Tensor, grad: torch.
                         need_bias: bool = True) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Returns (d_twiddle, d_input (batch, in_size), d_bias (out_size))."""
     return torch.ops.torch_butterfly.butterfly_linear_bw(twiddle, input, grad, increasing_stride, need_bias)
+
+
+def unitary_twiddle(angles: torch.Tensor) -> torch.Tensor:
+    """(..., 4) float32 angles (phi, alpha, psi, chi) -> (..., 2, 2) complex64 unitary blocks
+    [[cos(phi) e^{i(alpha+psi)}, sin(phi) e^{i(alpha+chi)}], [-sin(phi) e^{i(alpha-chi)}, cos(phi) e^{i(alpha-psi)}]],
+    differentiable; one kernel each way in place of the cos / sin / stack chain of the reference's
+    ButterflyUnitary.forward (torch_butterfly/butterfly.py:271-280)."""
+    return torch.ops.torch_butterfly.unitary_twiddle(angles)
+
+
+def unitary_twiddle_fw(angles: torch.Tensor) -> torch.Tensor:
+    return torch.ops.torch_butterfly.unitary_twiddle_fw(angles)
+
+
+def unitary_twiddle_bw(angles: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+    """Gradient of the angles for the gradient ``grad`` (..., 2, 2) of the blocks."""
+    return torch.ops.torch_butterfly.unitary_twiddle_bw(angles, grad)

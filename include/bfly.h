@@ -212,6 +212,18 @@ int bfly_linear_bw_f32(const float* twiddle, const float* x, int64_t x_sB, const
                        int nstacks, int log_n, int nblocks, int input_size, int output_size,
                        int increasing_stride, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Twiddles of a unitary butterfly from their angles, and the gradient of the angles.  Replaces the
+ * chain of cos / sin / stack operators (and autograd's backward of it) that the reference's
+ * ButterflyUnitary.forward runs on every call (torch_butterfly/butterfly.py:271-280).
+ *   angles     (blocks, 4) float32: phi, alpha, psi, chi of each 2x2 block
+ *   twiddle    (blocks, 2, 2) complex64 = [[cos(phi) e^{i(alpha+psi)},  sin(phi) e^{i(alpha+chi)}],
+ *                                          [-sin(phi) e^{i(alpha-chi)}, cos(phi) e^{i(alpha-psi)}]]
+ *   d_twiddle  gradient of the entries (dL/dRe + i dL/dIm), d_angles (blocks, 4) float32
+ * `blocks` = nstacks * nblocks * log_n * n/2.  All pointers 16-byte aligned, tensors contiguous. */
+int bfly_unitary_twiddle_fw(const float* angles, void* twiddle, int64_t blocks, void* stream);
+int bfly_unitary_twiddle_bw(const float* angles, const void* d_twiddle, float* d_angles, int64_t blocks,
+                            void* stream);
+
 /* Number of kernels the library has launched in this process so far (all entry points). */
 int64_t bfly_launch_count(void);
 

@@ -86,6 +86,17 @@ def assert_sum_accuracy(ours, ref32, ref64, what=""):
         what, int(bad.sum()), (err - allowed).max().item(), scale)
 
 
+def unitary_chain(angles):
+    """The reference's construction (torch_butterfly/butterfly.py:271-280) in plain torch."""
+    phi, alpha, psi, chi = torch.unbind(angles, -1)
+    c, s = torch.cos(phi), torch.sin(phi)
+    A = torch.stack((c * torch.cos(alpha + psi), c * torch.sin(alpha + psi)), dim=-1)
+    B = torch.stack((s * torch.cos(alpha + chi), s * torch.sin(alpha + chi)), dim=-1)
+    C = torch.stack((-s * torch.cos(alpha - chi), -s * torch.sin(alpha - chi)), dim=-1)
+    D = torch.stack((c * torch.cos(alpha - psi), c * torch.sin(alpha - psi)), dim=-1)
+    return torch.view_as_complex(torch.stack([torch.stack([A, B], dim=-2), torch.stack([C, D], dim=-2)], dim=-3))
+
+
 @pytest.fixture(scope="session")
 def oracle_mod():
     import oracle

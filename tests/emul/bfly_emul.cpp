@@ -12,6 +12,7 @@
 #include "bfly_bw2.h"
 #include "bfly_bw3.h"
 #include "bfly_driver.h"
+#include "bfly_glue.h"
 
 using namespace bfly;
 
@@ -352,6 +353,13 @@ static int max_conflicts(const Problem& q, int kmax) {
 }
 
 extern "C" {
+// the per-block arithmetic of the unitary twiddle kernels (bfly_glue.h), looped on the host
+void bfly_emul_unitary_fw(const float* angles, float* tw, int64_t blocks) {
+  for (int64_t i = 0; i < blocks; ++i) unitary_block_fw(angles + 4 * i, tw + 8 * i);
+}
+void bfly_emul_unitary_bw(const float* angles, const float* g, float* d, int64_t blocks) {
+  for (int64_t i = 0; i < blocks; ++i) unitary_block_bw(angles + 4 * i, g + 8 * i, d + 4 * i);
+}
 long bfly_emul_fw2_calls(void) { return g_fw2_calls; }
 long bfly_emul_bw3_calls(void) { return g_bw3_calls; }
 // the library's development switches (bfly_driver.h) for this emulator instance

@@ -4,13 +4,14 @@ that plans the GPU launches, compared with the oracle.  This checks panels, unit
 decomposition, twiddle addressing, padding/slicing and the phase plan of the backward; it
 is a test of index arithmetic, not a CPU implementation of the product."""
 import ctypes
+import math
 import os
 import subprocess
 
 import pytest
 import torch
 
-from conftest import ROOT, golden_files, load_golden, rel_err
+from conftest import ROOT, assert_rtol_atol, golden_files, load_golden, rel_err, unitary_chain
 
 EMUL_SRC = os.path.join(ROOT, "tests", "emul", "bfly_emul.cpp")
 EMUL_LIB = os.path.join(ROOT, "tests", "emul", "libbfly_emul.so")
@@ -357,3 +358,25 @@ def test_fused_linear_layer(emul, oracle_mod, log_n, S):
     rc = emul.bfly_emul_linear_bw(P(tw), P(x), I64(x.stride(0)), P(g), I64(g.stride(0)), P(d_tw), P(d_in), I64(d_in.stride(0)),
                                   P(None), 8, S, log_n, 1, n - 3, S * n, 1, 7)
     assert rc == -2 and (d_in == 7.0).all() and (d_tw == 7.0).all()
+
+
+def test_unitary_twiddle_arithmetic(emul):
+    """The per-block arithmetic of the unitary twiddle kernels against the reference's chain of
+    torch operators and autograd's backward of it."""
+    torch.manual_seed(2)
+    shape = (2, 2, 5, 16)
+    angles = torch.cat([torch.asin(torch.sqrt(torch.rand(shape + (1,)))), torch.rand(shape + (3,)) * 2 * math.pi], dim=-1)
+    blocks = angles.numel() // 4
+    tw = torch.empty(shape + (2, 2), dtype=torch.complex64)
+    emul.bfly_emul_unitary_fw(P(angles), P(tw), I64(blocks))
+    a = angles.clone().requires_grad_(True)
+    ref = unitary_chain(a)
+    assert_rtol_atol(tw, ref.detach(), "unitary twiddle", rtol=1e-6, atol=1e-6)
+    # unitary blocks: T T^H = I
+    eye = tw @ tw.conj().transpose(-1, -2)
+    assert (eye - torch.eye(2)).abs().max() < 1e-6
+    g = torch.randn(shape + (2, 2), dtype=torch.complex64)
+    ref.backward(g)
+    d = torch.empty_like(angles)
+    emul.bfly_emul_unitary_bw(P(angles), P(g), P(d), I64(blocks))
+    assert_rtol_atol(d, a.grad, "unitary twiddle gradient", rtol=1e-5, atol=1e-6)

@@ -152,3 +152,46 @@ def test_training_step_decreases_loss(dev):
         losses.append(loss.item())
     assert losses[-1] < 0.7 * losses[0]
     assert all(math.isfinite(v) for v in losses)
+
+
+def test_unitary_twiddle_kernels_match_the_torch_chain(dev):
+    """bfly_unitary_twiddle_fw / _bw (through the C ABI and through the differentiable torch
+    operator) against the reference's cos / sin / stack chain and autograd's backward of it
+    (torch_butterfly/butterfly.py:271-280); ButterflyUnitary trains through them."""
+    import math
+    import butterfly_b200 as bb
+    from butterfly_b200 import abi
+    from conftest import assert_rtol_atol, unitary_chain
+    torch.manual_seed(4)
+    shape = (3, 2, 11, 1024)
+    angles = torch.cat([torch.asin(torch.sqrt(torch.rand(shape + (1,)))), torch.rand(shape + (3,)) * 2 * math.pi], dim=-1).to(dev)
+    a = angles.clone().requires_grad_(True)
+    ref = unitary_chain(a)
+    g = torch.randn(shape + (2, 2), dtype=torch.complex64, device=dev)
+    ref.backward(g)
+    launches = abi.launch_count()
+    tw, rc = abi.unitary_twiddle_fw(angles)
+    d, rc2 = abi.unitary_twiddle_bw(angles, g)
+    assert rc == 0 and rc2 == 0 and abi.launch_count() - launches == 2
+    assert_rtol_atol(tw, ref.detach(), "unitary twiddle", rtol=1e-5, atol=1e-6)
+    assert_rtol_atol(d, a.grad, "unitary twiddle gradient", rtol=1e-5, atol=2e-6)
+    # the differentiable operator, with a lazily conjugated gradient
+    a2 = angles.clone().requires_grad_(True)
+    bb.unitary_twiddle(a2).backward(g.conj().conj())
+    assert torch.equal(a2.grad, d)
+    # empty tensors, misaligned pointers
+    assert abi.unitary_twiddle_fw(angles[:0])[0].shape == (0, 2, 11, 1024, 2, 2)
+    bad = torch.empty(4 * 8 + 1, device=dev)[1:].view(8, 4)
+    assert abi.unitary_twiddle_fw(bad, check=False)[1] == -3
+    # the layer: unitary matrix, gradients reach the angles
+    layer = bb.ButterflyUnitary(64, 64, bias=False).to(dev)
+    m = layer(torch.eye(64, dtype=torch.complex64, device=dev)).t()
+    assert (m @ m.conj().t() - torch.eye(64, device=dev)).abs().max() < 1e-5
+    x = torch.randn(32, 64, dtype=torch.complex64, device=dev)
+    layer(x).abs().pow(2).sum().backward()
+    ref_layer = bb.ButterflyUnitary(64, 64, bias=False).to(dev)
+    with torch.no_grad():
+        ref_layer.twiddle.copy_(layer.twiddle)
+    tw_ref = unitary_chain(ref_layer.twiddle)
+    bb.butterfly_multiply(tw_ref, x.unsqueeze(1), True).squeeze(1).abs().pow(2).sum().backward()
+    assert_rtol_atol(layer.twiddle.grad, ref_layer.twiddle.grad, "angle gradients through the layer", rtol=1e-4, atol=1e-4)
