@@ -43,7 +43,8 @@ from .multiply_base4 import (  # noqa: E402,F401
 )
 from . import abi  # noqa: E402,F401
 from .butterfly import Butterfly, ButterflyUnitary, ButterflyBmm, ButterflyBase4  # noqa: E402,F401
-from . import permutation, special, host, distributed, combine, kops  # noqa: E402,F401
+from . import permutation, complex_utils, diagonal, glue, special, host, distributed, combine, kops  # noqa: E402,F401
+from .glue import butterfly_multiply_glue  # noqa: E402,F401
 
 __all__ = [
     "butterfly_multiply", "butterfly_multiply_fw", "butterfly_multiply_bw",
@@ -51,5 +52,5 @@ __all__ = [
     "unitary_twiddle", "unitary_twiddle_fw", "unitary_twiddle_bw",
     "butterfly_multiply_base4", "butterfly_multiply_base4_fw", "butterfly_multiply_base4_bw",
     "twiddle_base2_to_base4", "abi", "__version__", "Butterfly", "ButterflyUnitary", "ButterflyBmm", "ButterflyBase4",
-    "permutation", "special", "combine", "kops",
+    "permutation", "special", "combine", "kops", "complex_utils", "diagonal", "glue", "butterfly_multiply_glue",
 ]

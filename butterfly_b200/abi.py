@@ -21,7 +21,7 @@ SYMBOLS = (
     "bfly_bw_workspace_bytes", "bfly_bw_f32", "bfly_bw_c64", "bfly4_fw_f32", "bfly4_bw_workspace_bytes",
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
     "bfly_linear_fw_f32", "bfly_linear_bw_f32", "bfly_linear_bw_workspace_bytes", "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
-    "bfly_unitary_twiddle_fw", "bfly_unitary_twiddle_bw",
+    "bfly_unitary_twiddle_fw", "bfly_unitary_twiddle_bw", "bfly_fw_glue_f32", "bfly_fw_glue_c64",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -255,6 +255,28 @@ def linear_bw(twiddle, x2d, grad2d, increasing_stride=True, with_bias=True, chec
     if check and rc != 0:
         raise BflyError(rc, "bfly_linear_bw_f32")
     return d_tw, d_in, d_b, rc
+
+
+def fw_glue(twiddle, x, increasing_stride=True, in_perm=None, out_diag=None, out_perm=None, out_real=False, check=True):
+    """``bfly_fw_glue_f32`` / ``bfly_fw_glue_c64``: the forward with gather / diagonal / real-complex
+    links folded into its launch.  x float32 with a complex twiddle = real input rows."""
+    _check_rows(x)
+    S, nblocks, log_n = twiddle.shape[:3]
+    n = 1 << log_n
+    B, _, in_size = x.shape
+    cplx = twiddle.is_complex()
+    x_real = cplx and not x.is_complex()
+    out = torch.empty((B, S, n), dtype=torch.float32 if (out_real or not cplx) else torch.complex64, device=x.device)
+    if cplx:
+        rc = lib().bfly_fw_glue_c64(_p(twiddle), _p(x), int(x_real), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), int(out_real),
+                                    _p(in_perm), _p(out_diag), _p(out_perm), B, S, log_n, nblocks, in_size, n,
+                                    int(increasing_stride), _stream())
+    else:
+        rc = lib().bfly_fw_glue_f32(_p(twiddle), _p(x), _i64(x.stride(0)), _i64(x.stride(1)), _p(out), _p(in_perm), _p(out_diag),
+                                    _p(out_perm), B, S, log_n, nblocks, in_size, n, int(increasing_stride), _stream())
+    if check and rc:
+        raise BflyError(rc, "bfly_fw_glue")
+    return out, rc
 
 
 def unitary_twiddle_fw(angles, check=True):

@@ -116,6 +116,53 @@ BFLY_HD void tile_store(T* __restrict__ dst, int64_t sB, int64_t sS, int ncols, 
   }
 }
 
+// Gather inside a tile row, staged through registers: every thread first reads the elements that
+// belong at its columns c = tid, tid + nthr, ... (from column perm[c], times diag[perm[c]] when a
+// diagonal is given), and after a barrier writes them to those columns.  v holds C / nthr values.
+template <typename T>
+BFLY_HD void tile_permute_read(const T* __restrict__ sm, int r, int logC, const int32_t* __restrict__ perm,
+                               const T* __restrict__ diag, int tid, int nthr, T* v) {
+  const int C = 1 << logC;
+  int j = 0;
+  for (int c = tid; c < C; c += nthr, ++j) {
+    const int src = perm ? perm[c] : c;
+    T t = sm[r * C + swzT<T>(src)];
+    if (diag) t = Ops<T>::mul(t, diag[src]);
+    v[j] = t;
+  }
+}
+template <typename T>
+BFLY_HD void tile_permute_write(T* __restrict__ sm, int r, int logC, int tid, int nthr, const T* v) {
+  const int C = 1 << logC;
+  int j = 0;
+  for (int c = tid; c < C; c += nthr, ++j) sm[r * C + swzT<T>(c)] = v[j];
+}
+
+// Whole-row tiles of a complex product fed from / written to float32 rows (real part only).
+BFLY_HD void tile_load_real(const float* __restrict__ src, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0,
+                            int R, int logC, cf* __restrict__ sm, int tid, int nthr) {
+  const int C = 1 << logC;
+  for (int e = tid; e < R * C; e += nthr) {
+    const int r = e >> logC, l = e & (C - 1);
+    const int row = row0 + r;
+    float v = 0.f;
+    if (row < B && l < ncols) v = src[(int64_t)row * sB + (int64_t)stack * sS + l];
+    sm[r * C + swzT<cf>(l)] = cf{v, 0.f};
+  }
+}
+BFLY_HD void tile_store_real(float* __restrict__ dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0, int R,
+                             int logC, const cf* __restrict__ sm, int tid, int nthr) {
+  const int C = 1 << logC;
+  for (int e = tid; e < R * C; e += nthr) {
+    const int r = e >> logC, l = e & (C - 1);
+    const int row = row0 + r;
+    if (row < B && l < ncols) dst[(int64_t)row * sB + (int64_t)stack * sS + l] = sm[r * C + swzT<cf>(l)].re;
+  }
+}
+// float products have no real / complex conversion; the overloads keep the kernel's code uniform
+BFLY_HD void tile_load_real(const float*, int64_t, int64_t, int, int, int, int, int, int, float*, int, int) {}
+BFLY_HD void tile_store_real(float*, int64_t, int64_t, int, int, int, int, int, int, const float*, int, int) {}
+
 // 16-byte-chunk variants for aligned tensors and panels whose segments hold whole chunks.
 // The swizzle moves whole chunks, so a chunk travels with one 16-byte access on both sides.
 // On the device the load is asynchronous (cp.async, zero-filling what lies outside the

@@ -233,13 +233,20 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
                    const std::vector<int>& cuts, T* const* snaps, const T* tw2, const T* tw4, const T* x,
                    int64_t x_sB, int64_t x_sS, int x_cols, T* out, int64_t out_sB, int64_t out_sS,
                    int out_cols, T* scratch = nullptr, int64_t scratch_sB = 0, int64_t scratch_sS = 0,
-                   void* pack_ws = nullptr, size_t pack_bytes = 0) {
+                   void* pack_ws = nullptr, size_t pack_bytes = 0, const FwGlue<T>* glue = nullptr) {
   if (q.B == 0 || t1 <= t0) return BFLY_OK;
+  if (glue) {
+    // glue operators work on tiles that hold whole rows, one gather slot per thread and column group
+    if (fw_pass_logc<T>(q.log_n) < q.log_n || ((1 << q.log_n) > kGlueSlots * ex.threads())) return BFLY_E_UNSUPPORTED;
+    if (sizeof(T) == 4 && (glue->x_real || glue->out_real)) return BFLY_E_ARG;
+  }
   if constexpr (sizeof(T) == 4) {
+   if (!glue) {
     // float rows of 512 .. 4096 columns: the packed-pair kernel, when the tensors qualify
     const int rc2 = drive_fw2(ex, q, st, t0, t1, cuts, snaps, tw2, x, x_sB, x_sS, x_cols, out, out_sB, out_sS, out_cols,
                               pack_ws, pack_bytes);
     if (rc2 != kFw2Declined) return rc2;
+   }
   }
   const int lc = fw_pass_logc<T>(q.log_n);
   if (((int64_t)sizeof(T) << lc) > kSmemMax) return BFLY_E_UNSUPPORTED;
@@ -270,12 +277,14 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
       p.tw[0] = tw2; p.tw[1] = tw4; p.tw_stack[0] = stk[0]; p.tw_stack[1] = stk[1];
       if (first) {
         p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
+        if (glue) { p.glue.in_perm = glue->in_perm; p.glue.x_real = glue->x_real; }
       } else {  // continue in place from the full-width rows written by the previous launch
         if (!work) return BFLY_E_UNSUPPORTED;
         p.x = work; p.x_sB = work_sB; p.x_sS = work_sS; p.x_cols = (int)n;
       }
       if (last) {
         p.out = out; p.out_sB = out_sB; p.out_sS = out_sS; p.out_cols = out_cols;
+        if (glue) { p.glue.out_perm = glue->out_perm; p.glue.out_diag = glue->out_diag; p.glue.out_real = glue->out_real; }
       } else {
         if (!work) return BFLY_E_UNSUPPORTED;
         p.out = work; p.out_sB = work_sB; p.out_sS = work_sS; p.out_cols = (int)n;
@@ -283,7 +292,7 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
       for (int i = 0; i < kMaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
       p.B = q.B; p.S = q.S; p.log_n = q.log_n;
       p.R = fw_rows_per_tile<T>(pn.logC, q.B, tune.ctas_per_sm, tune.max_rows);
-      p.vec_in = vec_ok<T>(p.x, p.x_sB, p.x_sS);
+      p.vec_in = p.x ? vec_ok<T>(p.x, p.x_sB, p.x_sS) : 0;
       p.vec_out = p.out ? vec_ok<T>(p.out, p.out_sB, p.out_sS) : 1;
       p.panel = pn;
       p.ngroups = (int)(g1 - g0);
@@ -324,6 +333,28 @@ int drive_fw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
   if (ws && !aligned16(ws)) ws = nullptr;  // optional scratch: without it the generic kernel runs
   return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), {}, nullptr, tw2, tw4, x, x_sB, x_sS, q.in_size,
                            out, (int64_t)q.S * n, n, q.out_size, (T*)nullptr, 0, 0, ws, ws ? ws_bytes : 0);
+}
+
+// The forward with glue operators folded into its launch (FwGlue).  x / out are null when
+// glue.x_real / glue.out_real carry the rows; strides count elements of whichever is used.  A
+// product of more than kMaxFwGroups stage groups runs as several launches: the intermediate rows
+// then need `out` (complex), so a real output of such a product is not supported.
+template <typename T, typename E>
+int drive_fw_glue(E& ex, const Problem& q, const T* tw2, const T* x, int64_t x_sB, int64_t x_sS, T* out,
+                  const FwGlue<T>& glue) {
+  int rc = check_problem(q);
+  if (rc != BFLY_OK) return rc;
+  if (q.base4) return BFLY_E_UNSUPPORTED;
+  if (q.B == 0) return BFLY_OK;
+  if ((!x && !glue.x_real) || (!out && !glue.out_real) || !tw2) return BFLY_E_ARG;
+  if ((x && glue.x_real) || (out && glue.out_real)) return BFLY_E_ARG;
+  if (!aligned16(tw2)) return BFLY_E_ALIGN;
+  if (glue.in_perm && q.in_size != (1 << q.log_n)) return BFLY_E_ARG;  // the gather addresses whole rows
+  if ((glue.out_perm || glue.out_diag) && q.out_size != (1 << q.log_n)) return BFLY_E_ARG;
+  const std::vector<Stage> st = problem_stages(q);
+  const int64_t n = (int64_t)1 << q.log_n;
+  return drive_fw_range<T>(ex, q, st, 0, (int)st.size(), {}, nullptr, tw2, (const T*)nullptr, x, x_sB, x_sS, q.in_size,
+                           out, (int64_t)q.S * n, n, q.out_size, (T*)nullptr, 0, 0, nullptr, 0, &glue);
 }
 
 // Scratch the forward can use (0 = none needed): room for the re-ordered twiddles of the

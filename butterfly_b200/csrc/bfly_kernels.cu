@@ -102,6 +102,17 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
     mbar_expect_tx(bar, tile_bytes);
     tma_load_tile(tma_smem(sm), &maps.in, bar, c1, c2, p.tma_sx ? stack : 0, row0);
   };
+  // gather (and scale) inside every row of the tile, staged through registers; rows are independent,
+  // so one barrier between a row's reads and its writes is enough
+  auto permute_rows = [&](const int32_t* perm, const T* diag) {
+    T v[kGlueSlots];
+    for (int r = 0; r < p.R; ++r) {
+      tile_permute_read<T>(sm, r, p.panel.logC, perm, diag, tid, kThreads, v);
+      __syncthreads();
+      tile_permute_write<T>(sm, r, p.panel.logC, tid, kThreads, v);
+    }
+    __syncthreads();
+  };
   uint32_t parity = 0;
   if (TMA && tid == 0 && blockIdx.x < ntiles) issue_load(blockIdx.x);
 
@@ -116,10 +127,12 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
         break;
       }
     } else {
-      tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
+      if (p.glue.x_real) tile_load_real(p.glue.x_real, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel.logC, sm, tid, kThreads);
+      else tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
       tile_load_wait();
       __syncthreads();
     }
+    if (p.glue.any_in()) permute_rows(p.glue.in_perm, nullptr);
     for (int g = 0; g < p.ngroups; ++g) {
       fw_group_dispatch<T, KMAX, LOGC, ROWS>(p, g, sm, tab, p.R, stack, pbase, tid, kThreads);
       const bool last = (g + 1 == p.ngroups);
@@ -142,6 +155,13 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
         }
       }
     }
+    if (p.glue.any_out()) {  // the diagonal and the gather of the result, on the finished tile
+      permute_rows(p.glue.out_perm, p.glue.out_diag);
+      if constexpr (TMA) {
+        fence_async_smem();  // the tile is read by the TMA unit next
+        __syncthreads();
+      }
+    }
     if constexpr (TMA) {
       if (tid == 0) {
         if (p.out) {
@@ -155,6 +175,9 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
           issue_load(tile + gridDim.x);
         }
       }
+    } else if (p.glue.out_real) {
+      tile_store_real(p.glue.out_real, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel.logC, sm, tid, kThreads);
+      __syncthreads();
     } else if (p.out) {
       tile_store_auto<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm, tid, kThreads);
       __syncthreads();
@@ -503,7 +526,7 @@ struct CudaExec {
     constexpr int F = (int)(sizeof(T) / 4);
     const int64_t n = (int64_t)1 << p.log_n;
     const TmaGeom geo = tma_geometry(p.panel, p.log_n, p.R, F);
-    bool tma = kTmaInstance && use_tma() && geo.ok && p.vec_in && (!p.out || p.vec_out) &&
+    bool tma = kTmaInstance && use_tma() && geo.ok && !p.glue.x_real && !p.glue.out_real && p.vec_in && (!p.out || p.vec_out) &&
                tma_describe(&maps.in, geo, p.x, p.x_sB, p.x_sS, p.x_cols, p.B, p.S, F) &&
                (!p.out || tma_describe(&maps.out, geo, p.out, p.out_sB, p.out_sS, p.out_cols, p.B, p.S, F));
     for (int i = 0; tma && i < 8; ++i)
@@ -665,6 +688,25 @@ static int fw_entry(bool base4, const void* tw2, const void* tw4, const void* x,
 }
 
 template <typename T>
+static int fw_glue_entry(const void* tw, const void* x, int x_is_real, int64_t x_sB, int64_t x_sS, void* out, int out_is_real,
+                         const int32_t* in_perm, const void* out_diag, const int32_t* out_perm, int B, int S, int log_n,
+                         int nblocks, int in_size, int out_size, int inc, void* stream) {
+  CudaExec ex;
+  int rc = make_exec(stream, ex);
+  if (rc) return rc;
+  Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, false};
+  FwGlue<T> glue{};
+  glue.in_perm = in_perm;
+  glue.out_perm = out_perm;
+  glue.out_diag = static_cast<const T*>(out_diag);
+  if (x_is_real) glue.x_real = static_cast<const float*>(x);
+  if (out_is_real) glue.out_real = static_cast<float*>(out);
+  if (((uintptr_t)in_perm | (uintptr_t)out_perm) & 3u) return BFLY_E_ALIGN;
+  return drive_fw_glue<T>(ex, q, static_cast<const T*>(tw), x_is_real ? nullptr : static_cast<const T*>(x), x_sB, x_sS,
+                          out_is_real ? nullptr : static_cast<T*>(out), glue);
+}
+
+template <typename T>
 static int fw_saving_entry(const void* tw2, const void* x, int64_t x_sB, int64_t x_sS, void* out, int B, int S,
                            int log_n, int nblocks, int in_size, int out_size, int inc, void* ws, size_t ws_bytes,
                            void* stream) {
@@ -808,6 +850,18 @@ int64_t bfly_fw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, in
   if (dtype == BFLY_F32) return (int64_t)fw_workspace_bytes<float>(q);
   if (dtype == BFLY_C64) return (int64_t)fw_workspace_bytes<cf>(q);
   return BFLY_E_UNSUPPORTED;
+}
+int bfly_fw_glue_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, const int32_t* in_perm,
+                     const float* out_diag, const int32_t* out_perm, int batch, int nstacks, int log_n, int nblocks,
+                     int input_size, int output_size, int increasing_stride, void* stream) {
+  return fw_glue_entry<float>(twiddle, x, 0, x_sB, x_sS, out, 0, in_perm, out_diag, out_perm, batch, nstacks, log_n, nblocks,
+                              input_size, output_size, increasing_stride, stream);
+}
+int bfly_fw_glue_c64(const void* twiddle, const void* x, int x_is_real, int64_t x_sB, int64_t x_sS, void* out, int out_is_real,
+                     const int32_t* in_perm, const void* out_diag, const int32_t* out_perm, int batch, int nstacks, int log_n,
+                     int nblocks, int input_size, int output_size, int increasing_stride, void* stream) {
+  return fw_glue_entry<cf>(twiddle, x, x_is_real, x_sB, x_sS, out, out_is_real, in_perm, out_diag, out_perm, batch, nstacks,
+                           log_n, nblocks, input_size, output_size, increasing_stride, stream);
 }
 int bfly_fw_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out, int batch,
                 int nstacks, int log_n, int nblocks, int input_size, int output_size, int increasing_stride,

@@ -171,6 +171,26 @@ struct FwGroup {
   uint16_t d[1 << kMaxK];           // swz(m << lbit): element m of a unit sits at swz(unit) ^ d[m]
 };
 
+// Glue operators folded into a forward launch whose tile holds whole rows (none of them set = the
+// plain product).  They replace element-wise and gather operators that would otherwise each make a
+// full pass over the rows in device memory:
+//   x_real    the input rows are float32 and enter the complex product with zero imaginary part
+//   in_perm   row[c] <- row[in_perm[c]] right after the load (n entries)
+//   out_diag  y[c] <- y[c] * out_diag[c] after the last factor (n entries) ...
+//   out_perm  ... then y[c] <- y[out_perm[c]] (n entries)
+//   out_real  only the real parts of the result are written, as float32 rows
+// x_real / out_real take the place of FwParams::x / ::out (same strides, counted in floats).
+constexpr int kGlueSlots = 16;  // columns per thread of a row in the gather passes
+template <typename T> struct FwGlue {
+  const int32_t* in_perm;
+  const int32_t* out_perm;
+  const T* out_diag;
+  const float* x_real;
+  float* out_real;
+  BFLY_HD bool any_in() const { return in_perm != nullptr; }
+  BFLY_HD bool any_out() const { return out_perm != nullptr || out_diag != nullptr; }
+};
+
 template <typename T> struct FwParams {
   const T* tw[2];            // radix-2 / radix-4 twiddle tensors
   int64_t tw_stack[2];       // elements per stack in each
@@ -191,6 +211,7 @@ template <typename T> struct FwParams {
   int tma, tma_sx, tma_so, tma_pbe, tma_f;
   Panel panel;
   int ngroups;
+  FwGlue<T> glue;
   FwGroup g[kMaxFwGroups];
 };
 

@@ -451,6 +451,65 @@ Tensor butterfly_multiply_base4(const Tensor& twiddle4, const Tensor& twiddle2, 
   return ButterflyMultiplyBase4::apply(twiddle4, twiddle2, input, increasing_stride, output_size);
 }
 
+// ---------------------------------------------------------------- forward with glue operators
+//
+// One launch for  [Real2Complex] [gather] butterfly [diagonal] [gather] [real part]  -- the modules
+// that surround a Butterfly in the reference's exact transforms (torch_butterfly/special.py,
+// permutation.py:65-75, complex_utils.py:100-142, diagonal.py:11-38).  Returns None
+// when the rows do not fit a tile (the caller then runs the operators one by one).
+c10::optional<Tensor> butterfly_multiply_glue_fw(const Tensor& twiddle, const Tensor& input, bool increasing_stride,
+                                  const c10::optional<Tensor>& in_perm, const c10::optional<Tensor>& out_diag,
+                                  const c10::optional<Tensor>& out_perm, bool out_real) {
+  BFLY_CHECK_CUDA(twiddle); BFLY_CHECK_CUDA(input); BFLY_CHECK_SAME_DEVICE(twiddle, input);
+  BFLY_CHECK_DIM(twiddle, 6); BFLY_CHECK_DIM(input, 3);
+  const int64_t batch = input.size(0), nstacks = input.size(1), input_size = input.size(2);
+  const int64_t nblocks = twiddle.size(1), log_n = twiddle.size(2);
+  TORCH_CHECK(log_n >= 1 && log_n <= 24, "butterfly_multiply_glue_fw: n must be a power of 2 (2 <= n <= 2^24)");
+  const int64_t n = (int64_t)1 << log_n;
+  TORCH_CHECK(twiddle.sizes() == torch::IntArrayRef({nstacks, nblocks, log_n, n / 2, 2, 2}),
+              "twiddle must have shape (nstacks, nblocks, log_n, n / 2, 2, 2)");
+  TORCH_CHECK(input_size <= n, "butterfly_multiply_glue_fw: input_size must be <= n");
+  const bool cplx = twiddle.scalar_type() == at::kComplexFloat;
+  TORCH_CHECK(cplx || twiddle.scalar_type() == at::kFloat, "butterfly_multiply_glue_fw: float32 or complex64 twiddle expected");
+  const bool x_real = cplx && input.scalar_type() == at::kFloat;
+  TORCH_CHECK(x_real || input.scalar_type() == twiddle.scalar_type(), "input must have the dtype of twiddle (or float32 for a complex twiddle)");
+  TORCH_CHECK(!out_real || cplx, "out_real needs a complex twiddle");
+  auto index_vec = [&](const c10::optional<Tensor>& t, const char* name) -> Tensor {
+    if (!t.has_value() || !t->defined()) return Tensor();
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->dim() == 1 && t->size(0) == n, name,
+                " must be an int32 CUDA vector of n entries");
+    return t->contiguous();
+  };
+  c10::cuda::CUDAGuard guard(input.device());
+  const Tensor ip = index_vec(in_perm, "in_perm"), op = index_vec(out_perm, "out_perm");
+  Tensor od;
+  if (out_diag.has_value() && out_diag->defined()) {
+    TORCH_CHECK(out_diag->is_cuda() && out_diag->scalar_type() == twiddle.scalar_type() && out_diag->dim() == 1 &&
+                    out_diag->size(0) == n, "out_diag must be a CUDA vector of n entries with the dtype of twiddle");
+    od = out_diag->resolve_conj().contiguous();
+  }
+  TORCH_CHECK(!ip.defined() || input_size == n, "in_perm needs input_size == n");
+  const Tensor tw = dense_twiddle(twiddle);
+  const Tensor x = rows_view(input);
+  Tensor output = torch::empty({batch, nstacks, n}, input.options().dtype(out_real ? at::kFloat : twiddle.scalar_type()));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  int rc;
+  if (cplx) {
+    rc = bfly_fw_glue_c64(tw.data_ptr(), x.data_ptr(), x_real, x.stride(0), x.stride(1), output.data_ptr(), out_real,
+                          ip.defined() ? ip.data_ptr<int32_t>() : nullptr, od.defined() ? od.data_ptr() : nullptr,
+                          op.defined() ? op.data_ptr<int32_t>() : nullptr, (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
+                          (int)input_size, (int)n, increasing_stride, stream.stream());
+  } else {
+    rc = bfly_fw_glue_f32(tw.data_ptr<float>(), x.data_ptr<float>(), x.stride(0), x.stride(1), output.data_ptr<float>(),
+                          ip.defined() ? ip.data_ptr<int32_t>() : nullptr, od.defined() ? od.data_ptr<float>() : nullptr,
+                          op.defined() ? op.data_ptr<int32_t>() : nullptr, (int)batch, (int)nstacks, (int)log_n, (int)nblocks,
+                          (int)input_size, (int)n, increasing_stride, stream.stream());
+  }
+  if (rc == BFLY_E_UNSUPPORTED) return c10::nullopt;
+  check_status(rc, "butterfly_multiply_glue_fw");
+  return output;
+}
+
 // ---------------------------------------------------------------- unitary twiddle synthesis
 //
 // (..., 4) float32 angles -> (..., 2, 2) complex64 blocks and back, one kernel each, in place of
@@ -519,6 +578,8 @@ TORCH_LIBRARY(torch_butterfly, m) {
         butterfly_linear_bw);
   m.def("butterfly_linear(Tensor twiddle, Tensor input, Tensor? bias, bool increasing_stride, int out_size) -> Tensor",
         butterfly_linear);
+  m.def("butterfly_multiply_glue_fw(Tensor twiddle, Tensor input, bool increasing_stride, Tensor? in_perm, Tensor? out_diag, Tensor? out_perm, bool out_real) -> Tensor?",
+        butterfly_multiply_glue_fw);
   m.def("unitary_twiddle_fw(Tensor angles) -> Tensor", unitary_twiddle_fw);
   m.def("unitary_twiddle_bw(Tensor angles, Tensor grad) -> Tensor", unitary_twiddle_bw);
   m.def("unitary_twiddle(Tensor angles) -> Tensor", unitary_twiddle);

@@ -212,6 +212,31 @@ int bfly_linear_bw_f32(const float* twiddle, const float* x, int64_t x_sB, const
                        int nstacks, int log_n, int nblocks, int input_size, int output_size,
                        int increasing_stride, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Forward with glue operators folded into the launch.  Replaces the element-wise and gather
+ * modules that surround a Butterfly in the reference's exact-transform pipelines, each of which is
+ * a pass of its own over the rows there: FixedPermutation (torch_butterfly/permutation.py:65-75),
+ * Real2Complex / Complex2Real and index_last_dim (torch_butterfly/complex_utils.py:100-142),
+ * Diagonal (torch_butterfly/diagonal.py:11-38), as composed in torch_butterfly/special.py
+ * (fft / ifft with their bit-reversal, circulant = fft, diagonal, ifft).  In order:
+ *   x_is_real   x holds float32 rows that enter the complex product with zero imaginary part
+ *   in_perm     (n int32, or NULL) row[c] <- row[in_perm[c]] before the first factor
+ *   out_diag    (n elements, or NULL) y[c] <- y[c] * out_diag[c] after the last factor
+ *   out_perm    (n int32, or NULL) y[c] <- y[out_perm[c]] after the diagonal
+ *   out_is_real out receives float32 rows: the real parts of the result
+ * Same arguments and result as bfly_fw_* otherwise; x_sB / x_sS count elements of x as given
+ * (floats when x_is_real), out is (batch, nstacks, n) contiguous in its own element type.
+ * Gathers and the diagonal need input_size == n / output_size == n.  Rows must fit one CTA's
+ * shared memory (n <= 4096 float32, n <= 2048 complex64); otherwise BFLY_E_UNSUPPORTED and the
+ * caller runs the operators one by one. */
+int bfly_fw_glue_f32(const float* twiddle, const float* x, int64_t x_sB, int64_t x_sS, float* out,
+                     const int32_t* in_perm, const float* out_diag, const int32_t* out_perm, int batch,
+                     int nstacks, int log_n, int nblocks, int input_size, int output_size,
+                     int increasing_stride, void* stream);
+int bfly_fw_glue_c64(const void* twiddle, const void* x, int x_is_real, int64_t x_sB, int64_t x_sS,
+                     void* out, int out_is_real, const int32_t* in_perm, const void* out_diag,
+                     const int32_t* out_perm, int batch, int nstacks, int log_n, int nblocks,
+                     int input_size, int output_size, int increasing_stride, void* stream);
+
 /* Twiddles of a unitary butterfly from their angles, and the gradient of the angles.  Replaces the
  * chain of cos / sin / stack operators (and autograd's backward of it) that the reference's
  * ButterflyUnitary.forward runs on every call (torch_butterfly/butterfly.py:271-280).

@@ -150,8 +150,20 @@ struct EmulExec {
     for (int64_t tile = 0; tile < ntiles; ++tile) {
       int row0, stack, pbase;
       fw_tile_coords(p, tile, row0, stack, pbase);
-      for (int tid = 0; tid < threads_; ++tid)
-        tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm.data(), tid, threads_);
+      for (int tid = 0; tid < threads_; ++tid) {
+        if (p.glue.x_real) tile_load_real(p.glue.x_real, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel.logC, sm.data(), tid, threads_);
+        else tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm.data(), tid, threads_);
+      }
+      // the kernel's gather pass: every thread reads, barrier, every thread writes
+      auto permute_rows = [&](const int32_t* perm, const T* diag) {
+        const int slots = (C + threads_ - 1) / threads_;
+        std::vector<T> v((size_t)threads_ * slots);
+        for (int r = 0; r < p.R; ++r) {
+          for (int tid = 0; tid < threads_; ++tid) tile_permute_read<T>(sm.data(), r, p.panel.logC, perm, diag, tid, threads_, v.data() + (size_t)tid * slots);
+          for (int tid = 0; tid < threads_; ++tid) tile_permute_write<T>(sm.data(), r, p.panel.logC, tid, threads_, v.data() + (size_t)tid * slots);
+        }
+      };
+      if (p.glue.any_in()) permute_rows(p.glue.in_perm, nullptr);
       for (int g = 0; g < p.ngroups; ++g) {
         for (int tid = 0; tid < threads_; ++tid)
           fw_group_dispatch<T, 4, 0, 0>(p, g, sm.data(), tab.data(), p.R, stack, pbase, tid, threads_);
@@ -159,7 +171,11 @@ struct EmulExec {
           for (int tid = 0; tid < threads_; ++tid)
             tile_store_auto<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm.data(), tid, threads_);
       }
-      if (p.out)
+      if (p.glue.any_out()) permute_rows(p.glue.out_perm, p.glue.out_diag);
+      if (p.glue.out_real)
+        for (int tid = 0; tid < threads_; ++tid)
+          tile_store_real(p.glue.out_real, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel.logC, sm.data(), tid, threads_);
+      else if (p.out)
         for (int tid = 0; tid < threads_; ++tid)
           tile_store_auto<T>(p.out, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_out != 0, sm.data(), tid, threads_);
     }
@@ -413,6 +429,23 @@ int bfly_emul_linear_bw(const void* tw, const void* x, int64_t x_sB, const void*
   void* wsp = (void*)(((uintptr_t)ws.data() + 255) / 256 * 256);
   return drive_linear_bw(ex, q, (const float*)tw, (const float*)x, x_sB, (const float*)g, g_sB, (float*)d_tw, (float*)d_in,
                          din_sB, (float*)d_bias, out_total, wsp, L.ws_bytes);
+}
+// the forward with glue operators (drive_fw_glue); dtype 0 float32, 1 complex64
+int bfly_emul_fw_glue(int dtype, const void* tw, const void* x, int x_is_real, int64_t x_sB, int64_t x_sS, void* out, int out_is_real,
+                      const int32_t* in_perm, const void* out_diag, const int32_t* out_perm, int B, int S, int log_n, int nblocks,
+                      int in_size, int out_size, int inc, int threads) {
+  EmulExec ex; ex.threads_ = threads;
+  Problem q{B, S, log_n, nblocks, in_size, out_size, inc != 0, false};
+  if (dtype == 0) {
+    FwGlue<float> g{};
+    g.in_perm = in_perm; g.out_perm = out_perm; g.out_diag = (const float*)out_diag;
+    return drive_fw_glue<float>(ex, q, (const float*)tw, (const float*)x, x_sB, x_sS, (float*)out, g);
+  }
+  FwGlue<cf> g{};
+  g.in_perm = in_perm; g.out_perm = out_perm; g.out_diag = (const cf*)out_diag;
+  if (x_is_real) g.x_real = (const float*)x;
+  if (out_is_real) g.out_real = (float*)out;
+  return drive_fw_glue<cf>(ex, q, (const cf*)tw, x_is_real ? nullptr : (const cf*)x, x_sB, x_sS, out_is_real ? nullptr : (cf*)out, g);
 }
 // number of backward phases and workspace bytes the planner chooses (for tests of the planner)
 int bfly_emul_bw_plan(int dtype, int base4, int B, int S, int log_n, int nblocks, int inc, int64_t* ws_bytes) {

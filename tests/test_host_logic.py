@@ -380,3 +380,52 @@ def test_unitary_twiddle_arithmetic(emul):
     d = torch.empty_like(angles)
     emul.bfly_emul_unitary_bw(P(angles), P(g), P(d), I64(blocks))
     assert_rtol_atol(d, a.grad, "unitary twiddle gradient", rtol=1e-5, atol=1e-6)
+
+
+def _glue_reference(oracle_mod, tw, x, inc, in_perm, out_diag, out_perm, out_real):
+    """The pipeline the glue forward replaces, operator by operator on the oracle."""
+    xin = x.to(tw.dtype)
+    if in_perm is not None:
+        xin = xin[..., in_perm.long()]
+    y = oracle_mod.multiply_fw(tw, xin.contiguous(), inc)
+    if out_diag is not None:
+        y = y * out_diag
+    if out_perm is not None:
+        y = y[..., out_perm.long()]
+    return y.real.contiguous() if out_real else y
+
+
+@pytest.mark.parametrize("cplx", [False, True])
+def test_forward_with_glue_operators(emul, oracle_mod, cplx):
+    """Gather before, diagonal and gather after, real input / output: the kernel's passes on the
+    tile (emulated thread by thread) against the chain of separate operators."""
+    torch.manual_seed(8)
+    dtype = torch.complex64 if cplx else torch.float32
+    for log_n, nb, B, S in ((6, 1, 5, 1), (9, 2, 9, 2), (11, 1, 3, 1)):
+        n = 1 << log_n
+        tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5
+        for combo in range(8 if cplx else 4):
+            use_in, use_out = bool(combo & 1), bool(combo & 2)
+            real_io = bool(combo & 4)
+            x = torch.randn(B, S, n, dtype=torch.float32 if real_io else dtype)
+            in_perm = torch.randperm(n, dtype=torch.int32) if use_in else None
+            out_perm = torch.randperm(n, dtype=torch.int32) if use_out else None
+            out_diag = torch.randn(n, dtype=dtype) if use_out else None
+            out = torch.full((B, S, n), float("nan"), dtype=torch.float32 if real_io else dtype)
+            rc = emul.bfly_emul_fw_glue(int(cplx), P(tw), P(x), int(real_io), I64(x.stride(0)), I64(x.stride(1)), P(out), int(real_io),
+                                        P(in_perm), P(out_diag), P(out_perm), B, S, log_n, nb, n, n, 1, 256)
+            assert rc == 0, (log_n, combo, rc)
+            want = _glue_reference(oracle_mod, tw, x, True, in_perm, out_diag, out_perm, real_io)
+            assert_rtol_atol(out, want, "glue forward n=%d combo=%d" % (n, combo), rtol=1e-4, atol=1e-4)
+    # rows wider than a tile, gathers on ragged sizes: refused
+    n = 1 << 13
+    tw = torch.randn(1, 1, 13, n // 2, 2, 2)
+    x = torch.randn(2, 1, n)
+    perm = torch.randperm(n, dtype=torch.int32)
+    assert emul.bfly_emul_fw_glue(0, P(tw), P(x), 0, I64(n), I64(n), P(torch.empty(2, 1, n)), 0, P(perm), None, None,
+                                  2, 1, 13, 1, n, n, 1, 256) == -2
+    tw = torch.randn(1, 1, 6, 32, 2, 2)
+    x = torch.randn(2, 1, 64)
+    perm = torch.randperm(64, dtype=torch.int32)
+    assert emul.bfly_emul_fw_glue(0, P(tw), P(x), 0, I64(64), I64(64), P(torch.empty(2, 1, 64)), 0, P(perm), None, None,
+                                  2, 1, 6, 1, 60, 64, 1, 256) == -1
