@@ -330,6 +330,70 @@ def measure_linear_layer(bb, configs, dev, peak, rank=0, iters=5, warm=3):
     return out
 
 
+def measure_glue_rows(bb, dev, peak, iters=5, warm=3):
+    """The layers next to the multiply, fused against link by link, on inputs larger than L2:
+    an FFT with its bit-reversal and a circulant on real rows (glue operators inside the forward
+    launch), a 2-D butterfly map (one multiply over the flattened image against two passes around a
+    transpose), and the unitary twiddle synthesis (one kernel each way against the torch chain)."""
+    import torch
+    from butterfly_b200 import special, combine
+    out = []
+    with torch.no_grad():
+        n, B = 2048, 16384  # 268 MB of complex64 rows
+        x = torch.randn(B, n, dtype=torch.complex64, device=dev)
+        fused, chained = special.fft(n).to(dev), special.fft(n, fused=False).to(dev)
+        e = {"name": "fft n=2048 complex64 with bit reversal", "batch": B,
+             "fused_fw_ms": _events_ms(lambda: fused(x), iters, warm), "link_by_link_fw_ms": _events_ms(lambda: chained(x), iters, warm),
+             "algorithmic_bytes": 2 * B * n * 8}
+        e["fused_gbs"] = e["algorithmic_bytes"] / e["fused_fw_ms"] / 1e6
+        e["fused_frac_of_hbm_peak"] = e["fused_gbs"] / peak
+        out.append(e)
+        del x
+        n, B = 2048, 32768  # 268 MB of float32 rows in, the same out
+        x = torch.randn(B, n, device=dev)
+        col = torch.randn(n)
+        fused, chained = special.circulant(col).to(dev), special.circulant(col, fused=False).to(dev)
+        e = {"name": "circulant n=2048 on float32 rows (real to complex, fft, diagonal, ifft, real part)", "batch": B,
+             "fused_fw_ms": _events_ms(lambda: fused(x), iters, warm), "link_by_link_fw_ms": _events_ms(lambda: chained(x), iters, warm),
+             "algorithmic_bytes": 2 * B * n * 4}
+        e["fused_gbs"] = e["algorithmic_bytes"] / e["fused_fw_ms"] / 1e6
+        e["fused_frac_of_hbm_peak"] = e["fused_gbs"] / peak
+        out.append(e)
+        del x
+        h = w = 64
+        B = 8192  # 268 MB of complex64 images
+        x = torch.randn(B, h, w, dtype=torch.complex64, device=dev)
+        b1 = bb.Butterfly(w, w, False, True, True).to(dev)
+        b2 = bb.Butterfly(h, h, False, True, True).to(dev)
+        one, two = combine.TensorProduct(b1, b2), combine.TensorProduct(b1, b2, fused=False)
+        e = {"name": "tensor product of two butterflies on 64x64 complex64 images", "batch": B,
+             "fused_fw_ms": _events_ms(lambda: one(x), iters, warm), "link_by_link_fw_ms": _events_ms(lambda: two(x), iters, warm),
+             "algorithmic_bytes": 2 * B * h * w * 8}
+        e["fused_gbs"] = e["algorithmic_bytes"] / e["fused_fw_ms"] / 1e6
+        e["fused_frac_of_hbm_peak"] = e["fused_gbs"] / peak
+        out.append(e)
+        del x
+    layer = bb.ButterflyUnitary(4096, 4096, bias=False, nblocks=2).to(dev)
+    angles = layer.twiddle.detach().clone().requires_grad_(True)
+    g = torch.randn(angles.shape[:-1] + (2, 2), dtype=torch.complex64, device=dev)
+
+    def chain():
+        phi, alpha, psi, chi = torch.unbind(angles, -1)
+        c, s_ = torch.cos(phi), torch.sin(phi)
+        pol = lambda r, a: torch.stack((r * torch.cos(a), r * torch.sin(a)), dim=-1)
+        tw = torch.stack([torch.stack([pol(c, alpha + psi), pol(s_, alpha + chi)], dim=-2),
+                          torch.stack([pol(-s_, alpha - chi), pol(c, alpha - psi)], dim=-2)], dim=-3)
+        torch.view_as_complex(tw).backward(g)
+        angles.grad = None
+
+    def kernels():
+        bb.unitary_twiddle(angles).backward(g)
+        angles.grad = None
+    out.append({"name": "unitary twiddle synthesis and its backward, n=4096, two blocks", "blocks_2x2": angles.numel() // 4,
+                "fused_fw_bw_ms": _events_ms(kernels, iters, warm), "link_by_link_fw_bw_ms": _events_ms(chain, iters, warm)})
+    return out
+
+
 def two_block_inputs(log_n, dev, elements=1 << 26):
     """Real fp32 two-block product (increasing then decreasing stride) over `elements` elements."""
     import math
@@ -496,6 +560,7 @@ def run_gpu_arm(args):
             other.append(measure_config(bb, configs, "two-block n=%d" % (1 << log_n), dev, peak,
                                         make=lambda: two_block_inputs(log_n, dev), ref_ops=ref_ops if log_n <= 11 else None))
         other.append(measure_linear_layer(bb, configs, dev, peak))
+        other.extend(measure_glue_rows(bb, dev, peak))
         if ref_ops is not None:
             ref_cuda_note = {"kind": "reference", "library": "oracle/_ref/_butterfly_ref_cuda.so",
                              "what": "csrc/cuda/butterfly_cuda.cu of the reference compiled unmodified for sm_100; "

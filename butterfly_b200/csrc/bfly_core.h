@@ -116,32 +116,128 @@ BFLY_HD void tile_store(T* __restrict__ dst, int64_t sB, int64_t sS, int ncols, 
   }
 }
 
-// Gather inside a tile row, staged through registers: every thread first reads the elements that
-// belong at its columns c = tid, tid + nthr, ... (from column perm[c], times diag[perm[c]] when a
-// diagonal is given), and after a barrier writes them to those columns.  v holds C / nthr values.
+// Gather inside a tile row, staged through registers.  A thread owns the columns
+// c_k = deposit(tid + k * nthr, colbit); tile_permute_plan packs, per owned column, (source column
+// << 16 | own column) once per pass; then for every row all threads read their sources (times
+// diag[source] when a diagonal is given), and after a barrier write their own columns.
 template <typename T>
-BFLY_HD void tile_permute_read(const T* __restrict__ sm, int r, int logC, const int32_t* __restrict__ perm,
-                               const T* __restrict__ diag, int tid, int nthr, T* v) {
+BFLY_HD int tile_permute_plan(int logC, const int32_t* __restrict__ perm, const uint8_t* colbit, int tid, int nthr, uint32_t* plan) {
   const int C = 1 << logC;
-  int j = 0;
-  for (int c = tid; c < C; c += nthr, ++j) {
+  int cnt = 0;
+#pragma unroll
+  for (int k = 0; k < kGlueSlots; ++k) {
+    const int i = tid + k * nthr;
+    if (i >= C) break;
+    const int c = deposit_unit(i, colbit, logC);
     const int src = perm ? perm[c] : c;
-    T t = sm[r * C + swzT<T>(src)];
+    plan[k] = ((uint32_t)src << 16) | (uint32_t)c;
+    cnt = k + 1;
+  }
+  return cnt;
+}
+template <typename T>
+BFLY_HD void tile_permute_read(const T* __restrict__ sm, int r, int logC, const T* __restrict__ diag, const uint32_t* plan, int cnt, T* v) {
+  const T* row = sm + ((size_t)r << logC);
+#pragma unroll
+  for (int k = 0; k < kGlueSlots; ++k) {  // fixed bound: plan and v stay in registers
+    if (k >= cnt) break;
+    const int src = (int)(plan[k] >> 16);
+    T t = row[swzT<T>(src)];
     if (diag) t = Ops<T>::mul(t, diag[src]);
-    v[j] = t;
+    v[k] = t;
   }
 }
 template <typename T>
-BFLY_HD void tile_permute_write(T* __restrict__ sm, int r, int logC, int tid, int nthr, const T* v) {
+BFLY_HD void tile_permute_write(T* __restrict__ sm, int r, int logC, const uint32_t* plan, int cnt, const T* v) {
+  T* row = sm + ((size_t)r << logC);
+#pragma unroll
+  for (int k = 0; k < kGlueSlots; ++k) {
+    if (k >= cnt) break;
+    row[swzT<T>((int)(plan[k] & 0xffffu))] = v[k];
+  }
+}
+
+// Diagonal without a gather: y[c] *= diag[c] in place, 16 bytes at a time; a thread keeps its
+// columns' diagonal entries in registers over the rows of the tile.  No barrier needed inside.
+template <typename T>
+BFLY_HD void tile_scale_rows(T* __restrict__ sm, int R, int logC, const T* __restrict__ diag, int tid, int nthr) {
+  constexpr int V = Vec16<T>::N, VL = Vec16<T>::LOG;
   const int C = 1 << logC;
-  int j = 0;
-  for (int c = tid; c < C; c += nthr, ++j) sm[r * C + swzT<T>(c)] = v[j];
+  if (logC < VL) {
+    for (int e = tid; e < R * C; e += nthr) {
+      const int l = e & (C - 1);
+      T* q = sm + (e >> logC) * C + swzT<T>(l);
+      *q = Ops<T>::mul(*q, diag[l]);
+    }
+    return;
+  }
+  constexpr int kChunks = kGlueSlots / V;  // chunks per thread and row when C / nthr == kGlueSlots
+  T d[kChunks][V];
+#pragma unroll
+  for (int k = 0; k < kChunks; ++k) {
+    const int l = (tid + k * nthr) << VL;
+    if (l >= C) break;
+#pragma unroll
+    for (int i = 0; i < V; ++i) d[k][i] = diag[l + i];
+  }
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int k = 0; k < kChunks; ++k) {
+      const int l = (tid + k * nthr) << VL;
+      if (l >= C) break;
+      T* q = sm + r * C + swzT<T>(l);  // the swizzle moves whole 16-byte chunks
+      T v[V];
+      sm_ld16<0>(sm_addr(q), v);
+#pragma unroll
+      for (int i = 0; i < V; ++i) v[i] = Ops<T>::mul(v[i], d[k][i]);
+      sm_st16<0>(sm_addr(q), v);
+    }
+  }
+}
+
+// Column bits for the gather passes (FwGlue::colbit).  The lanes of a warp run over column bits
+// 0, 4, 5, 6, 1: bits 4-6 are the ones the tile's swizzle folds into the bank bits, so consecutive
+// lanes land in different banks both at their own column and at its bit-reversed image (the common
+// gather).  Measured on B200 against lanes on bits 0-4: 0.40 vs 0.48 ms for an FFT of 16384 rows
+// of 2048 complex64 with its bit-reversal; candidates chosen by a bank-conflict model of 8-byte
+// accesses did worse than either.  Any choice is correct.
+inline void glue_column_bits(int logC, uint8_t* colbit) {
+  for (int j = 0; j < 16; ++j) colbit[j] = (uint8_t)j;
+  if (logC < 7) return;
+  const uint8_t lanes[5] = {0, 4, 5, 6, 1};
+  int k = 0;
+  for (int j = 0; j < 5; ++j) colbit[k++] = lanes[j];
+  for (int b = 0; b < logC; ++b)
+    if (b != 0 && b != 1 && b != 4 && b != 5 && b != 6) colbit[k++] = (uint8_t)b;
 }
 
 // Whole-row tiles of a complex product fed from / written to float32 rows (real part only).
 BFLY_HD void tile_load_real(const float* __restrict__ src, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0,
                             int R, int logC, cf* __restrict__ sm, int tid, int nthr) {
   const int C = 1 << logC;
+  const bool vec = logC >= 2 && (ncols & 3) == 0 && ((sB | sS) & 3) == 0 && (((uintptr_t)src) & 15u) == 0;
+  if (vec) {  // four floats per access: two 16-byte chunks of the complex tile, which the swizzle keeps 2 apart
+    const int Q = C >> 2;
+    for (int e = tid; e < R * Q; e += nthr) {
+      const int r = e / Q, l = (e - r * Q) << 2;
+      const int row = row0 + r;
+      float f[4] = {0.f, 0.f, 0.f, 0.f};
+      if (row < B && l < ncols) {
+        const float* q = src + (int64_t)row * sB + (int64_t)stack * sS + l;
+#if defined(__CUDA_ARCH__)
+        const float4 t = *reinterpret_cast<const float4*>(q);
+        f[0] = t.x; f[1] = t.y; f[2] = t.z; f[3] = t.w;
+#else
+        for (int i = 0; i < 4; ++i) f[i] = q[i];
+#endif
+      }
+      cf* d = sm + r * C;
+      const int a = swzT<cf>(l);
+      d[a] = cf{f[0], 0.f}; d[a + 1] = cf{f[1], 0.f};
+      d[a ^ 2] = cf{f[2], 0.f}; d[(a ^ 2) + 1] = cf{f[3], 0.f};
+    }
+    return;
+  }
   for (int e = tid; e < R * C; e += nthr) {
     const int r = e >> logC, l = e & (C - 1);
     const int row = row0 + r;
@@ -153,6 +249,24 @@ BFLY_HD void tile_load_real(const float* __restrict__ src, int64_t sB, int64_t s
 BFLY_HD void tile_store_real(float* __restrict__ dst, int64_t sB, int64_t sS, int ncols, int B, int stack, int row0, int R,
                              int logC, const cf* __restrict__ sm, int tid, int nthr) {
   const int C = 1 << logC;
+  const bool vec = logC >= 2 && (ncols & 3) == 0 && ((sB | sS) & 3) == 0 && (((uintptr_t)dst) & 15u) == 0;
+  if (vec) {
+    const int Q = C >> 2;
+    for (int e = tid; e < R * Q; e += nthr) {
+      const int r = e / Q, l = (e - r * Q) << 2;
+      const int row = row0 + r;
+      if (row >= B || l >= ncols) continue;
+      const cf* s_ = sm + r * C;
+      const int a = swzT<cf>(l);
+      float* q = dst + (int64_t)row * sB + (int64_t)stack * sS + l;
+#if defined(__CUDA_ARCH__)
+      *reinterpret_cast<float4*>(q) = make_float4(s_[a].re, s_[a + 1].re, s_[a ^ 2].re, s_[(a ^ 2) + 1].re);
+#else
+      q[0] = s_[a].re; q[1] = s_[a + 1].re; q[2] = s_[a ^ 2].re; q[3] = s_[(a ^ 2) + 1].re;
+#endif
+    }
+    return;
+  }
   for (int e = tid; e < R * C; e += nthr) {
     const int r = e >> logC, l = e & (C - 1);
     const int row = row0 + r;

@@ -278,6 +278,7 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
       if (first) {
         p.x = x; p.x_sB = x_sB; p.x_sS = x_sS; p.x_cols = x_cols;
         if (glue) { p.glue.in_perm = glue->in_perm; p.glue.x_real = glue->x_real; }
+        if (glue) glue_column_bits(pn.logC, p.glue.colbit);
       } else {  // continue in place from the full-width rows written by the previous launch
         if (!work) return BFLY_E_UNSUPPORTED;
         p.x = work; p.x_sB = work_sB; p.x_sS = work_sS; p.x_cols = (int)n;
@@ -285,6 +286,7 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
       if (last) {
         p.out = out; p.out_sB = out_sB; p.out_sS = out_sS; p.out_cols = out_cols;
         if (glue) { p.glue.out_perm = glue->out_perm; p.glue.out_diag = glue->out_diag; p.glue.out_real = glue->out_real; }
+        if (glue) glue_column_bits(pn.logC, p.glue.colbit);
       } else {
         if (!work) return BFLY_E_UNSUPPORTED;
         p.out = work; p.out_sB = work_sB; p.out_sS = work_sS; p.out_cols = (int)n;

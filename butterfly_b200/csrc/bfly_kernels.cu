@@ -68,7 +68,9 @@ struct FwMaps {
 // Tile traffic goes through the TMA unit when every tensor of the launch can be described to
 // it (p.tma): thread 0 issues one bulk tensor load per tile and one bulk tensor store per
 // output, everybody waits on an mbarrier.  Otherwise every thread copies 16-byte chunks.
-template <typename T, int KMAX, int LOGC, int ROWS, bool TMA>
+// GLUE: the instance also runs the glue operators of FwParams::glue (a separate instance, so that
+// the plain product keeps its register budget).
+template <typename T, int KMAX, int LOGC, int ROWS, bool TMA, bool GLUE>
 __global__ void __launch_bounds__(kThreads, (FwOcc<T, KMAX>::kMinBlocks))
 bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ FwMaps maps) {
   extern __shared__ __align__(16) unsigned char smem_dyn[];
@@ -105,11 +107,13 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
   // gather (and scale) inside every row of the tile, staged through registers; rows are independent,
   // so one barrier between a row's reads and its writes is enough
   auto permute_rows = [&](const int32_t* perm, const T* diag) {
+    uint32_t plan[kGlueSlots];
     T v[kGlueSlots];
+    const int cnt = tile_permute_plan<T>(p.panel.logC, perm, p.glue.colbit, tid, kThreads, plan);
     for (int r = 0; r < p.R; ++r) {
-      tile_permute_read<T>(sm, r, p.panel.logC, perm, diag, tid, kThreads, v);
+      tile_permute_read<T>(sm, r, p.panel.logC, diag, plan, cnt, v);
       __syncthreads();
-      tile_permute_write<T>(sm, r, p.panel.logC, tid, kThreads, v);
+      tile_permute_write<T>(sm, r, p.panel.logC, plan, cnt, v);
     }
     __syncthreads();
   };
@@ -127,12 +131,14 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
         break;
       }
     } else {
-      if (p.glue.x_real) tile_load_real(p.glue.x_real, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel.logC, sm, tid, kThreads);
+      if (GLUE && p.glue.x_real) tile_load_real(p.glue.x_real, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel.logC, sm, tid, kThreads);
       else tile_load_auto<T>(p.x, p.x_sB, p.x_sS, p.x_cols, p.B, stack, row0, p.R, p.panel, pbase, p.vec_in != 0, sm, tid, kThreads);
       tile_load_wait();
       __syncthreads();
     }
-    if (p.glue.any_in()) permute_rows(p.glue.in_perm, nullptr);
+    if constexpr (GLUE) {
+      if (p.glue.any_in()) permute_rows(p.glue.in_perm, nullptr);
+    }
     for (int g = 0; g < p.ngroups; ++g) {
       fw_group_dispatch<T, KMAX, LOGC, ROWS>(p, g, sm, tab, p.R, stack, pbase, tid, kThreads);
       const bool last = (g + 1 == p.ngroups);
@@ -155,11 +161,18 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
         }
       }
     }
-    if (p.glue.any_out()) {  // the diagonal and the gather of the result, on the finished tile
-      permute_rows(p.glue.out_perm, p.glue.out_diag);
-      if constexpr (TMA) {
-        fence_async_smem();  // the tile is read by the TMA unit next
-        __syncthreads();
+    if constexpr (GLUE) {
+      if (p.glue.any_out()) {  // the diagonal and the gather of the result, on the finished tile
+        if (p.glue.out_perm) {
+          permute_rows(p.glue.out_perm, p.glue.out_diag);
+        } else {
+          tile_scale_rows<T>(sm, p.R, p.panel.logC, p.glue.out_diag, tid, kThreads);
+          __syncthreads();
+        }
+        if constexpr (TMA) {
+          fence_async_smem();  // the tile is read by the TMA unit next
+          __syncthreads();
+        }
       }
     }
     if constexpr (TMA) {
@@ -175,7 +188,7 @@ bfly_fw_kernel(const __grid_constant__ FwParams<T> p, const __grid_constant__ Fw
           issue_load(tile + gridDim.x);
         }
       }
-    } else if (p.glue.out_real) {
+    } else if (GLUE && p.glue.out_real) {
       tile_store_real(p.glue.out_real, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel.logC, sm, tid, kThreads);
       __syncthreads();
     } else if (p.out) {
@@ -513,9 +526,13 @@ struct CudaExec {
     // the TMA variant exists for the instances with a compile-time tile shape (the generic
     // instances have no registers to spare for it)
     constexpr bool kTmaInstance = LOGC > 0;
-    int rc = set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, false>, smem);
+    const bool glue = p.glue.in_perm || p.glue.out_perm || p.glue.out_diag || p.glue.x_real || p.glue.out_real;
+    int rc = glue ? set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, false, true>, smem)
+                  : set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, false, false>, smem);
     if constexpr (kTmaInstance) {
-      if (rc == BFLY_OK) rc = set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, true>, smem);
+      if (rc == BFLY_OK)
+        rc = glue ? set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, true, true>, smem)
+                  : set_smem(bfly_fw_kernel<T, KMAX, LOGC, ROWS, true, false>, smem);
     }
     if (rc) return rc;
     const int64_t ntiles = fw_num_tiles(p);
@@ -539,11 +556,15 @@ struct CudaExec {
       bool launched = false;
       if constexpr (kTmaInstance) {
         if (tma) {
-          bfly_fw_kernel<T, KMAX, LOGC, ROWS, true><<<grid, kThreads, smem, stream>>>(p, maps);
+          if (glue) bfly_fw_kernel<T, KMAX, LOGC, ROWS, true, true><<<grid, kThreads, smem, stream>>>(p, maps);
+          else bfly_fw_kernel<T, KMAX, LOGC, ROWS, true, false><<<grid, kThreads, smem, stream>>>(p, maps);
           launched = true;
         }
       }
-      if (!launched) bfly_fw_kernel<T, KMAX, LOGC, ROWS, false><<<grid, kThreads, smem, stream>>>(p, maps);
+      if (!launched) {
+        if (glue) bfly_fw_kernel<T, KMAX, LOGC, ROWS, false, true><<<grid, kThreads, smem, stream>>>(p, maps);
+        else bfly_fw_kernel<T, KMAX, LOGC, ROWS, false, false><<<grid, kThreads, smem, stream>>>(p, maps);
+      }
     }
     g_launches.fetch_add(1);
     return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;

@@ -187,6 +187,10 @@ template <typename T> struct FwGlue {
   const T* out_diag;
   const float* x_real;
   float* out_real;
+  // gather passes: bit j of (thread + k * threads) becomes bit colbit[j] of the column a thread owns,
+  // chosen so that the lanes of a warp spread over the shared-memory banks on both sides of a
+  // bit-reversal gather (glue_column_bits)
+  uint8_t colbit[16];
   BFLY_HD bool any_in() const { return in_perm != nullptr; }
   BFLY_HD bool any_out() const { return out_perm != nullptr || out_diag != nullptr; }
 };

@@ -158,9 +158,15 @@ struct EmulExec {
       auto permute_rows = [&](const int32_t* perm, const T* diag) {
         const int slots = (C + threads_ - 1) / threads_;
         std::vector<T> v((size_t)threads_ * slots);
+        std::vector<uint32_t> plan((size_t)threads_ * slots);
+        std::vector<int> cnt(threads_);
+        for (int tid = 0; tid < threads_; ++tid)
+          cnt[tid] = tile_permute_plan<T>(p.panel.logC, perm, p.glue.colbit, tid, threads_, plan.data() + (size_t)tid * slots);
         for (int r = 0; r < p.R; ++r) {
-          for (int tid = 0; tid < threads_; ++tid) tile_permute_read<T>(sm.data(), r, p.panel.logC, perm, diag, tid, threads_, v.data() + (size_t)tid * slots);
-          for (int tid = 0; tid < threads_; ++tid) tile_permute_write<T>(sm.data(), r, p.panel.logC, tid, threads_, v.data() + (size_t)tid * slots);
+          for (int tid = 0; tid < threads_; ++tid)
+            tile_permute_read<T>(sm.data(), r, p.panel.logC, diag, plan.data() + (size_t)tid * slots, cnt[tid], v.data() + (size_t)tid * slots);
+          for (int tid = 0; tid < threads_; ++tid)
+            tile_permute_write<T>(sm.data(), r, p.panel.logC, plan.data() + (size_t)tid * slots, cnt[tid], v.data() + (size_t)tid * slots);
         }
       };
       if (p.glue.any_in()) permute_rows(p.glue.in_perm, nullptr);
@@ -171,7 +177,10 @@ struct EmulExec {
           for (int tid = 0; tid < threads_; ++tid)
             tile_store_auto<T>(p.snap[p.g[g].emit - 1], (int64_t)p.S * n, n, (int)n, p.B, stack, row0, p.R, p.panel, pbase, true, sm.data(), tid, threads_);
       }
-      if (p.glue.any_out()) permute_rows(p.glue.out_perm, p.glue.out_diag);
+      if (p.glue.any_out()) {
+        if (p.glue.out_perm) permute_rows(p.glue.out_perm, p.glue.out_diag);
+        else for (int tid = 0; tid < threads_; ++tid) tile_scale_rows<T>(sm.data(), p.R, p.panel.logC, p.glue.out_diag, tid, threads_);
+      }
       if (p.glue.out_real)
         for (int tid = 0; tid < threads_; ++tid)
           tile_store_real(p.glue.out_real, p.out_sB, p.out_sS, p.out_cols, p.B, stack, row0, p.R, p.panel.logC, sm.data(), tid, threads_);
