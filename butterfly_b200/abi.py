@@ -22,6 +22,7 @@ SYMBOLS = (
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
     "bfly_linear_fw_f32", "bfly_linear_bw_f32", "bfly_linear_bw_workspace_bytes", "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
     "bfly_unitary_twiddle_fw", "bfly_unitary_twiddle_bw", "bfly_fw_glue_f32", "bfly_fw_glue_c64",
+    "bfly_selftest_bounded_wait",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -365,6 +366,13 @@ def get_option(name):
 
 def launch_count():
     return int(lib().bfly_launch_count())
+
+
+def selftest_bounded_wait(polls=4096):
+    """``bfly_selftest_bounded_wait``: one warp waits on a barrier that never completes, gives up after `polls` polls."""
+    rc = lib().bfly_selftest_bounded_wait(int(polls), _stream())
+    if rc:
+        raise BflyError(rc, "bfly_selftest_bounded_wait")
 
 
 def device_error():

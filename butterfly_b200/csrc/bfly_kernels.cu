@@ -41,6 +41,29 @@ template <typename T, int KMAX> struct FwOcc {
 // is invalid); read and cleared by bfly_device_error().
 __device__ int g_device_error = 0;
 
+// Self-test of the give-up protocol: a wait on an mbarrier whose bytes never arrive (nothing is
+// ever copied to it), bounded by `limit` polls; when the bound runs out the warp raises the flag
+// exactly as the kernels do and returns.  One warp, no global memory touched but the flag.
+__global__ void bfly_wait_selftest_kernel(int limit) {
+  __shared__ __align__(8) unsigned long long slot;
+  const uint32_t bar = tma_smem(&slot);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    fence_async_smem();
+    mbar_expect_tx(bar, 16);  // the arrival is counted, the 16 bytes never come
+  }
+  __syncwarp();
+  bool ok = false;
+  for (int i = 0; i < limit && !ok; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done) : "r"(bar), "r"(0u) : "memory");
+    ok = done != 0;
+  }
+  if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) atomicExch(&g_device_error, 1);
+}
+
 // Device address of the flag on the current device (looked up once per device).
 static int device_error_ptr(int** out) {
   static std::mutex mu;
@@ -827,6 +850,14 @@ int bfly_set_option(const char* name, int value) { return set_option(name, value
 int bfly_get_option(const char* name, int* value) { return get_option(name, value); }
 int bfly_cuda_version(void) { return CUDA_VERSION; }
 int64_t bfly_launch_count(void) { return g_launches.load(); }
+
+int bfly_selftest_bounded_wait(int polls, void* stream) {
+  if (polls < 1 || polls > (1 << 20)) return BFLY_E_ARG;
+  bfly::bfly_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(polls);
+  if (cudaGetLastError() != cudaSuccess) return BFLY_E_CUDA;
+  g_launches.fetch_add(1);
+  return BFLY_OK;
+}
 
 int bfly_device_error(void) {
   int flag = 0;

@@ -259,6 +259,12 @@ int64_t bfly_launch_count(void);
  * reference; meant for tests and for hosts that want to double-check a run. */
 int bfly_device_error(void);
 
+/* Self-test of that protocol, for tests: launches one warp that waits, for at most `polls` polls
+ * (1 .. 2^20), on a barrier whose data never arrives, gives up, raises the flag and returns.  After
+ * it bfly_device_error() returns 1 once and the device is as usable as before.  No counterpart in
+ * the reference. */
+int bfly_selftest_bounded_wait(int polls, void* stream);
+
 /* Per-kernel timing for benchmarks.  While enabled, every launch is bracketed by a pair of
  * CUDA events on its stream.  bfly_profile_collect waits for the recorded launches, adds
  * their count and device time into launches[id] / total_ms[id] (ids below; n_ids entries each)

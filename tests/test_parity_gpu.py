@@ -396,6 +396,20 @@ def test_operator_semantics(dev, oracle_mod):
         assert torch.equal(y_all[:, s:s + 1], y_one)
 
 
+def test_bounded_wait_gives_up_and_reports(abi, dev, oracle_mod):
+    """A wait that cannot complete runs out of its bound, raises the device flag and returns; the
+    host reads the status once, and the device keeps working."""
+    assert abi.device_error() == 0
+    abi.selftest_bounded_wait(4096)
+    assert abi.device_error() == 1
+    assert abi.device_error() == 0   # read and cleared
+    tw = torch.randn(1, 1, 9, 256, 2, 2) / 2 ** 0.5
+    x = torch.randn(16, 1, 512)
+    y, rc = abi.fw(tw.to(dev), x.to(dev), True)
+    assert rc == 0 and rel_err(y, oracle_mod.multiply_fw(tw, x, True)) < TOL
+    assert abi.device_error() == 0
+
+
 def test_forward_without_grad_mode_saves_nothing(dev):
     """A forward under torch.no_grad() on parameters that require grad is the plain forward: the
     same launches and no snapshot planes, where the recording forward of a two-block product
