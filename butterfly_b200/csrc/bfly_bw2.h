@@ -29,7 +29,9 @@ template <typename T, int KW> struct AccStore {
   static constexpr int N = BwTwn<KW>::value;               // accumulators (elements of T) per sub-group
   static constexpr int NF = N * (int)(sizeof(T) / 4);      // 32-bit columns per sub-group
   // a thread's 128 columns: accumulators of sub-group j at j * NF, its twiddles at kTwBase + j * NF
+  // (four sub-groups of 16 columns for float, two of 32 for complex)
   static constexpr int kTwBase = 64;
+  static_assert(NF <= 32, "a sub-group's accumulators must fit a quarter of the thread's columns");
 #if defined(__CUDA_ARCH__)
   uint32_t taddr;  // TMEM address (lane << 16 | column) of this thread's first column
   __device__ __forceinline__ void ld_tw(int j, T* tw) const { ld_at(kTwBase + j * NF, tw); }
@@ -39,7 +41,16 @@ template <typename T, int KW> struct AccStore {
   __device__ __forceinline__ void ld_at(int col, T* acc) const {
     float* r = reinterpret_cast<float*>(acc);
     const uint32_t a = taddr + (uint32_t)col;
-    if constexpr (NF == 16) {
+    if constexpr (NF == 32) {
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]),
+            "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]), "=f"(r[16]),
+            "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]), "=f"(r[24]),
+            "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+          : "r"(a) : "memory");
+    } else if constexpr (NF == 16) {
       asm volatile(
           "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
           : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]),
@@ -58,7 +69,15 @@ template <typename T, int KW> struct AccStore {
   __device__ __forceinline__ void st_at(int col, const T* acc) const {
     const float* r = reinterpret_cast<const float*>(acc);
     const uint32_t a = taddr + (uint32_t)col;
-    if constexpr (NF == 16) {
+    if constexpr (NF == 32) {
+      asm volatile(
+          "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+          "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+          ::"r"(a), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]), "f"(r[8]), "f"(r[9]),
+            "f"(r[10]), "f"(r[11]), "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15]), "f"(r[16]), "f"(r[17]), "f"(r[18]),
+            "f"(r[19]), "f"(r[20]), "f"(r[21]), "f"(r[22]), "f"(r[23]), "f"(r[24]), "f"(r[25]), "f"(r[26]), "f"(r[27]),
+            "f"(r[28]), "f"(r[29]), "f"(r[30]), "f"(r[31]) : "memory");
+    } else if constexpr (NF == 16) {
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
           ::"r"(a), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]), "f"(r[8]), "f"(r[9]),

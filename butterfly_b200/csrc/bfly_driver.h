@@ -40,6 +40,7 @@ struct Options {
   int fw_logcmax = -1;  // generic forward: widest panel (log2 columns) of a pass
   int bw_rows = -1;     // backward: rows per batch
   int bw_maxsg = -1;    // backward: sub-groups per phase
+  int bw_c64_kw2 = 1;   // complex64 radix-2 backward on 2-stage sub-groups (tensor-memory kernel) for n >= 1024
   int autograd_save = -1;  // torch autograd operator: keep the forward's snapshots for the backward
 };
 struct OptionName { const char* name; const char* env; int Options::*field; };
@@ -51,6 +52,7 @@ inline const OptionName* option_names(int* count) {
       {"fw2_ctas", "BFLY_FW2_CTAS", &Options::fw2_ctas},
       {"fw_rows", "BFLY_FW_ROWS", &Options::fw_rows}, {"fw_logcmax", "BFLY_FW_LOGCMAX", &Options::fw_logcmax},
       {"bw_rows", "BFLY_BW_ROWS", &Options::bw_rows}, {"bw_maxsg", "BFLY_BW_MAXSG", &Options::bw_maxsg},
+      {"bw_c64_kw2", "BFLY_BW_C64_KW2", &Options::bw_c64_kw2},
       {"autograd_save", "BFLY_AUTOGRAD_SAVE", &Options::autograd_save},
   };
   *count = (int)(sizeof(names) / sizeof(names[0]));
@@ -107,7 +109,13 @@ template <> struct KernelCfg<cf> {
   static constexpr int kThreads = 256;
   // one-stage sub-groups for radix-2 products; a radix-4 factor needs the 2-bit window, and the
   // 16 complex accumulators per sub-group leave room for two sub-groups per phase
-  static int bw_kw(int log_n, bool base4) { return (base4 && log_n >= 2) ? 2 : 1; }
+  // Full panels of 1024 complex columns (n >= 1024) also take the 2-bit window for radix-2 products:
+  // phases of two 2-stage sub-groups on the kernel that keeps twiddles and accumulators in tensor
+  // memory (4 stages per phase, two CTAs per SM) measure faster than 10 one-stage sub-groups.
+  static int bw_kw(int log_n, bool base4) {
+    if (base4 && log_n >= 2) return 2;
+    return (log_n >= 10 && options().bw_v2 != 0 && options().bw_c64_kw2 != 0) ? 2 : 1;
+  }
   static int bw_max_sg(int kw) { return kw == 2 ? 2 : 10; }
 };
 

@@ -525,7 +525,7 @@ struct CudaExec {
   int num_sms() const { return dev.sms; }
   int threads() const { return kThreads; }
   static bool use_tma() { return options().tma != 0; }
-  bool has_bw2(size_t elem_size, int kw) const { return options().bw_v2 != 0 && elem_size == 4 && kw == 2; }
+  bool has_bw2(size_t /*elem_size*/, int kw) const { return options().bw_v2 != 0 && kw == 2; }
 
   template <typename T, int KW, int LOGC> int launch_bw2(const BwParams<T>& p_in) {
     BwParams<T> p = p_in;
@@ -691,7 +691,8 @@ struct CudaExec {
     return launch_bw<float, 1, 10, 0, 0>(p);
   }
   int run_bw(const BwParams<cf>& p, int KW) {
-    if (KW == 2) return p.nsg <= 2 ? launch_bw<cf, 2, 2, 0, 0>(p) : BFLY_E_UNSUPPORTED;  // radix-4 factors
+    if (p.v2 && KW == 2 && p.nsg <= 2) return p.panel.logC == 10 ? launch_bw2<cf, 2, 10>(p) : launch_bw2<cf, 2, 0>(p);
+    if (KW == 2) return p.nsg <= 2 ? launch_bw<cf, 2, 2, 0, 0>(p) : BFLY_E_UNSUPPORTED;  // radix-4 factors, narrow panels
     if (KW != 1) return BFLY_E_UNSUPPORTED;
     if (p.panel.logC == 9) {
       if (p.nsg >= 9 && p.Rb == 4) return launch_bw<cf, 1, 10, 9, 4>(p);

@@ -214,9 +214,29 @@ def test_backward_phase_plan_sizes(emul):
     # n = 4096, two blocks: 24 stages = three phases of 8 -> two (B,S,n) float snapshots
     assert emul.bfly_emul_bw_plan(0, 0, 16384, 1, 12, 2, 1, ctypes.byref(ws)) == 3
     assert ws.value == 2 * 16384 * 4096 * 4 + 24 * 2048 * 16  # two snapshots + re-ordered twiddles of the forward pass
-    # complex: panels of 512 columns, up to 10 stages per phase
+    # complex, n >= 1024: panels of 1024 columns, two 2-stage sub-groups (4 stages) per phase
     nph = emul.bfly_emul_bw_plan(1, 0, 8192, 1, 11, 1, 1, ctypes.byref(ws))
-    assert nph == 2 and ws.value == 8192 * 2048 * 8
+    assert nph == 3 and ws.value == 2 * 8192 * 2048 * 8
+    # complex, n < 1024: panels of 512 columns, up to 10 one-stage sub-groups per phase
+    nph = emul.bfly_emul_bw_plan(1, 0, 64, 1, 9, 2, 1, ctypes.byref(ws))
+    assert nph == 2 and ws.value == 64 * 512 * 8
+    with emul_option(emul, "bw_c64_kw2", 0):
+        nph = emul.bfly_emul_bw_plan(1, 0, 8192, 1, 11, 1, 1, ctypes.byref(ws))
+        assert nph == 2 and ws.value == 8192 * 2048 * 8
+
+
+def test_complex_backward_on_two_stage_subgroups(emul, oracle_mod):
+    """complex64 products of n >= 1024 run their backward phases on the tensor-memory kernel's step
+    routines with 2-bit windows (two sub-groups of two stages); emulated here against the oracle."""
+    torch.manual_seed(13)
+    for log_n, nb, B, S, inc in ((10, 1, 9, 1, True), (11, 2, 6, 1, False), (12, 1, 5, 2, True)):
+        n = 1 << log_n
+        tw = torch.randn(S, nb, log_n, n // 2, 2, 2, dtype=torch.complex64) / 2 ** 0.5
+        x = torch.randn(B, S, n - 5, dtype=torch.complex64)
+        g = torch.randn(B, S, n - 9, dtype=torch.complex64)
+        d2, _, dx = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, 256)
+        dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
+        assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5, (log_n, nb)
 
 
 def test_twiddle_stacks_beyond_32bit_offsets_are_refused(emul):
