@@ -231,6 +231,95 @@ int drive_fw2(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int
   return ex.run_fw2(p, ctas);
 }
 
+// Rows wider than 4096 floats on the packed-pair kernel: the stages are cut into passes whose bits
+// fit a panel of 4096 columns that the kernel sees as a row of its own -- the low 12 bits
+// (contiguous panels), or the top 7 bits with 32-column blocks (bits 0-4) riding along -- one
+// launch per pass, in place on `work` between the first read of x and the last write.  One real
+// stack, full-width input.  Returns kFw2Declined when the shape or the stage list does not fit.
+struct Fw2Pass { int t0, t1; Panel panel; };
+inline std::vector<Fw2Pass> plan_fw2_passes(const std::vector<Stage>& st, int t0, int t1, int log_n) {
+  std::vector<Fw2Pass> out;
+  const int top = log_n - 7;  // lowest bit of the strided panel
+  int t = t0;
+  while (t < t1) {
+    if (st[t].radix != 2) return {};
+    bool low = st[t].bit <= 11, high = st[t].bit >= top;
+    if (!low && !high) return {};
+    int e = t + 1;
+    while (e < t1 && st[e].radix == 2) {
+      const bool l2 = low && st[e].bit <= 11, h2 = high && st[e].bit >= top;
+      if (!l2 && !h2) break;
+      low = l2; high = h2;
+      ++e;
+    }
+    Fw2Pass ps;
+    ps.t0 = t; ps.t1 = e;
+    ps.panel = low ? Panel{12, 12, 12, log_n - 12} : Panel{12, 5, top, log_n - 12};
+    out.push_back(ps);
+    t = e;
+  }
+  return out;
+}
+
+template <typename E>
+int drive_fw2_view(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int t1, const std::vector<int>& cuts,
+                   float* const* snaps, const float* tw2, const float* x, int64_t x_sB, int x_cols, float* out, int64_t out_sB,
+                   float* scratch, int64_t scratch_sB, void* pack_ws, size_t pack_bytes) {
+  if (q.base4 || !tw2 || !pack_ws || !fw2_enabled() || q.S != 1 || q.log_n <= kFw2MaxLogN || q.log_n > 19) return kFw2Declined;
+  const int64_t n = (int64_t)1 << q.log_n;
+  if (x_cols < n || (int)cuts.size() > kFw2MaxSnap) return kFw2Declined;
+  const std::vector<Fw2Pass> passes = plan_fw2_passes(st, t0, t1, q.log_n);
+  if (passes.empty()) return kFw2Declined;
+  float* work = out; int64_t work_sB = out_sB;
+  if (!work) { work = scratch; work_sB = scratch_sB; }
+  if (passes.size() > 1 && !work) return kFw2Declined;
+  // plan everything before the first launch: a pass that does not fit must not leave half a product behind
+  std::vector<Fw2Params> launches;
+  for (size_t pi = 0; pi < passes.size(); ++pi) {
+    const Fw2Pass& ps = passes[pi];
+    std::vector<Stage> local(st);
+    for (int k = ps.t0; k < ps.t1; ++k) {
+      const int b = st[k].bit;
+      local[k].bit = b < ps.panel.lseg ? b : b - ps.panel.pb + ps.panel.lseg;
+      if (local[k].bit < 0 || local[k].bit > 11) return kFw2Declined;
+    }
+    std::vector<Fw2Group> groups;
+    if (!plan_fw2_groups(local, ps.t0, ps.t1, cuts, 12, groups)) return kFw2Declined;
+    Fw2Params p;
+    std::memset(&p, 0, sizeof(p));
+    int64_t stk[2];
+    twiddle_stack_sizes(q, stk);
+    p.tw = tw2; p.tw_stack = stk[0];
+    p.view = 1; p.view_row = (int)n; p.panel = ps.panel;
+    p.B = q.B; p.S = 1 << ps.panel.npanels_log; p.log_n = 12;
+    const int ctas = options().fw2_ctas == 1 ? 1 : 2;
+    p.P = 1;
+    p.Rw = fw2_rows_per_thread(q.B, p.S, p.P, ctas * ex.num_sms(), ctas == 1 ? 14 : 7);
+    p.R = p.P * p.Rw;
+    p.packed = static_cast<float*>(pack_ws);
+    p.packed_stack = (int64_t)groups.back().pk_off + (int64_t)groups.back().nst * 8 * (4096 / 16);
+    if ((size_t)p.packed_stack * p.S * 16 > pack_bytes) return kFw2Declined;
+    const bool first = pi == 0, last = pi + 1 == passes.size();
+    p.x = first ? x : work; p.x_sB = first ? x_sB : work_sB; p.x_sS = 0; p.x_cols = 4096;
+    p.out = last ? out : work; p.out_sB = last ? out_sB : work_sB; p.out_sS = 0; p.out_cols = 4096;
+    for (int i = 0; i < kFw2MaxSnap; ++i) p.snap[i] = (snaps && i < (int)cuts.size()) ? snaps[i] : nullptr;
+    p.ngroups = (int)groups.size();
+    for (int g = 0; g < p.ngroups; ++g) {
+      p.g[g] = groups[g];
+      if (groups[g].sync == 2 || (groups[g].emit && !groups[g].local)) p.cta_syncs = 1;
+    }
+    if (!groups.back().local) p.cta_syncs = 1;
+    launches.push_back(p);
+  }
+  const int ctas = options().fw2_ctas == 1 ? 1 : 2;
+  for (size_t pi = 0; pi < launches.size(); ++pi) {
+    const int rc = ex.run_fw2(launches[pi], ctas);
+    if (rc == kFw2Declined) return pi == 0 ? kFw2Declined : BFLY_E_UNSUPPORTED;
+    if (rc != BFLY_OK) return rc;
+  }
+  return BFLY_OK;
+}
+
 // Run stages [t0, t1) of the product with the row-owner forward kernel.  `cuts` lists the
 // stage indices after which a snapshot is written (slot i -> snaps[i]); `out` may be null when
 // only snapshots are wanted.  Rows that fit one SM's shared memory run in one pass; wider rows
@@ -254,6 +343,10 @@ int drive_fw_range(E& ex, const Problem& q, const std::vector<Stage>& st, int t0
     const int rc2 = drive_fw2(ex, q, st, t0, t1, cuts, snaps, tw2, x, x_sB, x_sS, x_cols, out, out_sB, out_sS, out_cols,
                               pack_ws, pack_bytes);
     if (rc2 != kFw2Declined) return rc2;
+    // rows wider than the kernel's tile: its panel view, pass by pass
+    const int rc3 = drive_fw2_view(ex, q, st, t0, t1, cuts, snaps, tw2, x, x_sB, x_cols, out, out_sB, scratch, scratch_sB,
+                                   pack_ws, pack_bytes);
+    if (rc3 != kFw2Declined) return rc3;
    }
   }
   const int lc = fw_pass_logc<T>(q.log_n);

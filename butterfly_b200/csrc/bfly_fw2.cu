@@ -38,6 +38,24 @@ static bool fw2_describe(CUtensorMap* map, const void* ptr, int64_t sB, int64_t 
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same view of the 4096-column panels of wider rows (Fw2Params::view): dim1 runs over the
+// panel's 128 column blocks (`blk_stride` floats apart), dim2 over the panels (`panel_stride`).
+static bool fw2_describe_view(CUtensorMap* map, const void* ptr, int64_t sB, int64_t blk_stride, int64_t panel_stride,
+                              int npanels, int B, int rows) {
+  EncodeTiledFn enc = tma_encoder();
+  if (!enc || !ptr || B < 1 || rows < 1 || rows > 256) return false;
+  if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || sB <= 0 || sB % 4 != 0) return false;
+  const cuuint64_t dims[4] = {32, 128, (cuuint64_t)npanels, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)(blk_stride * 4), (cuuint64_t)(panel_stride * 4), (cuuint64_t)(sB * 4)};
+  const cuuint32_t box[4] = {32, 16, 1, (cuuint32_t)rows};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16 != 0 || strides[i] >= ((cuuint64_t)1 << 40)) return false;
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 __device__ __forceinline__ void tma_load_box4(uint32_t dst, const CUtensorMap* map, uint32_t bar, int blk, int stack, int row) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -262,6 +280,21 @@ int fw2_launch(const Fw2Params& p_in, int ctas_per_sm, int sms, cudaStream_t str
   std::memset(&maps, 0, sizeof(maps));
   const int xc = std::min(p.x_cols, n);
   if (!p.packed || reinterpret_cast<uintptr_t>(p.packed) % 16 != 0) return kFw2Declined;
+  if (p.view) {
+    // panels of wider rows: contiguous panels follow each other, strided ones interleave block by block
+    const bool contig = p.panel.lseg == p.panel.logC;
+    const int64_t blk = contig ? 32 : ((int64_t)1 << p.panel.pb), pan = contig ? n : 32;
+    if (!contig && p.panel.lseg != 5) return kFw2Declined;
+    if (p.bias) return kFw2Declined;
+    if (!fw2_describe_view(&maps.in, p.x, p.x_sB, blk, pan, p.S, p.B, p.Rw)) return kFw2Declined;
+    p.x_stack = 1;
+    p.has_out = p.out != nullptr;
+    p.out_cols = n;
+    if (p.has_out && !fw2_describe_view(&maps.out, p.out, p.out_sB, blk, pan, p.S, p.B, p.Rw)) return kFw2Declined;
+    p.out_stack = 1;
+    for (int i = 0; i < kFw2MaxSnap; ++i)
+      if (p.snap[i] && !fw2_describe_view(&maps.snap[i], p.snap[i], p.view_row, blk, pan, p.S, p.B, p.Rw)) return kFw2Declined;
+  } else {
   if (!fw2_describe(&maps.in, p.x, p.x_sB, p.x_sS, xc, p.B, p.S, p.Rw)) return kFw2Declined;
   p.x_stack = (p.S > 1 && p.x_sS != 0) ? 1 : 0;
   p.has_out = p.out != nullptr;
@@ -273,6 +306,7 @@ int fw2_launch(const Fw2Params& p_in, int ctas_per_sm, int sms, cudaStream_t str
   }
   for (int i = 0; i < kFw2MaxSnap; ++i)
     if (p.snap[i] && !fw2_describe(&maps.snap[i], p.snap[i], (int64_t)p.S * n, n, n, p.B, p.S, p.Rw)) return kFw2Declined;
+  }
   const size_t smem = fw2_smem_bytes(p);
   if (smem > (size_t)(ctas_per_sm == 1 ? 227 : 113) * 1024) return kFw2Declined;
   const int64_t entries = fw2_pack_entries(p);

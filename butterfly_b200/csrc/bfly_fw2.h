@@ -152,9 +152,19 @@ struct Fw2Params {
   // output positions below bias_len (the output buffer is then one (B, S * n) matrix)
   const float* bias;
   int bias_len;
+  // Panel view (rows wider than 4096 columns, one real stack): the launch's S "stacks" are the
+  // column panels of `panel` (4096 columns each: contiguous, or 32-column blocks at a power-of-two
+  // stride), log_n = 12 and the stage bits are panel-local.  Tensors are then addressed as
+  // row * sB + fw2_view_col(panel index, local column); snapshots are rows of view_row floats.
+  int view;
+  int view_row;
+  Panel panel;
   int ngroups;
   Fw2Group g[kFw2MaxGroups];
 };
+
+// Real column of local column c of panel pi in a panel view.
+BFLY_HD int fw2_view_col(const Fw2Params& p, int pi, int c) { return p.panel.col(p.panel.base(pi), c); }
 
 // Cut stages [t0, t1) (radix 2 only) into groups.  `cuts`: stage indices after which a snapshot
 // is written (slot i).  Returns false when the range does not qualify.
@@ -256,13 +266,15 @@ BFLY_HD int fw2_unit_col(const Fw2Group& g, int u) {
 // holds (t00, t11, t01, t10) of the block of register k.
 BFLY_HD void fw2_pack_entry(const Fw2Params& p, const Fw2Group& g, int stack, int u, int s, int j, float* out4) {
   const int b = g.contig ? 1 : g.b;
-  const int c0 = fw2_unit_col(g, u);
+  const int c0 = p.view ? fw2_view_col(p, stack, fw2_unit_col(g, u)) : fw2_unit_col(g, u);
   const int kind = fw2_variant_kind(g.variant, s);
-  const float* twp = p.tw + (int64_t)stack * p.tw_stack + g.tw_off[s];
+  const float* twp = p.tw + (p.view ? (int64_t)0 : (int64_t)stack * p.tw_stack) + g.tw_off[s];
   if (kind < 3) {
-    const int pp = j >> 1, half = j & 1, q = b + kind;
+    const int pp = j >> 1, half = j & 1;
     const int m0 = ((pp >> kind) << (kind + 1)) | (pp & ((1 << kind) - 1));
-    const int col = c0 | (m0 << b);
+    // in a panel view the local column and the local stage bit translate to the real ones first
+    const int col = p.view ? fw2_view_col(p, stack, fw2_unit_col(g, u) | (m0 << b)) : (c0 | (m0 << b));
+    const int q = p.view ? p.panel.global_bit(b + kind) : b + kind;
     const int i0 = ((col >> (q + 1)) << q) | (col & ((1 << q) - 1));  // column bit q deleted
     const float* A = twp + (size_t)i0 * 4;
     out4[0] = A[2 * half]; out4[1] = A[4 + 2 * half]; out4[2] = A[2 * half + 1]; out4[3] = A[4 + 2 * half + 1];
@@ -450,8 +462,11 @@ BFLY_HD size_t fw2_tile_bytes(const Fw2Params& p) { return ((size_t)p.R * sizeof
 // the tile, then one mbarrier per warp and the give-up flag
 BFLY_HD size_t fw2_smem_bytes(const Fw2Params& p) { return fw2_tile_bytes(p) + 8 * 8 + 16; }
 // bytes of the re-ordered twiddle copy (same size as the twiddle tensor): 0 when the shape does
-// not take this kernel
+// not take this kernel.  Rows wider than 4096 columns (one stack, up to 2^19) run pass by pass on
+// panels; a pass holds at most 24 stages (the low 12 bits at the end of one block and the start of
+// the next) and re-uses the space.
 inline size_t fw2_packed_bytes(int S, int log_n, int nblocks) {
+  if (log_n > kFw2MaxLogN && log_n <= 19 && S == 1) return (size_t)24 * ((size_t)8 << log_n);
   if (log_n < kFw2MinLogN || log_n > kFw2MaxLogN) return 0;
   return (size_t)S * nblocks * log_n * ((size_t)8 << log_n);
 }

@@ -36,6 +36,7 @@ struct EmulExec {
     if (!fw2) return kFw2Declined;
     Fw2Params p = p_in;
     const int n = 1 << p.log_n;
+    if (p.view && ((p.panel.lseg != p.panel.logC && p.panel.lseg != 5) || p.bias)) return kFw2Declined;
     if (p.x_cols % 32 != 0 && p.x_cols < n) return kFw2Declined;  // what the TMA descriptors would refuse
     if (p.out && p.out_cols % 32 != 0) return kFw2Declined;
     p.has_out = p.out != nullptr;
@@ -50,8 +51,10 @@ struct EmulExec {
           float& t = tile[fw2_tile_index(p.R, r, c)];
           const int row = row0 + r;
           const bool in = row < p.B && c < cols;
-          if (load) t = in ? src[(int64_t)row * sB + (int64_t)stack * sS + c] : 0.f;
-          else if (in) dst[(int64_t)row * sB + (int64_t)stack * sS + c] = t;
+          // a panel view addresses (panel, local column) -> real column of the one real stack
+          const int64_t at = p.view ? (int64_t)row * sB + fw2_view_col(p, stack, c) : (int64_t)row * sB + (int64_t)stack * sS + c;
+          if (load) t = in ? src[at] : 0.f;
+          else if (in) dst[at] = t;
         }
     };
     for (int64_t t = 0; t < ntiles; ++t) {
@@ -64,7 +67,7 @@ struct EmulExec {
           if (tid & 1) fw2_group_dispatch<true>(p, p.g[gi], tile.data(), tid, T);  // both row-loop forms
           else fw2_group_dispatch<false>(p, p.g[gi], tile.data(), tid, T);
         }
-        if (p.g[gi].emit) box_copy(false, nullptr, p.snap[p.g[gi].emit - 1], (int64_t)p.S * n, n, n, stack, row0);
+        if (p.g[gi].emit) box_copy(false, nullptr, p.snap[p.g[gi].emit - 1], p.view ? (int64_t)p.view_row : (int64_t)p.S * n, n, n, stack, row0);
       }
       if (p.has_out && p.bias)  // the store epilogue of the device kernel
         for (int r = 0; r < p.R; ++r)
