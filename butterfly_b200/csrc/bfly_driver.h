@@ -41,6 +41,7 @@ struct Options {
   int bw_rows = -1;     // backward: rows per batch
   int bw_maxsg = -1;    // backward: sub-groups per phase
   int bw_c64_kw2 = 1;   // complex64 radix-2 backward on 2-stage sub-groups (tensor-memory kernel) for n >= 1024
+  int bw3_min_rows = 160;  // fewest rows per CTA for which a plain backward phase takes the packed-pair kernel
   int autograd_save = -1;  // torch autograd operator: keep the forward's snapshots for the backward
 };
 struct OptionName { const char* name; const char* env; int Options::*field; };
@@ -53,6 +54,7 @@ inline const OptionName* option_names(int* count) {
       {"fw_rows", "BFLY_FW_ROWS", &Options::fw_rows}, {"fw_logcmax", "BFLY_FW_LOGCMAX", &Options::fw_logcmax},
       {"bw_rows", "BFLY_BW_ROWS", &Options::bw_rows}, {"bw_maxsg", "BFLY_BW_MAXSG", &Options::bw_maxsg},
       {"bw_c64_kw2", "BFLY_BW_C64_KW2", &Options::bw_c64_kw2},
+      {"bw3_min_rows", "BFLY_BW3_MIN_ROWS", &Options::bw3_min_rows},
       {"autograd_save", "BFLY_AUTOGRAD_SAVE", &Options::autograd_save},
   };
   *count = (int)(sizeof(names) / sizeof(names[0]));
@@ -624,7 +626,10 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
           b.vec_x = vec_ok<T>(b.xin, b.xin_sB, b.xin_sS);
           b.vec_g = vec_ok<T>(b.gin, b.gin_sB, b.gin_sS);
           b.vec_o = vec_ok<T>(b.gout, b.gout_sB, b.gout_sS);
-          const int rc3 = ex.run_bw3(p3);
+          // Its per-CTA set-up (pairing the twiddles into tensor memory) is amortised over the CTA's
+          // rows: with few rows per CTA the scalar tensor-memory kernel is faster (measured: equal
+          // from ~200 rows per CTA up, 10-25 % faster at 50 and fewer).
+          const int rc3 = rows3 >= o.bw3_min_rows ? ex.run_bw3(p3) : kFw2Declined;
           if (rc3 == BFLY_OK) continue;
           if (rc3 != kFw2Declined) return rc3;
         }

@@ -100,6 +100,11 @@ def test_reference_test_files_pass_unchanged(shim, test_file, selection):
     path = os.path.join(oracle.REF_PKG, "tests", test_file)
     out = _run(shim, '''
         import pytest
+        # The reference's tests draw unseeded inputs and hold float32 twiddle gradients of un-normalised
+        # products (sums of cancelling terms of magnitude ~60) to atol 1e-5 against another summation
+        # order; about one seed in ten lands an entry just outside, whatever the implementation.  A fixed
+        # seed makes the run repeatable.
+        torch.manual_seed(0)
         args = [%r, "-q", "-p", "no:cacheprovider"]
         if %r:
             args += ["-k", %r]
