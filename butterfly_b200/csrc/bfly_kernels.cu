@@ -17,6 +17,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <mutex>
+#include <tuple>
 #include <vector>
 
 #include "../../include/bfly.h"
@@ -502,19 +503,37 @@ static int device_info(DeviceInfo& out) {
   return BFLY_OK;
 }
 
+// Function attributes of a kernel instance are set once per (instance, device), and again only
+// when a launch needs more dynamic shared memory than any before it: the launch path only looks
+// the pair up.
 template <typename K>
 static int set_smem(K kernel, size_t bytes) {
-  // the attribute is per device and cheap to set; set it on every launch that needs it
+  struct Entry { const void* fn; int dev; size_t bytes; };
+  static std::mutex mu;
+  static std::vector<Entry> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return BFLY_E_NODEVICE;
+  const void* fn = reinterpret_cast<const void*>(kernel);
+  std::lock_guard<std::mutex> lk(mu);
+  Entry* e = nullptr;
+  for (auto& k : done)
+    if (k.fn == fn && k.dev == dev) e = &k;
+  if (e && e->bytes >= bytes) return BFLY_OK;
   if (bytes > 48 * 1024) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
       cudaGetLastError();
       return BFLY_E_CUDA;
     }
   }
-  // ask for the largest shared-memory carve-out so that two CTAs of up to 113 KB share an SM
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
-    cudaGetLastError();
-    return BFLY_E_CUDA;
+  if (!e) {
+    // ask for the largest shared-memory carve-out so that two CTAs of up to 113 KB share an SM
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+      cudaGetLastError();
+      return BFLY_E_CUDA;
+    }
+    done.push_back(Entry{fn, dev, bytes});
+  } else {
+    e->bytes = bytes;
   }
   return BFLY_OK;
 }
