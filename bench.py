@@ -245,6 +245,20 @@ def _events_ms(fn, iters, warm):
     return a.elapsed_time(b) / iters
 
 
+def _graph_us_per_call(fn, iters=200):
+    """Device time of one operator call replayed from a CUDA graph (no host work per call)."""
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return _events_ms(graph.replay, iters, 20) * 1e3
+
+
 def _host_us_per_call(fn, iters=200):
     """Host time of one operator call (enqueue only: the stream is drained before and after)."""
     import torch
@@ -285,6 +299,7 @@ def measure_config(bb, configs, name, dev, peak, make=None, iters=5, warm=3, ref
                    fw_bw_frac_of_hbm_peak=(fwb + bwb) / (fw_ms + bw_ms) / 1e6 / peak)
     else:
         out["fw_host_us_per_call"] = _host_us_per_call(fw)  # latency-bound case: the launch path matters
+        out["fw_graph_replay_us"] = _graph_us_per_call(fw)  # the same call captured once into a CUDA graph
     if ref_ops is not None and not d.get("base4"):
         n = d["n"]
         rfw = lambda: ref_ops.butterfly_multiply_fw(tw, x, inc, n)

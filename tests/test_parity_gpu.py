@@ -566,3 +566,33 @@ def test_against_reference_cuda_extension(dev, oracle_mod, name):
     # both twiddle gradients are float sums of thousands of terms in different orders: compare at the
     # accuracy such sums have
     assert rel_err(d_tw, dtr) < 2e-5
+
+
+def test_operators_capture_into_a_cuda_graph(dev, oracle_mod):
+    """The operators only enqueue work on the current stream (descriptor encoding is host work, scratch
+    comes from torch's allocator), so a forward + backward captures into a CUDA graph and replays on
+    new data in the same buffers."""
+    import butterfly_b200 as bb
+    torch.manual_seed(17)
+    for dtype, log_n, nb, B in ((torch.float32, 10, 2, 256), (torch.complex64, 10, 1, 64)):
+        n = 1 << log_n
+        tw = (torch.randn(1, nb, log_n, n // 2, 2, 2, dtype=dtype) / 2 ** 0.5).to(dev)
+        x = torch.randn(B, 1, n, dtype=dtype, device=dev)
+        g = torch.randn(B, 1, n, dtype=dtype, device=dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):  # warm-up outside the capture (lazy initialisation, attributes)
+            bb.butterfly_multiply_fw(tw, x, True)
+            bb.butterfly_multiply_bw(tw, x, g, True)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y = bb.butterfly_multiply_fw(tw, x, True)
+            d_tw, d_x = bb.butterfly_multiply_bw(tw, x, g, True)
+        x.copy_(torch.randn(B, 1, n, dtype=dtype))
+        g.copy_(torch.randn(B, 1, n, dtype=dtype))
+        graph.replay()
+        torch.cuda.synchronize()
+        yr = oracle_mod.multiply_fw(tw.cpu(), x.cpu(), True)
+        dtr, dxr = oracle_mod.multiply_bw(tw.cpu(), x.cpu(), g.cpu(), True)
+        assert rel_err(y, yr) < TOL and rel_err(d_x, dxr) < TOL and rel_err(d_tw, dtr) < TOL
