@@ -22,7 +22,7 @@ SYMBOLS = (
     "bfly4_bw_f32", "bfly_launch_count", "bfly_profile_enable", "bfly_profile_collect", "bfly_bw_f32_noalloc",
     "bfly_linear_fw_f32", "bfly_linear_bw_f32", "bfly_linear_bw_workspace_bytes", "bfly_device_error", "bfly_set_option", "bfly_get_option", "bfly4_fw_c64", "bfly4_bw_c64", "bfly_fw_f32_saving", "bfly_fw_c64_saving", "bfly_bw_f32_saved", "bfly_bw_c64_saved",
     "bfly_unitary_twiddle_fw", "bfly_unitary_twiddle_bw", "bfly_fw_glue_f32", "bfly_fw_glue_c64",
-    "bfly_selftest_bounded_wait",
+    "bfly_selftest_bounded_wait", "bfly_device_error_async",
 )
 
 NOALLOC_SCRATCH_BYTES = 32 << 20
@@ -373,6 +373,15 @@ def selftest_bounded_wait(polls=4096):
     rc = lib().bfly_selftest_bounded_wait(int(polls), _stream())
     if rc:
         raise BflyError(rc, "bfly_selftest_bounded_wait")
+
+
+def device_error_async(host_flag):
+    """``bfly_device_error_async``: enqueue a copy of the give-up flag into `host_flag` (a pinned int32 tensor of
+    one element) on the current stream; read it after the next synchronisation."""
+    assert host_flag.dtype == torch.int32 and host_flag.numel() == 1 and not host_flag.is_cuda
+    rc = lib().bfly_device_error_async(ctypes.c_void_p(host_flag.data_ptr()), _stream())
+    if rc:
+        raise BflyError(rc, "bfly_device_error_async")
 
 
 def device_error():

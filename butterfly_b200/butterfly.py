@@ -168,6 +168,12 @@ class Butterfly(nn.Module):
             self.twiddle *= scale ** (1.0 / (self.twiddle.shape[1] * self.twiddle.shape[2]))
         return self
 
+    def diagonal_multiply_(self, diagonal, diag_first):
+        """Fold a diagonal into this (single-stack, bias-free) layer in place: input -> diagonal -> butterfly when
+        diag_first, else input -> butterfly -> diagonal (torch_butterfly/butterfly.py:181-190 of the reference)."""
+        from .combine import diagonal_butterfly
+        return diagonal_butterfly(self, diagonal, diag_first, inplace=True)
+
     def to_base4(self):
         """The same matrix as a ButterflyBase4 layer (pairs of factors fused into 4x4 blocks)."""
         with torch.no_grad():

@@ -879,6 +879,12 @@ int bfly_selftest_bounded_wait(int polls, void* stream) {
   return BFLY_OK;
 }
 
+int bfly_device_error_async(int* host_flag, void* stream) {
+  if (!host_flag) return BFLY_E_ARG;
+  return cudaMemcpyFromSymbolAsync(host_flag, bfly::g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost,
+                                   (cudaStream_t)stream) == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
+}
+
 int bfly_device_error(void) {
   int flag = 0;
   const int zero = 0;

@@ -9,6 +9,7 @@ gradient is additive over rows, so the chunks' partial gradients are summed on t
 """
 import torch
 
+from . import abi
 from .multiply import butterfly_multiply_bw, butterfly_multiply_fw
 
 
@@ -32,6 +33,7 @@ class HostPipeline:
         self.s_in = torch.cuda.Stream(self.device)
         self.s_comp = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
+        self.flag = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     def fw_bw(self, twiddle, x_host, grad_host, increasing_stride, out_host, d_x_host, d_twiddle_host):
         B = x_host.shape[0]
@@ -74,6 +76,8 @@ class HostPipeline:
             if d_tw_total is not None:
                 d_tw_total.record_stream(self.s_out)
                 d_twiddle_host.copy_(d_tw_total, non_blocking=True)
+            # the kernels' give-up flag travels with the last download; wait() looks at it
+            abi.device_error_async(self.flag)
             self.done = torch.cuda.Event()
             self.done.record(self.s_out)
         cur.wait_stream(self.s_out)
@@ -81,9 +85,14 @@ class HostPipeline:
         return d_tw_total
 
     def wait(self):
-        """Blocks the host until the downloads of the last fw_bw call have landed in host memory."""
+        """Blocks the host until the downloads of the last fw_bw call have landed in host memory; raises if
+        a kernel of that call gave up on a bounded wait (its results are then invalid)."""
         if getattr(self, "done", None) is not None:
             self.done.synchronize()
+            if int(self.flag.item()) != 0:
+                code = abi.device_error()  # clears the flag
+                raise RuntimeError("butterfly_b200: a kernel gave up on a bounded wait (flag %d); the results of the "
+                                   "last fw_bw call are invalid" % code)
 
     # The two copy directions alone, with the same chunking and streams: what each direction of the
     # host link sustains without the other (benchmarks report them beside the pipelined number).

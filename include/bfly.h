@@ -258,6 +258,12 @@ int64_t bfly_launch_count(void);
  * call, 1 = a wait ran out, 2 = a kernel found its shared-memory window misaligned) and clears it; a negative status on a CUDA error.  No counterpart in the
  * reference; meant for tests and for hosts that want to double-check a run. */
 int bfly_device_error(void);
+/* The same flag without waiting for the device: enqueues, on `stream`, a copy of the flag into
+ * *host_flag (host memory, pinned for a truly asynchronous copy).  The caller reads it after its own
+ * next synchronisation with that stream; the flag is not cleared (bfly_device_error clears it).  A
+ * training loop calls this once per step behind its kernels and looks at the value where it
+ * synchronises anyway (butterfly_b200/host.py does, in HostPipeline.wait). */
+int bfly_device_error_async(int* host_flag, void* stream);
 
 /* Self-test of that protocol, for tests: launches one warp that waits, for at most `polls` polls
  * (1 .. 2^20), on a barrier whose data never arrives, gives up, raises the flag and returns.  After

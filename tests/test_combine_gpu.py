@@ -1,6 +1,7 @@
 """combine.py and kops.py on the GPU: butterflies folded with diagonals, multiplied together, and
 as 2-D maps -- the tensor product run as ONE multiply against the reference's two-pass form
 (what the reference checks in tests/test_combine.py:16-95)."""
+import copy
 import math
 
 import pytest
@@ -35,6 +36,9 @@ def test_diagonal_butterfly(dev, cplx, increasing_stride, nblocks):
             want = b(x * d) if diag_first else b(x) * d
             bd = bb.combine.diagonal_butterfly(b, d, diag_first, inplace=False)
             assert_rtol_atol(bd(x), want, "diagonal folded into the butterfly", rtol=1e-4, atol=1e-4)
+            b2 = copy.deepcopy(b)
+            assert b2.diagonal_multiply_(d, diag_first) is b2   # the method form, in place
+            assert torch.equal(b2.twiddle, bd.twiddle)
 
 
 @pytest.mark.parametrize("cplx", [False, True])

@@ -195,3 +195,36 @@ def test_unitary_twiddle_kernels_match_the_torch_chain(dev):
     tw_ref = unitary_chain(ref_layer.twiddle)
     bb.butterfly_multiply(tw_ref, x.unsqueeze(1), True).squeeze(1).abs().pow(2).sum().backward()
     assert_rtol_atol(layer.twiddle.grad, ref_layer.twiddle.grad, "angle gradients through the layer", rtol=1e-4, atol=1e-4)
+
+
+def test_host_pipeline_results_and_give_up_flag(dev, oracle_mod):
+    """HostPipeline.fw_bw from pinned host memory: after wait() the host buffers hold the results (read at
+    once, no other synchronisation); a raised give-up flag makes wait() raise and is cleared."""
+    import butterfly_b200 as bb
+    from butterfly_b200 import abi
+    from butterfly_b200.host import HostPipeline
+    from conftest import rel_err
+    torch.manual_seed(6)
+    B, S, log_n, nb = 100, 2, 9, 2
+    n = 1 << log_n
+    tw = torch.randn(S, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
+    x = torch.randn(B, S, n).pin_memory()
+    g = torch.randn(B, S, n).pin_memory()
+    out = torch.empty(B, S, n).pin_memory()
+    d_x = torch.empty(B, S, n).pin_memory()
+    d_tw = torch.empty_like(tw).pin_memory()
+    pipe = HostPipeline(dev, chunks=3)
+    pipe.fw_bw(tw.to(dev), x, g, True, out, d_x, d_tw)
+    pipe.wait()
+    yr = oracle_mod.multiply_fw(tw, x, True)
+    dtr, dxr = oracle_mod.multiply_bw(tw, x, g, True)
+    assert rel_err(out, yr) < 2e-5 and rel_err(d_x, dxr) < 2e-5 and rel_err(d_tw, dtr) < 2e-5
+    # a kernel that gave up (the library's self-test warp) is reported at the pipeline's sync point
+    abi.selftest_bounded_wait(2048)
+    pipe.fw_bw(tw.to(dev), x, g, True, out, d_x, d_tw)
+    with pytest.raises(RuntimeError, match="gave up"):
+        pipe.wait()
+    assert abi.device_error() == 0
+    pipe.fw_bw(tw.to(dev), x, g, True, out, d_x, d_tw)
+    pipe.wait()
+    assert rel_err(out, yr) < 2e-5

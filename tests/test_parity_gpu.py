@@ -407,6 +407,10 @@ def test_bounded_wait_gives_up_and_reports(abi, dev, oracle_mod):
     host reads the status once, and the device keeps working."""
     assert abi.device_error() == 0
     abi.selftest_bounded_wait(4096)
+    flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    abi.device_error_async(flag)       # the non-synchronising read: value valid after the caller's own sync
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 1
     assert abi.device_error() == 1
     assert abi.device_error() == 0   # read and cleared
     tw = torch.randn(1, 1, 9, 256, 2, 2) / 2 ** 0.5
