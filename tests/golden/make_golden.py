@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the REFERENCE implementation.
 
-Run in a container that has the reference tree (default /root/reference) and the
-reference's CPU operator compiled by `make -C oracle refcpu`:
+Run where the reference tree is available (BFLY_REFERENCE_DIR, or a directory `reference` beside
+this repository) and the reference's CPU operator has been compiled by `make -C oracle refcpu`:
 
     python tests/golden/make_golden.py
 
@@ -28,8 +28,10 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("BFLY_REFERENCE_DIR", "/root/reference")
 sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+
+REF = oracle.reference_dir()  # BFLY_REFERENCE_DIR, or the sibling directory `reference`
 
 
 def _load_reference_python():
