@@ -23,8 +23,11 @@ class HostPipeline:
     out_host, d_x_host (B, nstacks, n); all pinned.
 
     fw_bw only ENQUEUES the work: when it returns, the caller's current stream has been made to
-    wait for the copies, but the host has not.  Call ``wait()`` (or synchronise the current
-    stream) before reading out_host / d_x_host / d_twiddle_host on the CPU.
+    wait for the kernels (the returned device tensor), not for the downloads, and the host has not
+    waited for anything.  Call ``wait()`` before reading out_host / d_x_host / d_twiddle_host on
+    the CPU, ``join()`` before device work that must follow the downloads.  Consecutive calls
+    overlap: the uploads of the next call run while the downloads of this one drain (downloads are
+    ordered among themselves, so re-using the same host buffers keeps the last call's results).
     """
 
     def __init__(self, device, chunks=8):
@@ -80,9 +83,16 @@ class HostPipeline:
             abi.device_error_async(self.flag)
             self.done = torch.cuda.Event()
             self.done.record(self.s_out)
-        cur.wait_stream(self.s_out)
+        # The caller's stream waits for the compute stream only (the returned device tensor is final
+        # there); it does not wait for the downloads, so that the uploads of the next call overlap them.
+        # Host code reads the host buffers after wait(); device work that must follow the downloads
+        # calls join().
         cur.wait_stream(self.s_comp)
         return d_tw_total
+
+    def join(self):
+        """Makes the current stream wait for the downloads enqueued so far (no host synchronisation)."""
+        torch.cuda.current_stream(self.device).wait_stream(self.s_out)
 
     def wait(self):
         """Blocks the host until the downloads of the last fw_bw call have landed in host memory; raises if
