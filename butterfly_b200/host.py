@@ -37,6 +37,7 @@ class HostPipeline:
         self.s_comp = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
         self.flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.inflight = []
 
     def fw_bw(self, twiddle, x_host, grad_host, increasing_stride, out_host, d_x_host, d_twiddle_host):
         B = x_host.shape[0]
@@ -44,6 +45,10 @@ class HostPipeline:
         n = grad_host.shape[2]
         dev = self.device
         cur = torch.cuda.current_stream(dev)
+        # at most two calls in flight: the host waits for the call before the previous one, so that
+        # device buffers are recycled instead of growing with every call enqueued ahead
+        while len(self.inflight) >= 2:
+            self.inflight.pop(0).synchronize()
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_stream(cur)
         bounds = [(B * c // self.chunks, B * (c + 1) // self.chunks) for c in range(self.chunks)]
@@ -83,6 +88,7 @@ class HostPipeline:
             abi.device_error_async(self.flag)
             self.done = torch.cuda.Event()
             self.done.record(self.s_out)
+            self.inflight.append(self.done)
         # The caller's stream waits for the compute stream only (the returned device tensor is final
         # there); it does not wait for the downloads, so that the uploads of the next call overlap them.
         # Host code reads the host buffers after wait(); device work that must follow the downloads
