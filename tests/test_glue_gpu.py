@@ -148,3 +148,25 @@ def test_fused_chain_gradients(dev, cplx):
     for a, b in zip(got, want):
         assert a.dtype == b.dtype
         assert_rtol_atol(a, b, "fused chain", rtol=1e-4, atol=2e-4)
+
+
+def test_glue_falls_back_link_by_link(dev):
+    """A product of more stage groups than one launch carries, ending in a real part, is not covered by
+    the fused launch (its intermediate rows need a complex buffer): the operator runs the links one by
+    one and still differentiates."""
+    import butterfly_b200 as bb
+    torch.manual_seed(5)
+    log_n, nb = 6, 16  # 96 stages = 48 two-stage groups of the complex forward
+    n = 1 << log_n
+    tw = (torch.randn(1, nb, log_n, n // 2, 2, 2, dtype=torch.complex64) / 2 ** 0.5).to(dev).requires_grad_(True)
+    x = torch.randn(5, 1, n, device=dev, requires_grad=True)
+    perm = torch.randperm(n, device=dev).to(torch.int32)
+    y = bb.butterfly_multiply_glue(tw, x, True, in_perm=perm, out_real=True)
+    want = bb.butterfly_multiply(tw, x.to(torch.complex64)[..., perm.long()], True).real
+    assert y.dtype == torch.float32
+    assert_rtol_atol(y, want.detach(), "fallback output", rtol=1e-5, atol=1e-5)
+    g = torch.randn_like(y)
+    gx, gt = torch.autograd.grad(y, (x, tw), g)
+    wx, wt = torch.autograd.grad(want, (x, tw), g)
+    assert_rtol_atol(gx, wx, "fallback d_input", rtol=1e-4, atol=1e-4)
+    assert_rtol_atol(gt, wt, "fallback d_twiddle", rtol=1e-4, atol=1e-4)
