@@ -74,6 +74,7 @@ bfly_bw3_kernel(const __grid_constant__ Bw3Params p, const __grid_constant__ CUt
   __syncthreads();  // the unit-position table is complete
   float tr[32], ar[32];  // tensor-memory fetch buffers (operands of the step that comes next, when prefetching)
   if (kBw3Prefetch) bw3_prefetch(p, acc, 0, tr, ar);
+  if (kBw3PrefetchTw) acc.ld32(bw3_step_sg(q.nsg, 0) * 64, tr);
   const int nsteps = bw3_num_steps(q.nsg);
   // bias gradient of a fused linear layer: this thread's 8 columns of the panel, summed over the
   // rows of the incoming gradient
@@ -131,7 +132,7 @@ bfly_bw3_kernel(const __grid_constant__ Bw3Params p, const __grid_constant__ CUt
     }
   }
   if (tid == 0) tma_store_wait_all();
-  if (kBw3Prefetch) acc.wait_ld();  // the fetch issued by the last step
+  if (kBw3Prefetch || kBw3PrefetchTw) acc.wait_ld();  // the fetch issued by the last step
   if (!gave_up) bw3_flush(p, acc, stack, pbase, tid);
   if (!gave_up && q.dbias) {
 #pragma unroll

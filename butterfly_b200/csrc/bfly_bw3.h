@@ -34,6 +34,12 @@ constexpr int kBw3TmemCols = 256; // per CTA: 4 sub-groups x (32 twiddle + 32 ac
 // 1: a step requests the tensor-memory operands of the step after it before it ends (their latency
 // overlaps the barrier; costs 64 registers that stay live across steps); 0: every step fetches its own
 constexpr bool kBw3Prefetch = BFLY_BW3_PREFETCH != 0;
+#ifndef BFLY_BW3_PREFETCH_TW
+#define BFLY_BW3_PREFETCH_TW 0
+#endif
+// 1: a step requests only the twiddles of the step after it (32 registers live across the barrier;
+// measured: no gain over 0)
+constexpr bool kBw3PrefetchTw = BFLY_BW3_PREFETCH_TW != 0 && !kBw3Prefetch;
 
 // Stage kinds on the 4 packed registers (register index m = two window bits):
 //   0 / 1: radix-2 stage between registers that differ in register bit 0 / 1
@@ -332,13 +338,17 @@ constexpr int kBw3RowBytes = 4096;                       // 1024 floats
 constexpr int kBw3TileBytes = kBw3Rows * kBw3RowBytes;   // one snapshot tile of a batch
 
 // Forward recompute of sub-group j over the batch: snapshot tile j -> tile j + 1.
-template <int NST, int KA, int KB, bool CONTIG>
-BFLY_HD void bw3_fw_rows(const smaddr_t* a, const f2* T) {
+// `ready` runs after the shared-memory loads have been issued and before the arithmetic: it waits
+// for the step's tensor-memory operands and packs them into T (and A), so that the two latencies
+// overlap instead of following each other.
+template <int NST, int KA, int KB, bool CONTIG, typename READY>
+BFLY_HD void bw3_fw_rows(const smaddr_t* a, const f2* T, READY&& ready) {
   f2 v[kBw3Rows][4];
   static_for<0, kBw3Rows>([&](auto rc) {
     constexpr int r = decltype(rc)::value;
     bw3_unit_ld<CONTIG, r * kBw3RowBytes>(a, v[r]);
   });
+  ready();
   bw3_stage_fw<KA>(v, T);
   if constexpr (NST > 1) bw3_stage_fw<KB>(v, T + 8);
   static_for<0, kBw3Rows>([&](auto rc) {
@@ -347,14 +357,15 @@ BFLY_HD void bw3_fw_rows(const smaddr_t* a, const f2* T) {
   });
 }
 // Reverse step of sub-group j over the batch: a = addresses in snapshot tile j, ag = in the gradient tile.
-template <int NST, int KA, int KB, bool CONTIG>
-BFLY_HD void bw3_bw_rows(const smaddr_t* a, const smaddr_t* ag, const f2* T, f2* A) {
+template <int NST, int KA, int KB, bool CONTIG, typename READY>
+BFLY_HD void bw3_bw_rows(const smaddr_t* a, const smaddr_t* ag, const f2* T, f2* A, READY&& ready) {
   f2 x[kBw3Rows][4], g[kBw3Rows][4];
   static_for<0, kBw3Rows>([&](auto rc) {
     constexpr int r = decltype(rc)::value;
     bw3_unit_ld<CONTIG, r * kBw3RowBytes>(a, x[r]);
     bw3_unit_ld<CONTIG, r * kBw3RowBytes>(ag, g[r]);
   });
+  ready();
   if constexpr (NST > 1) {
     f2 x1[kBw3Rows][4];
 #pragma unroll
@@ -430,19 +441,34 @@ BFLY_HD void bw3_step(const Bw3Params& p, const ACC& acc, const uint32_t* meta, 
   const uint32_t word = bw3_step_table(const_cast<uint32_t*>(meta), nsg)[j];
   const int var = (int)(word & 0xff);
   const bool contig = (word >> 8) != 0;
-  if (!kBw3Prefetch) bw3_prefetch(p, acc, step, tr, ar);
-  acc.wait_ld();
-  f2 T[16];
-  bw3_pack16(tr, T);
-  bw3_pack16(tr + 16, T + 8);
+  if (kBw3PrefetchTw) {
+    if (is_bw) acc.ld32(j * 64 + 32, ar);  // the twiddles were requested by the step before
+  } else if (!kBw3Prefetch) {
+    bw3_prefetch(p, acc, step, tr, ar);
+  }
+  f2 T[16], A[16];
   const int next = step + 1 < bw3_num_steps(nsg) ? step + 1 : 0;
+  // the next step's operands, unless it re-reads the accumulators this step is about to store
+  const bool same_acc = is_bw && bw3_step_is_bw(nsg, next) && bw3_step_sg(nsg, next) == j;
+  auto ready = [&]() {
+    acc.wait_ld();
+    bw3_pack16(tr, T);
+    bw3_pack16(tr + 16, T + 8);
+    if (is_bw) {
+      bw3_pack16(ar, A);
+      bw3_pack16(ar + 16, A + 8);
+    }
+    // the fetch buffers are free (T and A hold the packed copies)
+    if (kBw3Prefetch && !same_acc) bw3_prefetch(p, acc, next, tr, ar);
+    // twiddles of the step that follows: their latency overlaps this step's arithmetic and the barrier
+    if (kBw3PrefetchTw) acc.ld32(bw3_step_sg(nsg, next) * 64, tr);
+  };
   if (!is_bw) {
-    if (kBw3Prefetch) bw3_prefetch(p, acc, next, tr, ar);  // the fetch buffers are free: T holds the packed copy
     switch (var) {
 #define BFLY_X(ID, N, KA, KB)                                             \
   case ID:                                                                \
-    if (contig) bw3_fw_rows<N, KA, KB, true>(a, T);                       \
-    else bw3_fw_rows<N, KA, KB, false>(a, T);                             \
+    if (contig) bw3_fw_rows<N, KA, KB, true>(a, T, ready);                \
+    else bw3_fw_rows<N, KA, KB, false>(a, T, ready);                      \
     break;
       BFLY_BW3_VARIANTS(BFLY_X)
 #undef BFLY_X
@@ -451,17 +477,11 @@ BFLY_HD void bw3_step(const Bw3Params& p, const ACC& acc, const uint32_t* meta, 
     return;
   }
   bw3_addresses(sm_addr(sm), o, nsg, ag);  // the gradient tile follows the nsg snapshot tiles
-  f2 A[16];
-  bw3_pack16(ar, A);
-  bw3_pack16(ar + 16, A + 8);
-  // the next step's operands, unless it re-reads the accumulators this step is about to store
-  const bool same_acc = bw3_step_is_bw(nsg, next) && bw3_step_sg(nsg, next) == j;
-  if (kBw3Prefetch && !same_acc) bw3_prefetch(p, acc, next, tr, ar);
   switch (var) {
 #define BFLY_X(ID, N, KA, KB)                                             \
   case ID:                                                                \
-    if (contig) bw3_bw_rows<N, KA, KB, true>(a, ag, T, A);                \
-    else bw3_bw_rows<N, KA, KB, false>(a, ag, T, A);                      \
+    if (contig) bw3_bw_rows<N, KA, KB, true>(a, ag, T, A, ready);         \
+    else bw3_bw_rows<N, KA, KB, false>(a, ag, T, A, ready);               \
     break;
     BFLY_BW3_VARIANTS(BFLY_X)
 #undef BFLY_X
