@@ -210,7 +210,7 @@ def run_reference_arm(args):
 
 # (config, kernel) -> (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch of the capture):
 # mean over the phase launches of one backward call in the ncu capture summarised under profiles/
-NCU_DRAM_BYTES = {("cfg2", "bfly_bw3_kernel"): (174.6e6, 4096), ("cfg2", "bfly_bw2_kernel"): (165.1e6, 4096),
+NCU_DRAM_BYTES = {("cfg2", "bfly_bw3_kernel"): (569.9e6, 12288), ("cfg2", "bfly_bw2_kernel"): (165.1e6, 4096),
                   ("cfg2", "bfly_fw2_kernel"): (85.9e6, 4096)}
 
 
