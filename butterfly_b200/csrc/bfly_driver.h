@@ -213,9 +213,12 @@ int drive_fw2(E& ex, const Problem& q, const std::vector<Stage>& st, int t0, int
   twiddle_stack_sizes(q, stk);
   p.tw = tw2; p.tw_stack = stk[0];
   p.B = q.B; p.S = q.S; p.log_n = q.log_n;
-  const int ctas = options().fw2_ctas == 1 ? 1 : 2;
-  p.P = kFw2Threads / ((1 << q.log_n) / 16);
-  p.Rw = fw2_rows_per_thread(q.B, q.S, p.P, ctas * ex.num_sms(), ctas == 1 ? 14 : 7);
+  // rows of 8192 columns: one 512-thread CTA per SM with a 7-row tile (224 KB), the whole product in one launch
+  const bool wide = q.log_n == kFw2WideLogN;
+  const int ctas = (wide || options().fw2_ctas == 1) ? 1 : 2;
+  p.threads = wide ? kFw2WideThreads : kFw2Threads;
+  p.P = p.threads / ((1 << q.log_n) / 16);
+  p.Rw = fw2_rows_per_thread(q.B, q.S, p.P, ctas * ex.num_sms(), (ctas == 1 && !wide) ? 14 : 7);
   p.R = p.P * p.Rw;
   p.packed = static_cast<float*>(pack_ws);
   p.packed_stack = (int64_t)groups.back().pk_off + (int64_t)groups.back().nst * 8 * ((1 << q.log_n) / 16);

@@ -71,14 +71,15 @@ __device__ __forceinline__ void tma_store_box4(const CUtensorMap* map, uint32_t 
 // with a warp barrier between windows inside the chunk and a CTA barrier around the windows
 // that reach across chunks -- and stores the box.  Every wait is bounded; a warp whose wait runs
 // out raises the CTA's give-up flag, which all warps read after the next CTA barrier.
-template <int CTAS>
-__global__ void __launch_bounds__(kFw2Threads, CTAS)
+// THREADS = 512 (CTAS = 1): rows of 8192 columns, sixteen warps with one 512-column chunk each.
+template <int CTAS, int THREADS>
+__global__ void __launch_bounds__(THREADS, CTAS)
 bfly_fw2_kernel(const __grid_constant__ Fw2Params p, const __grid_constant__ Fw2Maps maps, int* __restrict__ err) {
   extern __shared__ __align__(1024) unsigned char smem[];
   float* tile = reinterpret_cast<float*>(smem);
   const uint32_t smem0 = tma_smem(smem);
   const uint32_t tile_bytes = (uint32_t)fw2_tile_bytes(p);
-  volatile int* give_up = reinterpret_cast<volatile int*>(smem + tile_bytes + 64);
+  volatile int* give_up = reinterpret_cast<volatile int*>(smem + tile_bytes + (THREADS / 32) * 8);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if ((smem0 & 1023u) != 0) {  // the hardware swizzle works on address bits
     if (tid == 0) atomicExch(err, 2);
@@ -156,7 +157,7 @@ bfly_fw2_kernel(const __grid_constant__ Fw2Params p, const __grid_constant__ Fw2
   // With one CTA per SM there are registers for two sets of twiddles: the set of the next group
   // (of the next tile, after the last group) is fetched while the current group computes.  TA/TB
   // trade places every group; `flip` says which one is current.
-  constexpr bool kPrefetch = (CTAS == 1);
+  constexpr bool kPrefetch = (CTAS == 1 && THREADS == 256);
   f2 TA[48], TB[kPrefetch ? 48 : 1];
   bool flip = false;
   if (kPrefetch && blockIdx.x < ntiles) fw2_fetch_tw(p, p.g[0], (int)(blockIdx.x % p.S), tid, TA);
@@ -250,7 +251,7 @@ int bias_add_launch(float* out, const float* bias, int64_t B, int len, int64_t p
   return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
 }
 
-template <int CTAS>
+template <int CTAS, int THREADS>
 static int fw2_launch_ctas(const Fw2Params& p, const Fw2Maps& maps, int grid, size_t smem, cudaStream_t stream, int* err) {
   static std::mutex mu;
   static bool attr_done[64] = {false};
@@ -259,9 +260,9 @@ static int fw2_launch_ctas(const Fw2Params& p, const Fw2Maps& maps, int grid, si
   {
     std::lock_guard<std::mutex> lk(mu);
     if (!attr_done[dev]) {
-      if (cudaFuncSetAttribute(bfly_fw2_kernel<CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(bfly_fw2_kernel<CTAS, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (CTAS == 1 ? 227 : 113) * 1024) != cudaSuccess ||
-          cudaFuncSetAttribute(bfly_fw2_kernel<CTAS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+          cudaFuncSetAttribute(bfly_fw2_kernel<CTAS, THREADS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
         cudaGetLastError();
         return BFLY_E_CUDA;
@@ -269,7 +270,7 @@ static int fw2_launch_ctas(const Fw2Params& p, const Fw2Maps& maps, int grid, si
       attr_done[dev] = true;
     }
   }
-  bfly_fw2_kernel<CTAS><<<grid, kFw2Threads, smem, stream>>>(p, maps, err);
+  bfly_fw2_kernel<CTAS, THREADS><<<grid, THREADS, smem, stream>>>(p, maps, err);
   return cudaGetLastError() == cudaSuccess ? BFLY_OK : BFLY_E_CUDA;
 }
 
@@ -313,8 +314,9 @@ int fw2_launch(const Fw2Params& p_in, int ctas_per_sm, int sms, cudaStream_t str
   bfly_fw2_pack_kernel<<<(int)std::min<int64_t>((entries + 255) / 256, 4 * sms), 256, 0, stream>>>(p);
   if (cudaGetLastError() != cudaSuccess) return BFLY_E_CUDA;
   const int grid = (int)std::min<int64_t>(fw2_num_tiles(p), (int64_t)ctas_per_sm * sms);
-  const int rc = ctas_per_sm == 1 ? fw2_launch_ctas<1>(p, maps, grid, smem, stream, err)
-                                  : fw2_launch_ctas<2>(p, maps, grid, smem, stream, err);
+  const int rc = fw2_threads(p) == kFw2WideThreads ? fw2_launch_ctas<1, kFw2WideThreads>(p, maps, grid, smem, stream, err)
+                 : ctas_per_sm == 1              ? fw2_launch_ctas<1, kFw2Threads>(p, maps, grid, smem, stream, err)
+                                                 : fw2_launch_ctas<2, kFw2Threads>(p, maps, grid, smem, stream, err);
   if (rc == BFLY_OK && launches) *launches = 2;
   return rc;
 }

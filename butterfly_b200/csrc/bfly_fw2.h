@@ -26,6 +26,8 @@ constexpr int kFw2Threads = 256;
 constexpr int kFw2MaxGroups = 48;
 constexpr int kFw2MaxSnap = 8;
 constexpr int kFw2MinLogN = 9, kFw2MaxLogN = 12;
+// rows of 8192 columns run on one 512-thread CTA per SM (16 warps, one 512-column chunk each)
+constexpr int kFw2WideLogN = 13, kFw2WideThreads = 512;
 constexpr int kFw2Declined = 1;  // run_fw2: the launch does not qualify, use the generic kernel
 
 // ---------------------------------------------------------------- packed pairs
@@ -159,6 +161,7 @@ struct Fw2Params {
   int view;
   int view_row;
   Panel panel;
+  int threads;       // threads per CTA: 0 = 256; 512 for rows of 8192 columns (one CTA per SM)
   int ngroups;
   Fw2Group g[kFw2MaxGroups];
 };
@@ -170,7 +173,7 @@ BFLY_HD int fw2_view_col(const Fw2Params& p, int pi, int c) { return p.panel.col
 // is written (slot i).  Returns false when the range does not qualify.
 inline bool plan_fw2_groups(const std::vector<Stage>& st, int t0, int t1, const std::vector<int>& cuts, int log_n,
                             std::vector<Fw2Group>& out) {
-  if (log_n < kFw2MinLogN || log_n > kFw2MaxLogN) return false;
+  if (log_n < kFw2MinLogN || log_n > kFw2WideLogN) return false;
   for (int t = t0; t < t1; ++t)
     if (st[t].radix != 2 || st[t].which != 0) return false;
   auto is_cut = [&](int idx) { return std::find(cuts.begin(), cuts.end(), idx) != cuts.end(); };
@@ -460,15 +463,19 @@ BFLY_HD void fw2_group_dispatch(const Fw2Params& p, const Fw2Group& g, float* ti
 BFLY_HD int64_t fw2_num_tiles(const Fw2Params& p) { return (int64_t)((p.B + p.R - 1) / p.R) * p.S; }
 BFLY_HD size_t fw2_tile_bytes(const Fw2Params& p) { return ((size_t)p.R * sizeof(float)) << p.log_n; }
 // the tile, then one mbarrier per warp and the give-up flag
-BFLY_HD size_t fw2_smem_bytes(const Fw2Params& p) { return fw2_tile_bytes(p) + 8 * 8 + 16; }
+BFLY_HD int fw2_threads(const Fw2Params& p) { return p.threads > 0 ? p.threads : kFw2Threads; }
+BFLY_HD size_t fw2_smem_bytes(const Fw2Params& p) { return fw2_tile_bytes(p) + (size_t)(fw2_threads(p) / 32) * 8 + 16; }
 // bytes of the re-ordered twiddle copy (same size as the twiddle tensor): 0 when the shape does
 // not take this kernel.  Rows wider than 4096 columns (one stack, up to 2^19) run pass by pass on
 // panels; a pass holds at most 24 stages (the low 12 bits at the end of one block and the start of
 // the next) and re-uses the space.
 inline size_t fw2_packed_bytes(int S, int log_n, int nblocks) {
-  if (log_n > kFw2MaxLogN && log_n <= 19 && S == 1) return (size_t)24 * ((size_t)8 << log_n);
+  const size_t whole = (size_t)S * nblocks * log_n * ((size_t)8 << log_n);
+  const size_t passes = (log_n > kFw2MaxLogN && log_n <= 19 && S == 1) ? (size_t)24 * ((size_t)8 << log_n) : 0;
+  if (log_n == kFw2WideLogN) return whole > passes ? whole : passes;  // one launch, or the panel passes as a fallback
+  if (passes) return passes;
   if (log_n < kFw2MinLogN || log_n > kFw2MaxLogN) return 0;
-  return (size_t)S * nblocks * log_n * ((size_t)8 << log_n);
+  return whole;
 }
 
 }  // namespace bfly

@@ -61,7 +61,7 @@ struct EmulExec {
       const int stack = (int)(t % p.S), row0 = (int)(t / p.S) * p.R;
       box_copy(true, p.x, nullptr, p.x_sB, p.x_sS, std::min(p.x_cols, n), stack, row0);
       for (int gi = 0; gi < p.ngroups; ++gi) {
-        for (int tid = 0; tid < kFw2Threads; ++tid) {
+        for (int tid = 0; tid < fw2_threads(p); ++tid) {
           f2 T[48];
           fw2_fetch_tw(p, p.g[gi], stack, tid, T);
           if (tid & 1) fw2_group_dispatch<true>(p, p.g[gi], tile.data(), tid, T);  // both row-loop forms

@@ -43,9 +43,13 @@ def test_workspace_query_and_argument_errors():
     assert abi.fw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 10 * 512 * 16
     assert abi.fw_workspace_bytes(torch.float32, 256, 3, 12, 2) == 3 * 2 * 12 * 2048 * 16
     assert abi.fw_workspace_bytes(torch.float32, 256, 1, 8, 1) == 0
-    # wider single-stack rows run pass by pass on 4096-column panels: room for the largest pass (24 stages)
+    # rows of 8192 columns run in one launch on a 512-thread CTA (twiddle-sized scratch, or room for the
+    # panel passes that serve as its fallback); wider single-stack rows run pass by pass on 4096-column
+    # panels: room for the largest pass (24 stages)
     assert abi.fw_workspace_bytes(torch.float32, 256, 1, 13, 1) == 24 * 8 * 8192
-    assert abi.fw_workspace_bytes(torch.float32, 256, 2, 13, 1) == 0
+    assert abi.fw_workspace_bytes(torch.float32, 256, 2, 13, 3) == 2 * 3 * 13 * 8 * 8192
+    assert abi.fw_workspace_bytes(torch.float32, 256, 1, 14, 1) == 24 * 8 * 16384
+    assert abi.fw_workspace_bytes(torch.float32, 256, 2, 14, 1) == 0
     assert abi.fw_workspace_bytes(torch.complex64, 256, 1, 10, 1) == 0
     # 10 stages: two phases = one snapshot, plus the scratch of the forward pass that writes it
     assert abi.bw_workspace_bytes(torch.float32, 256, 1, 10, 1) == 256 * 1024 * 4 + 10 * 512 * 16

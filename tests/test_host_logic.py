@@ -453,28 +453,36 @@ def test_forward_with_glue_operators(emul, oracle_mod, cplx):
 
 
 def test_packed_pair_forward_on_wide_rows(emul, oracle_mod):
-    """float32 rows of 8192 / 16384 columns run the packed-pair forward pass by pass on 4096-column
-    panels (contiguous for the low bits, 32-column blocks at a stride for the top bits), also as the
-    backward's snapshot pass; input narrower than n falls back to the generic kernel."""
+    """float32 rows of 8192 columns run the packed-pair forward in one launch (512-thread CTAs); rows of
+    16384 columns pass by pass on 4096-column panels (contiguous for the low bits, 32-column blocks at
+    a stride for the top bits); both also as the backward's snapshot pass.  Input that the kernel's
+    descriptors cannot cover falls back to the generic kernel."""
     torch.manual_seed(21)
     for log_n, nb, B, inc in ((13, 2, 5, True), (13, 1, 3, False), (14, 2, 2, True)):
         n = 1 << log_n
         tw = torch.randn(1, nb, log_n, n // 2, 2, 2) / 2 ** 0.5
         x = torch.randn(B, 1, n)
         calls = emul.bfly_emul_fw2_calls()
-        y = emul_fw(emul, tw, None, x, inc, n - 100, log_n, nb, False, 256, tail_untouched=False)
-        assert emul.bfly_emul_fw2_calls() - calls == (3 if nb == 2 else 2), (log_n, nb)
-        assert rel_err(y, oracle_mod.multiply_fw(tw, x, inc, n - 100)) < 2e-5
+        y = emul_fw(emul, tw, None, x, inc, n - 96, log_n, nb, False, 256, tail_untouched=False)
+        assert emul.bfly_emul_fw2_calls() - calls == (1 if log_n == 13 else 3), (log_n, nb)
+        assert rel_err(y, oracle_mod.multiply_fw(tw, x, inc, n - 96)) < 2e-5
         g = torch.randn(B, 1, n)
         calls = emul.bfly_emul_fw2_calls()
         d2, _, dx = emul_bw(emul, tw, None, x, g, inc, log_n, nb, False, 256)
         assert emul.bfly_emul_fw2_calls() > calls  # the snapshot pass
         dtr, dxr = oracle_mod.multiply_bw(tw, x, g, inc)
         assert rel_err(d2, dtr) < 2e-5 and rel_err(dx, dxr) < 2e-5
-    # ragged input: generic passes
+    # two stacks of 8192 columns: still one launch; with the one-launch path refused (input not a
+    # multiple of 32 columns) a single stack cannot take the panel passes either: generic passes
     n = 1 << 13
+    tw2 = torch.randn(2, 1, 13, n // 2, 2, 2) / 2 ** 0.5
+    x2 = torch.randn(3, 2, n)
+    calls = emul.bfly_emul_fw2_calls()
+    y2 = emul_fw(emul, tw2, None, x2, False, n, 13, 1, False, 256)
+    assert emul.bfly_emul_fw2_calls() - calls == 1
+    assert rel_err(y2, oracle_mod.multiply_fw(tw2, x2, False, n)) < 2e-5
     tw = torch.randn(1, 1, 13, n // 2, 2, 2) / 2 ** 0.5
-    x = torch.randn(3, 1, n - 64)
+    x = torch.randn(3, 1, n - 65)
     calls = emul.bfly_emul_fw2_calls()
     y = emul_fw(emul, tw, None, x, True, n, 13, 1, False, 256)
     assert emul.bfly_emul_fw2_calls() == calls
