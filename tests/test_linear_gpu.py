@@ -24,7 +24,7 @@ def _oracle_layer(oracle_mod, tw, x, bias, g, inc, out_size, dtype=None):
     return y, dt, dx.sum(1), cast(g).sum(0)
 
 
-@pytest.mark.parametrize("log_n,S", [(10, 4), (11, 2), (12, 1), (9, 3)])
+@pytest.mark.parametrize("log_n,S", [(10, 4), (11, 2), (12, 1), (9, 3), (13, 2)])
 def test_fused_linear_through_c_abi(oracle_mod, log_n, S):
     from butterfly_b200 import abi
     dev = torch.device("cuda", 0)
