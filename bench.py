@@ -554,38 +554,6 @@ def run_gpu_arm(args):
                 "backward_frac_of_hbm_peak": bwb / (bw_total_ms * 1e-3) / 1e9 / peak,
                 "op_frac_of_hbm_peak": (step_bytes / (ms_per_step * 1e-3) / 1e9) / peak}
 
-    # ---- the other configurations and the reference's CUDA extension (the kernel to beat), untimed
-    # by the headline loop
-    other, ref_cuda_note = None, None
-    if rank == 0 and world == 1 and not args.no_other and args.batch is None:
-        ref_ops = None
-        if not args.no_refcuda:
-            try:
-                import oracle
-                if oracle.reference_available(cuda=True):
-                    ref_ops = oracle.load_reference_ops(cuda=True)
-                else:
-                    ref_cuda_note = {"kind": "unavailable", "why": "oracle/_ref/_butterfly_ref_cuda.so not built"}
-            except Exception as e:  # the comparison column is optional
-                ref_cuda_note = {"kind": "unavailable", "why": repr(e)[:200]}
-        other = []
-        for name in ("cfg1", "cfg2", "cfg3", "cfg4", "cfg5"):
-            other.append(measure_config(bb, configs, name, dev, peak, ref_ops=ref_ops))
-        for log_n in (10, 11, 13):
-            other.append(measure_config(bb, configs, "two-block n=%d" % (1 << log_n), dev, peak,
-                                        make=lambda: two_block_inputs(log_n, dev), ref_ops=ref_ops if log_n <= 11 else None))
-        other.append(measure_linear_layer(bb, configs, dev, peak))
-        other.extend(measure_glue_rows(bb, dev, peak))
-        if ref_ops is not None:
-            ref_cuda_note = {"kind": "reference", "library": "oracle/_ref/_butterfly_ref_cuda.so",
-                             "what": "csrc/cuda/butterfly_cuda.cu of the reference compiled unmodified for sm_100; "
-                                     "reference_cuda_*_ms in other_configs"}
-    elif rank == 0 and world > 1 and not args.no_other:
-        # the multi-GPU configuration: this rank's shard of cfg5 (8192 rows, stack-broadcast input)
-        other = [measure_config(bb, configs, "cfg5", dev, peak,
-                                make=lambda: configs.make_inputs("cfg5", rank=rank, device=dev)),
-                 measure_linear_layer(bb, configs, dev, peak, rank=rank)]
-
     # ---- end to end through the public operator with host buffers
     e2e = None
     if not args.no_e2e:
@@ -633,6 +601,38 @@ def run_gpu_arm(args):
                "steps": e2e_steps, "api": "butterfly_b200.host.HostPipeline.fw_bw (%d row chunks, 3 streams)" % args.e2e_chunks,
                "h2d_alone_gbs_per_rank": h2d / h2d_ms / 1e6, "d2h_alone_gbs_per_rank": (d2h - hdt.numel() * sz) / d2h_ms / 1e6,
                "pcie_gbs_aggregate": (h2d + d2h) * world / (ems / e2e_steps) / 1e6}
+
+    # ---- the other configurations and the reference's CUDA extension (the kernel to beat), untimed
+    # by the headline loop
+    other, ref_cuda_note = None, None
+    if rank == 0 and world == 1 and not args.no_other and args.batch is None:
+        ref_ops = None
+        if not args.no_refcuda:
+            try:
+                import oracle
+                if oracle.reference_available(cuda=True):
+                    ref_ops = oracle.load_reference_ops(cuda=True)
+                else:
+                    ref_cuda_note = {"kind": "unavailable", "why": "oracle/_ref/_butterfly_ref_cuda.so not built"}
+            except Exception as e:  # the comparison column is optional
+                ref_cuda_note = {"kind": "unavailable", "why": repr(e)[:200]}
+        other = []
+        for name in ("cfg1", "cfg2", "cfg3", "cfg4", "cfg5"):
+            other.append(measure_config(bb, configs, name, dev, peak, ref_ops=ref_ops))
+        for log_n in (10, 11, 13):
+            other.append(measure_config(bb, configs, "two-block n=%d" % (1 << log_n), dev, peak,
+                                        make=lambda: two_block_inputs(log_n, dev), ref_ops=ref_ops if log_n <= 11 else None))
+        other.append(measure_linear_layer(bb, configs, dev, peak))
+        other.extend(measure_glue_rows(bb, dev, peak))
+        if ref_ops is not None:
+            ref_cuda_note = {"kind": "reference", "library": "oracle/_ref/_butterfly_ref_cuda.so",
+                             "what": "csrc/cuda/butterfly_cuda.cu of the reference compiled unmodified for sm_100; "
+                                     "reference_cuda_*_ms in other_configs"}
+    elif rank == 0 and world > 1 and not args.no_other:
+        # the multi-GPU configuration: this rank's shard of cfg5 (8192 rows, stack-broadcast input)
+        other = [measure_config(bb, configs, "cfg5", dev, peak,
+                                make=lambda: configs.make_inputs("cfg5", rank=rank, device=dev)),
+                 measure_linear_layer(bb, configs, dev, peak, rank=rank)]
 
     # the sampler ran through the kernel-timed loop, the per-kernel pass and the end-to-end loop
     clocks = sampler.stop() if rank == 0 else None
