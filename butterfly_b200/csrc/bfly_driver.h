@@ -41,7 +41,7 @@ struct Options {
   int bw_rows = -1;     // backward: rows per batch
   int bw_maxsg = -1;    // backward: sub-groups per phase
   int bw_c64_kw2 = 1;   // complex64 radix-2 backward on 2-stage sub-groups (tensor-memory kernel) for n >= 1024
-  int bw3_min_rows = 160;  // fewest rows per CTA for which a plain backward phase takes the packed-pair kernel
+  int bw3_min_rows = 100;  // fewest rows per CTA for which a plain backward phase takes the packed-pair kernel
   int autograd_save = -1;  // torch autograd operator: keep the forward's snapshots for the backward
 };
 struct OptionName { const char* name; const char* env; int Options::*field; };
@@ -630,8 +630,8 @@ int drive_bw(E& ex, const Problem& q, const T* tw2, const T* tw4, const T* x, in
           b.vec_g = vec_ok<T>(b.gin, b.gin_sB, b.gin_sS);
           b.vec_o = vec_ok<T>(b.gout, b.gout_sB, b.gout_sS);
           // Its per-CTA set-up (pairing the twiddles into tensor memory) is amortised over the CTA's
-          // rows: with few rows per CTA the scalar tensor-memory kernel is faster (measured: equal
-          // from ~200 rows per CTA up, 10-25 % faster at 50 and fewer).
+          // rows: with few rows per CTA the scalar tensor-memory kernel is faster (measured: the
+          // packed-pair kernel 4-5 % faster at 222 rows per CTA, equal at 111, 6-13 % slower at 56 and 28).
           const int rc3 = rows3 >= o.bw3_min_rows ? ex.run_bw3(p3) : kFw2Declined;
           if (rc3 == BFLY_OK) continue;
           if (rc3 != kFw2Declined) return rc3;
