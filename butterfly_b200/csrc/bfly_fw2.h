@@ -1,4 +1,6 @@
-// Packed-pair forward kernel for float32 radix-2 products on rows of 512 .. 4096 columns.
+// Packed-pair forward kernel for float32 radix-2 products on rows of 512 .. 8192 columns (256-thread
+// CTAs, two per SM, up to 4096 columns; one 512-thread CTA per SM for 8192), and, panel by panel, on
+// wider rows.
 //
 // A thread owns 16 elements of a row: the 8 values of a three-bit register window, each with
 // its right-hand neighbour (column bit 0), held as 8 two-float registers.  A butterfly stage on

@@ -19,9 +19,9 @@
  *             element strides of the batch and stack dims (x_sS may be 0: one row
  *             broadcast to every stack, as Butterfly.pre_process's expand() produces)
  *   out       (batch, nstacks, n) contiguous; only columns < output_size are written (products
- *             with rows wider than 16 KB -- n > 4096 float32, > 2048 complex64 -- or of more than
- *             about 120 stages run as several launches and use the columns beyond output_size as
- *             working space)
+ *             with rows wider than one launch covers -- n > 8192 float32 (4096 without the forward's
+ *             workspace), > 2048 complex64 -- or of more than about 120 stages run as several
+ *             launches and use the columns beyond output_size as working space)
  *   grad      (batch, nstacks, output_size), strides g_sB / g_sS, last dim contiguous
  *   d_twiddle (d_twiddle4, d_twiddle2): like the twiddle they belong to, 16-byte aligned
  *   d_x       (batch, nstacks, max(input_size, n)) contiguous; columns < input_size
@@ -62,7 +62,8 @@ int bfly_cuda_version(void);
 
 /* Scratch bytes the forward can use for this shape (0 = none; dtype is BFLY_F32 or BFLY_C64):
  * room for a copy of the twiddles re-ordered for the fastest forward kernel (float32 rows of
- * 512 .. 4096 columns).  Returns a negative status on error. */
+ * 512 .. 8192 columns in one launch; wider single-stack rows pass by pass).  Returns a negative
+ * status on error. */
 int64_t bfly_fw_workspace_bytes(int dtype, int batch, int nstacks, int log_n, int nblocks);
 
 /* Forward: out = B_{nblocks-1} ... B_0 x.
